@@ -1,0 +1,480 @@
+// Host side of the C ABI declared in include/fwd_eb.h: argument checks,
+// strategy choice and kernel launches.  No allocation, no synchronisation.
+//
+// Replaces the launch code of Forward's EmbeddingBag plugin
+// (source/trt_engine/trt_network_crt/plugins/embedding_bag_plugin/
+// embedding_bag_plugin.cu:182-206) and the rank / op dispatch of
+// EmbeddingBagPlugin::enqueue (embedding_bag_plugin.cpp:146-189).
+#include <atomic>
+#include <climits>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "eb_kernels.cuh"
+#include "fwd_eb.h"
+
+namespace fwd_eb {
+
+static thread_local char g_err[512] = "";
+static std::atomic<uint64_t> g_launches{0};
+
+static int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+  return (int)e;
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Shape-derived launch plan.
+struct Plan {
+  PoolArgs a;
+  bool vec;      // 16-byte chunks (else one element per chunk)
+  int ve;        // elements per chunk
+  int cpl;       // chunks per lane: 1, 2 or 4
+  int tiles;     // column tiles (grid.y)
+  int op;        // Op
+  int strategy;  // resolved FWD_EB_STRATEGY_*
+  bool table_f16;
+};
+
+static int ceil_log2(int x) {
+  int l = 0;
+  while ((1 << l) < x) ++l;
+  return l;
+}
+
+static constexpr int kSmCount = 148;
+
+// Split factor for the SPLIT strategy: enough CTAs for about four per SM, no
+// slice shorter than 256 indices, at most 64 splits.
+static int choose_splits(const fwd_eb_params* p) {
+  if (p->num_bags <= 0) return 1;
+  long long avg = p->fixed_len > 0 ? p->fixed_len : p->num_indices / p->num_bags;
+  long long want = (4LL * kSmCount + p->num_bags - 1) / p->num_bags;
+  long long cap = avg / 256;
+  if (want > cap) want = cap;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+static size_t split_workspace_bytes(const fwd_eb_params* p, int splits) {
+  if (splits <= 1) return 0;
+  size_t slots = (size_t)p->num_bags * (size_t)splits;
+  size_t acc = slots * (size_t)p->dim * sizeof(float);
+  acc = (acc + 255) & ~(size_t)255;
+  return acc + slots * 2 * sizeof(int);
+}
+
+static int validate(const fwd_eb_params* p) {
+  if (!p) return fail(FWD_EB_EINVAL, "params is null");
+  if (p->dim <= 0) return fail(FWD_EB_EINVAL, "dim must be positive (got %d)", p->dim);
+  if (p->num_rows < 0 || p->num_indices < 0 || p->num_bags < 0)
+    return fail(FWD_EB_EINVAL, "negative size");
+  if (p->num_rows > INT_MAX)
+    return fail(FWD_EB_ETOOBIG, "num_rows per device is limited to 2^31-1 (got %lld)",
+                (long long)p->num_rows);
+  if (p->table_dtype != FWD_EB_F32 && p->table_dtype != FWD_EB_F16)
+    return fail(FWD_EB_EINVAL, "unknown table_dtype %d", p->table_dtype);
+  if (p->out_dtype != FWD_EB_F32 && p->out_dtype != FWD_EB_F16)
+    return fail(FWD_EB_EINVAL, "unknown out_dtype %d", p->out_dtype);
+  if (p->index_dtype != FWD_EB_I32 && p->index_dtype != FWD_EB_I64)
+    return fail(FWD_EB_EINVAL, "unknown index_dtype %d", p->index_dtype);
+  switch (p->mode) {
+    case FWD_EB_MODE_SUM:
+    case FWD_EB_MODE_MEAN:
+    case FWD_EB_MODE_MAX:
+    case FWD_EB_MODE_SQUARE_SUM:
+    case FWD_EB_MODE_GATHER:
+      break;
+    default:
+      return fail(FWD_EB_EINVAL, "unknown mode %d", p->mode);
+  }
+  if (p->num_rows > 0 && !p->table) return fail(FWD_EB_EINVAL, "table is null");
+  if (p->num_indices > 0 && !p->indices) return fail(FWD_EB_EINVAL, "indices is null");
+  if (p->table_stride != 0 && p->table_stride < p->dim)
+    return fail(FWD_EB_EINVAL, "table_stride smaller than dim");
+  if (p->out_stride != 0 && p->out_stride < p->dim)
+    return fail(FWD_EB_EINVAL, "out_stride smaller than dim");
+  if (p->fixed_len < 0) return fail(FWD_EB_EINVAL, "fixed_len is negative");
+  if (p->mode == FWD_EB_MODE_GATHER) {
+    if (p->num_indices > 0 && !p->out) return fail(FWD_EB_EINVAL, "out is null");
+    if (p->per_sample_weights)
+      return fail(FWD_EB_EINVAL, "per_sample_weights are not defined for GATHER");
+    return 0;
+  }
+  if (p->num_bags > 0 && !p->out) return fail(FWD_EB_EINVAL, "out is null");
+  if (p->fixed_len > 0) {
+    if (p->num_indices != p->num_bags * (int64_t)p->fixed_len)
+      return fail(FWD_EB_EINVAL, "num_indices (%lld) != num_bags (%lld) * fixed_len (%d)",
+                  (long long)p->num_indices, (long long)p->num_bags, p->fixed_len);
+  } else if (p->num_bags > 0 && !p->offsets) {
+    return fail(FWD_EB_EINVAL, "offsets is null and fixed_len is 0");
+  }
+  if (p->per_sample_weights && p->mode != FWD_EB_MODE_SUM)
+    return fail(FWD_EB_EINVAL, "per_sample_weights need mode SUM (torch rule)");
+  if (p->strategy < FWD_EB_STRATEGY_AUTO || p->strategy > FWD_EB_STRATEGY_SPLIT)
+    return fail(FWD_EB_EINVAL, "unknown strategy %d", p->strategy);
+  return 0;
+}
+
+static int pick_strategy(const fwd_eb_params* p) {
+  if (p->strategy != FWD_EB_STRATEGY_AUTO) return p->strategy;
+  if (p->num_bags <= 0) return FWD_EB_STRATEGY_GROUP;
+  const long long avg = p->fixed_len > 0 ? p->fixed_len : p->num_indices / p->num_bags;
+  // Many bags, or bags too short to share: a lane group each keeps enough rows in flight.
+  if (avg < 64 || p->num_bags >= 8192) return FWD_EB_STRATEGY_GROUP;
+  // Few long bags: split them when scratch is on offer and a CTA per bag would leave SMs idle.
+  if (p->num_bags < 2 * kSmCount && avg >= 1024) {
+    int splits = choose_splits(p);
+    if (splits > 1 && p->workspace && p->workspace_bytes >= split_workspace_bytes(p, splits))
+      return FWD_EB_STRATEGY_SPLIT;
+  }
+  return FWD_EB_STRATEGY_CTA;
+}
+
+static int make_plan(const fwd_eb_params* p, Plan* pl) {
+  int rc = validate(p);
+  if (rc) return rc;
+  memset(pl, 0, sizeof(*pl));
+  PoolArgs& a = pl->a;
+  const int tsize = p->table_dtype == FWD_EB_F16 ? 2 : 4;
+  const int osize = p->out_dtype == FWD_EB_F16 ? 2 : 4;
+  const long long tstride = p->table_stride ? p->table_stride : p->dim;
+  const long long ostride = p->out_stride ? p->out_stride : p->dim;
+  pl->table_f16 = p->table_dtype == FWD_EB_F16;
+
+  const long long row_bytes = (long long)p->dim * tsize;
+  pl->vec = (row_bytes % 16 == 0) && ((tstride * tsize) % 16 == 0) && aligned16(p->table);
+  pl->ve = pl->vec ? 16 / tsize : 1;
+  a.nchunks = pl->vec ? (int)(row_bytes / 16) : p->dim;
+  a.lanes_log2 = ceil_log2(a.nchunks < 32 ? a.nchunks : 32);
+  const int lanes = 1 << a.lanes_log2;
+  const int per_lane = (a.nchunks + lanes - 1) / lanes;
+  if (pl->vec) {
+    pl->cpl = per_lane <= 1 ? 1 : (per_lane <= 2 ? 2 : 4);
+  } else {
+    pl->cpl = 4;
+  }
+  const int tile_chunks = pl->cpl * lanes;
+  pl->tiles = (a.nchunks + tile_chunks - 1) / tile_chunks;
+
+  a.table = static_cast<const char*>(p->table);
+  a.row_bytes_stride = tstride * tsize;
+  a.num_rows = p->num_rows;
+  a.row_lo = p->row_lo;
+  a.indices = p->indices;
+  a.offsets = p->offsets;
+  a.num_indices = p->num_indices;
+  a.num_bags = p->num_bags;
+  a.psw = p->per_sample_weights;
+  a.padding_idx = p->padding_idx;
+  a.out = static_cast<char*>(p->out);
+  a.out_stride = ostride;
+  a.dim = p->dim;
+  a.fixed_len = p->fixed_len;
+  a.idx64 = p->index_dtype == FWD_EB_I64;
+  a.include_last = p->include_last_offset != 0;
+  a.out_f16 = p->out_dtype == FWD_EB_F16;
+  a.out_vec = pl->vec && aligned16(p->out) && ((ostride * osize) % 16 == 0);
+  a.mean = p->mode == FWD_EB_MODE_MEAN;
+  a.mean_raw_len = (p->flags & FWD_EB_FLAG_MEAN_RAW_LENGTH) != 0;
+  a.mean_double_round = (p->flags & FWD_EB_FLAG_MEAN_SINGLE_ROUNDING) == 0;
+  a.splits = 1;
+
+  switch (p->mode) {
+    case FWD_EB_MODE_MAX:
+      pl->op = kOpMax;
+      break;
+    case FWD_EB_MODE_SQUARE_SUM:
+      pl->op = kOpSquareSum;
+      break;
+    default:
+      pl->op = p->per_sample_weights ? kOpWeighted : kOpSum;
+  }
+
+  if (p->mode == FWD_EB_MODE_GATHER) {
+    pl->strategy = FWD_EB_STRATEGY_GROUP;
+    return 0;
+  }
+  pl->strategy = pick_strategy(p);
+  if (pl->strategy == FWD_EB_STRATEGY_SPLIT) {
+    int splits = choose_splits(p);
+    if (splits <= 1) {
+      pl->strategy = FWD_EB_STRATEGY_CTA;
+    } else {
+      size_t need = split_workspace_bytes(p, splits);
+      if (!p->workspace || p->workspace_bytes < need)
+        return fail(FWD_EB_EWORKSPACE, "split strategy needs %zu bytes of workspace, got %zu", need,
+                    p->workspace ? p->workspace_bytes : (size_t)0);
+      if (reinterpret_cast<uintptr_t>(p->workspace) & 255u)
+        return fail(FWD_EB_EALIGN, "workspace must be 256-byte aligned");
+      a.splits = splits;
+      size_t acc = (size_t)p->num_bags * splits * p->dim * sizeof(float);
+      acc = (acc + 255) & ~(size_t)255;
+      a.ws_acc = static_cast<float*>(p->workspace);
+      a.ws_meta = reinterpret_cast<int*>(static_cast<char*>(p->workspace) + acc);
+    }
+  }
+  return 0;
+}
+
+// ---- kernel dispatch ---------------------------------------------------------
+
+template <typename TW, int VE, int CPL, int OP, int U>
+static cudaError_t launch_pool(const Plan& pl, cudaStream_t st) {
+  const PoolArgs& a = pl.a;
+  if (pl.strategy == FWD_EB_STRATEGY_GROUP) {
+    const long long threads = a.num_bags << a.lanes_log2;
+    const long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+    if (blocks == 0) return cudaSuccess;
+    if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+    dim3 grid((unsigned)blocks, (unsigned)pl.tiles);
+    eb_pool_group_kernel<TW, VE, CPL, OP, U><<<grid, kCtaThreads, 0, st>>>(a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaGetLastError();
+  }
+  const long long blocks = a.num_bags * a.splits;
+  if (blocks == 0) return cudaSuccess;
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  const int groups = kCtaThreads >> a.lanes_log2;
+  const size_t smem = (size_t)kCtaThreads * CPL * VE * sizeof(float) + (size_t)groups * 2 * sizeof(int);
+  dim3 grid((unsigned)blocks, (unsigned)pl.tiles);
+  eb_pool_cta_kernel<TW, VE, CPL, OP, U><<<grid, kCtaThreads, smem, st>>>(a);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess || a.splits <= 1) return e;
+  const long long total = a.num_bags * a.dim;
+  const long long fblocks = (total + kCtaThreads - 1) / kCtaThreads;
+  if (fblocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  eb_split_finish_kernel<OP><<<(unsigned)fblocks, kCtaThreads, 0, st>>>(a, pl.table_f16 ? 1 : 0);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+template <typename TW, int VE, int CPL, int U>
+static cudaError_t launch_op(const Plan& pl, cudaStream_t st) {
+  switch (pl.op) {
+    case kOpSum:
+      return launch_pool<TW, VE, CPL, kOpSum, U>(pl, st);
+    case kOpWeighted:
+      return launch_pool<TW, VE, CPL, kOpWeighted, U>(pl, st);
+    case kOpMax:
+      return launch_pool<TW, VE, CPL, kOpMax, U>(pl, st);
+    default:
+      return launch_pool<TW, VE, CPL, kOpSquareSum, U>(pl, st);
+  }
+}
+
+// Row loads kept in flight per lane group: 8 x 16 B for one chunk per lane,
+// fewer when a lane owns several chunks so the register count stays put.
+template <typename TW>
+static cudaError_t launch_shape(const Plan& pl, cudaStream_t st) {
+  constexpr int VE = 16 / (int)sizeof(TW);
+  if (!pl.vec) return launch_op<TW, 1, 4, 4>(pl, st);
+  switch (pl.cpl) {
+    case 1:
+      return launch_op<TW, VE, 1, 8>(pl, st);
+    case 2:
+      return launch_op<TW, VE, 2, 4>(pl, st);
+    default:
+      return launch_op<TW, VE, 4, 2>(pl, st);
+  }
+}
+
+template <typename TW>
+static cudaError_t launch_gather(const Plan& pl, bool keep, cudaStream_t st) {
+  const PoolArgs& a = pl.a;
+  const long long threads = a.num_indices << a.lanes_log2;
+  const long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+  if (blocks == 0) return cudaSuccess;
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  if (pl.vec) {
+    eb_gather_kernel<TW, 16 / (int)sizeof(TW)><<<(unsigned)blocks, kCtaThreads, 0, st>>>(a, keep);
+  } else {
+    eb_gather_kernel<TW, 1><<<(unsigned)blocks, kCtaThreads, 0, st>>>(a, keep);
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+}  // namespace fwd_eb
+
+using namespace fwd_eb;
+
+extern "C" {
+
+int fwd_eb_version(void) { return FWD_EB_ABI_VERSION; }
+
+size_t fwd_eb_params_size(void) { return sizeof(fwd_eb_params); }
+
+const char* fwd_eb_last_error_string(void) { return g_err; }
+
+uint64_t fwd_eb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int fwd_eb_pick_strategy(const fwd_eb_params* p) {
+  Plan pl;
+  fwd_eb_params q;
+  if (!p) return fail(FWD_EB_EINVAL, "params is null");
+  q = *p;
+  if (q.strategy == FWD_EB_STRATEGY_SPLIT) q.strategy = FWD_EB_STRATEGY_AUTO;
+  int rc = validate(&q);
+  if (rc) return rc;
+  (void)pl;
+  if (q.mode == FWD_EB_MODE_GATHER) return FWD_EB_STRATEGY_GROUP;
+  return pick_strategy(&q);
+}
+
+size_t fwd_eb_workspace_size(const fwd_eb_params* p) {
+  if (!p || validate(p) != 0 || p->mode == FWD_EB_MODE_GATHER) return 0;
+  if (p->strategy == FWD_EB_STRATEGY_GROUP || p->strategy == FWD_EB_STRATEGY_CTA) return 0;
+  // AUTO: what SPLIT would need if AUTO could choose it for this shape.
+  if (p->strategy == FWD_EB_STRATEGY_AUTO) {
+    if (p->num_bags <= 0) return 0;
+    const long long avg = p->fixed_len > 0 ? p->fixed_len : p->num_indices / p->num_bags;
+    if (avg < 64 || p->num_bags >= 8192) return 0;
+    if (!(p->num_bags < 2 * kSmCount && avg >= 1024)) return 0;
+  }
+  return split_workspace_bytes(p, choose_splits(p));
+}
+
+int fwd_eb_forward(const fwd_eb_params* p, void* stream) {
+  Plan pl;
+  int rc = make_plan(p, &pl);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (p->mode == FWD_EB_MODE_GATHER) {
+    const bool keep = (p->flags & FWD_EB_FLAG_GATHER_KEEP_SKIPPED) != 0;
+    e = pl.table_f16 ? launch_gather<__half>(pl, keep, st) : launch_gather<float>(pl, keep, st);
+  } else {
+    e = pl.table_f16 ? launch_shape<__half>(pl, st) : launch_shape<float>(pl, st);
+  }
+  if (e != cudaSuccess) return cuda_fail(e, "kernel launch");
+  g_err[0] = '\0';
+  return 0;
+}
+
+// ---- the reference's three launchers, same argument order --------------------
+
+static void legacy_params(fwd_eb_params* p, const int* d_input, float* d_output,
+                          const float* d_data, int count, int dim, int data_offset, int op_type) {
+  memset(p, 0, sizeof(*p));
+  p->table = d_data;
+  p->table_dtype = FWD_EB_F32;
+  p->dim = dim;
+  p->num_rows = count;
+  p->row_lo = data_offset;
+  p->indices = d_input;
+  p->index_dtype = FWD_EB_I32;
+  p->mode = op_type;
+  p->padding_idx = -1;
+  p->out = d_output;
+  p->out_dtype = FWD_EB_F32;
+}
+
+int fwd_eb_gather_f32(const int* d_input, float* d_output, int batch_size, int offset,
+                      const float* d_data, int count, int dim, int data_offset, void* stream) {
+  if (batch_size < 0 || offset < 0) return fail(FWD_EB_EINVAL, "negative size");
+  fwd_eb_params p;
+  legacy_params(&p, d_input, d_output, d_data, count, dim, data_offset, FWD_EB_MODE_GATHER);
+  p.num_indices = (int64_t)batch_size * offset;
+  return fwd_eb_forward(&p, stream);
+}
+
+int fwd_eb_bag_fixed_f32(const int* d_input, float* d_output, int batch_size, int offset,
+                         const float* d_data, int count, int dim, int data_offset, int op_type,
+                         void* stream) {
+  if (batch_size < 0 || offset <= 0) return fail(FWD_EB_EINVAL, "bad batch_size / offset");
+  fwd_eb_params p;
+  legacy_params(&p, d_input, d_output, d_data, count, dim, data_offset, op_type);
+  p.fixed_len = offset;
+  p.num_bags = batch_size;
+  p.num_indices = (int64_t)batch_size * offset;
+  return fwd_eb_forward(&p, stream);
+}
+
+int fwd_eb_bag_f32(const int* d_input, const int* d_offsets, float* d_output, int input_size,
+                   int block_size, const float* d_data, int count, int dim, int data_offset,
+                   int op_type, void* stream) {
+  if (input_size < 0 || block_size < 0) return fail(FWD_EB_EINVAL, "negative size");
+  fwd_eb_params p;
+  legacy_params(&p, d_input, d_output, d_data, count, dim, data_offset, op_type);
+  p.offsets = d_offsets;
+  p.num_bags = block_size;
+  p.num_indices = input_size;
+  return fwd_eb_forward(&p, stream);
+}
+
+// ---- helpers -----------------------------------------------------------------
+
+int fwd_eb_fill_table(void* d_table, int32_t table_dtype, int64_t num_rows, int32_t dim,
+                      int64_t row_lo, uint64_t seed, float scale, void* stream) {
+  if (!d_table || num_rows < 0 || dim <= 0) return fail(FWD_EB_EINVAL, "bad table arguments");
+  if (table_dtype != FWD_EB_F32 && table_dtype != FWD_EB_F16)
+    return fail(FWD_EB_EINVAL, "unknown table_dtype %d", table_dtype);
+  if (num_rows == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const long long total = (long long)num_rows * dim;
+  long long blocks = (total + kCtaThreads - 1) / kCtaThreads;
+  const long long cap = (long long)kSmCount * 32;
+  if (blocks > cap) blocks = cap;
+  if (table_dtype == FWD_EB_F16) {
+    eb_fill_table_kernel<__half><<<(unsigned)blocks, kCtaThreads, 0, st>>>(
+        static_cast<__half*>(d_table), num_rows, dim, row_lo, seed, scale);
+  } else {
+    eb_fill_table_kernel<float><<<(unsigned)blocks, kCtaThreads, 0, st>>>(
+        static_cast<float*>(d_table), num_rows, dim, row_lo, seed, scale);
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "fill_table launch");
+  return 0;
+}
+
+int fwd_eb_combine_partials(const void* d_parts, int32_t part_dtype, int32_t num_parts,
+                            int64_t part_stride_elems, int64_t count, void* d_out,
+                            int32_t out_dtype, void* stream) {
+  if (!d_parts || !d_out || num_parts <= 0 || count < 0 || part_stride_elems < count)
+    return fail(FWD_EB_EINVAL, "bad combine arguments");
+  if (count == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
+  const long long cap = (long long)kSmCount * 16;
+  if (blocks > cap) blocks = cap;
+  const unsigned g = (unsigned)blocks;
+  if (part_dtype == FWD_EB_F32 && out_dtype == FWD_EB_F32) {
+    eb_combine_partials_kernel<float, float><<<g, kCtaThreads, 0, st>>>(
+        static_cast<const float*>(d_parts), num_parts, part_stride_elems, count,
+        static_cast<float*>(d_out));
+  } else if (part_dtype == FWD_EB_F32 && out_dtype == FWD_EB_F16) {
+    eb_combine_partials_kernel<float, __half><<<g, kCtaThreads, 0, st>>>(
+        static_cast<const float*>(d_parts), num_parts, part_stride_elems, count,
+        static_cast<__half*>(d_out));
+  } else if (part_dtype == FWD_EB_F16 && out_dtype == FWD_EB_F32) {
+    eb_combine_partials_kernel<__half, float><<<g, kCtaThreads, 0, st>>>(
+        static_cast<const __half*>(d_parts), num_parts, part_stride_elems, count,
+        static_cast<float*>(d_out));
+  } else if (part_dtype == FWD_EB_F16 && out_dtype == FWD_EB_F16) {
+    eb_combine_partials_kernel<__half, __half><<<g, kCtaThreads, 0, st>>>(
+        static_cast<const __half*>(d_parts), num_parts, part_stride_elems, count,
+        static_cast<__half*>(d_out));
+  } else {
+    return fail(FWD_EB_EINVAL, "unknown dtype in combine");
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "combine launch");
+  return 0;
+}
+
+}  // extern "C"

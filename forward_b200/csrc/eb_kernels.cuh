@@ -1,0 +1,567 @@
+// Device code of the EmbeddingBag gather-and-pool path for sm_100a.
+//
+// Replaces the three kernels of Forward's EmbeddingBag plugin
+// (source/trt_engine/trt_network_crt/plugins/embedding_bag_plugin/
+// embedding_bag_plugin.cu:66-181).  The reference pools through shared-memory
+// atomics with one column per thread; here a *lane group* owns a bag:
+//
+//   * a table row is cut into 16-byte chunks and lane l of the group loads
+//     chunk l (and l + lanes, ... when the row is wider than the group), so one
+//     warp-wide load instruction fetches 32/lanes whole rows with every sector
+//     fully used;
+//   * the group reads `lanes` indices with one coalesced load, the warp votes
+//     (ballot) on which of them survive the padding / table-window filter, and
+//     the survivors are walked in bag order by shuffling the row number from
+//     the lane that loaded it; U row loads are issued before the first add so
+//     U * row_bytes per group are in flight;
+//   * every column is accumulated in fp32 registers in bag order, which is the
+//     order torch CPU uses, so sum / mean / weighted sum / max reproduce it
+//     exactly; max keeps the first of equal values because the comparison is
+//     strict and rows arrive in order.
+//
+// Three strategies share that inner loop: a group per bag (many bags), a CTA
+// per bag (long bags; groups take consecutive slices and are folded in slice
+// order through shared memory) and split bags (several CTAs per bag, partial
+// results in caller-provided scratch, folded in order by a second kernel).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fwd_eb {
+
+constexpr unsigned kFull = 0xffffffffu;
+constexpr int kCtaThreads = 256;
+
+enum Op { kOpSum = 0, kOpWeighted = 1, kOpMax = 2, kOpSquareSum = 3 };
+
+struct PoolArgs {
+  const char* table;        // device bytes
+  long long row_bytes_stride;  // bytes between rows
+  long long num_rows;
+  long long row_lo;
+  const void* indices;
+  const void* offsets;
+  long long num_indices;
+  long long num_bags;
+  const float* psw;
+  long long padding_idx;
+  char* out;
+  long long out_stride;     // elements between output rows
+  float* ws_acc;            // split strategy: [num_bags, splits, dim] fp32
+  int* ws_meta;             // split strategy: [num_bags, splits, 2] {counted, have}
+  int dim;
+  int nchunks;              // chunks per row (16 B vectors, or elements in scalar mode)
+  int lanes_log2;           // lanes per group
+  int fixed_len;
+  int idx64;
+  int include_last;
+  int out_f16;
+  int out_vec;              // output rows are 16 B aligned: vector stores allowed
+  int mean;                 // divide by the bag's count at the end
+  int mean_raw_len;         // ... by the raw bag length instead of the non-padding count
+  int mean_double_round;    // fp16 mean the way torch CPU rounds it
+  int splits;               // split strategy: CTAs per bag
+};
+
+template <typename TW, int VE>
+struct Chunk;
+template <>
+struct Chunk<float, 4> { using type = float4; };
+template <>
+struct Chunk<__half, 8> { using type = uint4; };
+template <>
+struct Chunk<float, 1> { using type = float; };
+template <>
+struct Chunk<__half, 1> { using type = __half; };
+
+__device__ __forceinline__ void unpack(const float4& v, float (&f)[4]) {
+  f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+__device__ __forceinline__ void unpack(const uint4& v, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void unpack(const float& v, float (&f)[1]) { f[0] = v; }
+__device__ __forceinline__ void unpack(const __half& v, float (&f)[1]) { f[0] = __half2float(v); }
+
+template <typename V>
+__device__ __forceinline__ V load_chunk(const char* p) {
+  return __ldg(reinterpret_cast<const V*>(p));
+}
+
+template <int OP>
+__device__ __forceinline__ void fold(float& acc, float x, float w, bool first) {
+  if (OP == kOpSum) {
+    acc = __fadd_rn(acc, x);
+  } else if (OP == kOpWeighted) {
+    acc = __fmaf_rn(w, x, acc);
+  } else if (OP == kOpSquareSum) {
+    acc = __fadd_rn(acc, __fmul_rn(x, x));
+  } else {  // max: the first row is taken as is, later rows only when strictly greater
+    acc = (first || x > acc) ? x : acc;
+  }
+}
+
+__device__ __forceinline__ long long load_index(const void* p, int idx64, long long i) {
+  return idx64 ? __ldg(reinterpret_cast<const long long*>(p) + i)
+               : static_cast<long long>(__ldg(reinterpret_cast<const int*>(p) + i));
+}
+
+__device__ __forceinline__ void bag_bounds(const PoolArgs& a, long long bag, long long& start,
+                                           long long& end) {
+  if (a.fixed_len > 0) {
+    start = bag * a.fixed_len;
+    end = start + a.fixed_len;
+  } else {
+    start = load_index(a.offsets, a.idx64, bag);
+    end = (a.include_last || bag + 1 < a.num_bags) ? load_index(a.offsets, a.idx64, bag + 1)
+                                                    : a.num_indices;
+  }
+  // a malformed offsets array must not turn into a wild read
+  if (start < 0) start = 0;
+  if (end > a.num_indices) end = a.num_indices;
+  if (end < start) end = start;
+}
+
+// State one lane group carries while it walks a range of a bag.
+template <int CPL, int VE>
+struct Accum {
+  float v[CPL][VE];
+  int counted;  // non-padding indices seen (inside or outside the table window)
+  bool have;    // at least one row was folded in
+};
+
+// One lane's share of walking indices [start, end) of a bag.  All 32 lanes of
+// the warp must call this together (the loops are warp-uniform; a group with
+// nothing left simply has its predicates off).
+template <typename TW, int VE, int CPL, int OP, int U>
+__device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, long long end,
+                                           int chunk0, Accum<CPL, VE>& s) {
+  using V = typename Chunk<TW, VE>::type;
+  const int lanes = 1 << a.lanes_log2;
+  const unsigned lane = threadIdx.x & 31u;
+  const int lig = lane & (lanes - 1);
+  const int gbase = lane & ~(lanes - 1);
+  const unsigned gmask = lanes == 32 ? kFull : ((1u << lanes) - 1u);
+  const int vbytes = VE * (int)sizeof(TW);
+
+  bool chunk_ok[CPL];
+  int chunk_off[CPL];
+#pragma unroll
+  for (int c = 0; c < CPL; ++c) {
+    int chunk = chunk0 + c * lanes + lig;
+    chunk_ok[c] = chunk < a.nchunks;
+    chunk_off[c] = chunk * vbytes;
+  }
+
+  // fetch one index per lane: local row (>= 0) or -1 for "skip"
+  auto fetch = [&](long long pos, int& row, float& w, bool& counted) {
+    row = -1;
+    w = 1.0f;
+    counted = false;
+    if (pos < end) {
+      long long idx = load_index(a.indices, a.idx64, pos);
+      if (a.padding_idx < 0 || idx != a.padding_idx) {
+        counted = true;
+        long long r = idx - a.row_lo;
+        if (r >= 0 && r < a.num_rows) {
+          row = (int)r;
+          if (OP == kOpWeighted) w = __ldg(a.psw + pos);
+        }
+      }
+    }
+  };
+
+  long long base = start;
+  int cur_row, nxt_row;
+  float cur_w, nxt_w;
+  bool cur_counted, nxt_counted;
+  fetch(base + lig, cur_row, cur_w, cur_counted);
+
+  while (__any_sync(kFull, base < end)) {
+    fetch(base + lanes + lig, nxt_row, nxt_w, nxt_counted);  // next block of indices, early
+    unsigned m = (__ballot_sync(kFull, cur_row >= 0) >> gbase) & gmask;
+    s.counted += __popc((__ballot_sync(kFull, cur_counted) >> gbase) & gmask);
+
+    while (__any_sync(kFull, m != 0u)) {
+      int src[U];
+      int row[U];
+      float w[U];
+      V val[U][CPL];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        src[u] = m ? (__ffs(m) - 1) : -1;
+        m &= (m - 1u);  // clears the lowest set bit; 0 stays 0
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        int from = gbase + (src[u] < 0 ? 0 : src[u]);
+        row[u] = __shfl_sync(kFull, cur_row, from);
+        if (OP == kOpWeighted) w[u] = __shfl_sync(kFull, cur_w, from);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (src[u] >= 0) {
+          const char* rp = a.table + (long long)row[u] * a.row_bytes_stride;
+#pragma unroll
+          for (int c = 0; c < CPL; ++c) {
+            if (chunk_ok[c]) val[u][c] = load_chunk<V>(rp + chunk_off[c]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (src[u] >= 0) {
+#pragma unroll
+          for (int c = 0; c < CPL; ++c) {
+            if (chunk_ok[c]) {
+              float f[VE];
+              unpack(val[u][c], f);
+#pragma unroll
+              for (int e = 0; e < VE; ++e) {
+                fold<OP>(s.v[c][e], f[e], OP == kOpWeighted ? w[u] : 1.0f, !s.have);
+              }
+            }
+          }
+          s.have = true;
+        }
+      }
+    }
+    cur_row = nxt_row;
+    cur_w = nxt_w;
+    cur_counted = nxt_counted;
+    base += lanes;
+  }
+}
+
+// Final value of one column: mean division and rounding rules.
+__device__ __forceinline__ float finish(const PoolArgs& a, float acc, int counted,
+                                        long long raw_len, bool table_f16) {
+  if (!a.mean) return acc;
+  long long d = a.mean_raw_len ? raw_len : (long long)counted;
+  if (d < 1) d = 1;
+  float denom = (float)d;
+  if (a.out_f16 && table_f16 && a.mean_double_round) {
+    acc = __half2float(__float2half_rn(acc));
+  }
+  return __fdiv_rn(acc, denom);
+}
+
+// Write this lane's chunks of one output row.
+template <int VE, int CPL>
+__device__ __forceinline__ void store_row(const PoolArgs& a, long long out_row, int chunk0,
+                                          const float (&v)[CPL][VE]) {
+  const int lanes = 1 << a.lanes_log2;
+  const int lig = (threadIdx.x & 31u) & (lanes - 1);
+#pragma unroll
+  for (int c = 0; c < CPL; ++c) {
+    int chunk = chunk0 + c * lanes + lig;
+    if (chunk >= a.nchunks) continue;
+    long long col = (long long)chunk * VE;
+    if (a.out_f16) {
+      __half* o = reinterpret_cast<__half*>(a.out) + out_row * a.out_stride + col;
+      if (VE == 8 && a.out_vec) {
+        uint4 pk;
+        __half2* h = reinterpret_cast<__half2*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[c][2 * e], v[c][2 * e + 1]);
+        *reinterpret_cast<uint4*>(o) = pk;
+      } else if (VE == 4 && a.out_vec) {
+        uint2 pk;
+        __half2* h = reinterpret_cast<__half2*>(&pk);
+        h[0] = __floats2half2_rn(v[c][0], v[c][1]);
+        h[1] = __floats2half2_rn(v[c][2], v[c][3]);
+        *reinterpret_cast<uint2*>(o) = pk;
+      } else {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) o[e] = __float2half_rn(v[c][e]);
+      }
+    } else {
+      float* o = reinterpret_cast<float*>(a.out) + out_row * a.out_stride + col;
+      if (VE >= 4 && a.out_vec) {
+#pragma unroll
+        for (int e = 0; e < VE; e += 4) {
+          *reinterpret_cast<float4*>(o + e) =
+              make_float4(v[c][e], v[c][e + 1], v[c][e + 2], v[c][e + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < VE; ++e) o[e] = v[c][e];
+      }
+    }
+  }
+}
+
+template <int CPL, int VE>
+__device__ __forceinline__ void clear(Accum<CPL, VE>& s) {
+#pragma unroll
+  for (int c = 0; c < CPL; ++c)
+#pragma unroll
+    for (int e = 0; e < VE; ++e) s.v[c][e] = 0.0f;
+  s.counted = 0;
+  s.have = false;
+}
+
+// ---- strategy 1: one lane group per bag -------------------------------------
+// grid.x covers bags (kCtaThreads / lanes bags per CTA), grid.y covers column
+// tiles of 32 * CPL chunks for rows wider than one tile.
+template <typename TW, int VE, int CPL, int OP, int U>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_pool_group_kernel(const PoolArgs a) {
+  const int lanes_log2 = a.lanes_log2;
+  const long long bag =
+      ((long long)blockIdx.x * kCtaThreads + threadIdx.x) >> lanes_log2;
+  const int chunk0 = blockIdx.y * (CPL << lanes_log2);
+  const bool live = bag < a.num_bags;
+  long long start = 0, end = 0;
+  if (live) bag_bounds(a, bag, start, end);
+
+  Accum<CPL, VE> s;
+  clear(s);
+  pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
+
+  if (live) {
+    const bool tf16 = sizeof(TW) == 2;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c)
+#pragma unroll
+      for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
+    store_row<VE, CPL>(a, bag, chunk0, s.v);
+  }
+}
+
+// ---- strategies 2 and 3: a CTA (or `splits` CTAs) per bag --------------------
+// Lane groups take consecutive slices of the bag (of the split's part of it),
+// stage their fp32 partials in shared memory and thread t folds column t over
+// the groups in slice order, which keeps both the summation order fixed and the
+// first-of-equals rule for max.  With splits > 1 the folded partial goes to the
+// scratch arrays instead of the output and eb_split_finish_kernel completes it.
+template <typename TW, int VE, int CPL, int OP, int U>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_pool_cta_kernel(const PoolArgs a) {
+  extern __shared__ float smem[];  // [groups][tile_cols] then int[groups][2]
+  const int lanes_log2 = a.lanes_log2;
+  const int lanes = 1 << lanes_log2;
+  const int groups = kCtaThreads >> lanes_log2;
+  const int tile_chunks = CPL << lanes_log2;
+  const int tile_cols = tile_chunks * VE;
+  const int chunk0 = blockIdx.y * tile_chunks;
+  const long long bag = blockIdx.x / a.splits;
+  const int split = blockIdx.x % a.splits;
+  const int g = threadIdx.x >> lanes_log2;
+  const int lig = (threadIdx.x & 31u) & (lanes - 1);
+
+  long long bstart, bend;
+  bag_bounds(a, bag, bstart, bend);
+  const long long blen = bend - bstart;
+  // slice of this split, then of this group, both in whole index blocks
+  const long long total_slices = (long long)a.splits * groups;
+  long long per = (blen + total_slices - 1) / total_slices;
+  per = ((per + lanes - 1) >> lanes_log2) << lanes_log2;
+  const long long slot = (long long)split * groups + g;
+  long long start = bstart + slot * per;
+  long long end = start + per;
+  if (start > bend) start = bend;
+  if (end > bend) end = bend;
+
+  Accum<CPL, VE> s;
+  clear(s);
+  pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
+
+  float* part = smem;
+  int* meta = reinterpret_cast<int*>(smem + (size_t)groups * tile_cols);
+#pragma unroll
+  for (int c = 0; c < CPL; ++c) {
+    int chunk_in_tile = c * lanes + lig;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) part[(size_t)g * tile_cols + chunk_in_tile * VE + e] = s.v[c][e];
+  }
+  if (lig == 0) {
+    meta[2 * g] = s.counted;
+    meta[2 * g + 1] = s.have ? 1 : 0;
+  }
+  __syncthreads();
+
+  int counted = 0;
+  for (int k = 0; k < groups; ++k) counted += meta[2 * k];
+  const bool tf16 = sizeof(TW) == 2;
+  for (int col = threadIdx.x; col < tile_cols; col += kCtaThreads) {
+    const long long gcol = (long long)chunk0 * VE + col;
+    if (gcol >= a.dim) continue;
+    float acc = 0.0f;
+    bool have = false;
+    for (int k = 0; k < groups; ++k) {
+      if (!meta[2 * k + 1]) continue;
+      float x = part[(size_t)k * tile_cols + col];
+      if (OP == kOpMax) {
+        acc = (!have || x > acc) ? x : acc;
+      } else {
+        acc = have ? __fadd_rn(acc, x) : x;
+      }
+      have = true;
+    }
+    if (a.splits > 1) {
+      a.ws_acc[(bag * a.splits + split) * a.dim + gcol] = acc;
+    } else {
+      acc = finish(a, acc, counted, blen, tf16);
+      if (a.out_f16) {
+        reinterpret_cast<__half*>(a.out)[bag * a.out_stride + gcol] = __float2half_rn(acc);
+      } else {
+        reinterpret_cast<float*>(a.out)[bag * a.out_stride + gcol] = acc;
+      }
+    }
+  }
+  if (a.splits > 1 && threadIdx.x == 0 && blockIdx.y == 0) {
+    int have_any = 0;
+    for (int k = 0; k < groups; ++k) have_any |= meta[2 * k + 1];
+    a.ws_meta[(bag * a.splits + split) * 2] = counted;
+    a.ws_meta[(bag * a.splits + split) * 2 + 1] = have_any;
+  }
+}
+
+// Folds the `splits` partials of every bag in split order; one thread per
+// output element.
+template <int OP>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_split_finish_kernel(const PoolArgs a, int table_f16) {
+  const long long t = (long long)blockIdx.x * kCtaThreads + threadIdx.x;
+  if (t >= a.num_bags * a.dim) return;
+  const long long bag = t / a.dim;
+  const int col = (int)(t - bag * a.dim);
+  float acc = 0.0f;
+  bool have = false;
+  int counted = 0;
+  for (int sidx = 0; sidx < a.splits; ++sidx) {
+    const long long slot = bag * a.splits + sidx;
+    counted += a.ws_meta[2 * slot];
+    if (!a.ws_meta[2 * slot + 1]) continue;
+    float x = a.ws_acc[slot * a.dim + col];
+    if (OP == kOpMax) {
+      acc = (!have || x > acc) ? x : acc;
+    } else {
+      acc = have ? __fadd_rn(acc, x) : x;
+    }
+    have = true;
+  }
+  long long bstart, bend;
+  bag_bounds(a, bag, bstart, bend);
+  acc = finish(a, acc, counted, bend - bstart, table_f16 != 0);
+  if (a.out_f16) {
+    reinterpret_cast<__half*>(a.out)[bag * a.out_stride + col] = __float2half_rn(acc);
+  } else {
+    reinterpret_cast<float*>(a.out)[bag * a.out_stride + col] = acc;
+  }
+}
+
+// ---- gather: out[t, :] = table[indices[t] - row_lo, :] -----------------------
+// One lane group per index; skipped indices give a zero row (or are left alone
+// when keep_skipped is set, the reference behaviour).
+template <typename TW, int VE>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_gather_kernel(const PoolArgs a, int keep_skipped) {
+  using V = typename Chunk<TW, VE>::type;
+  const int lanes = 1 << a.lanes_log2;
+  const int lig = (threadIdx.x & 31u) & (lanes - 1);
+  const long long t = ((long long)blockIdx.x * kCtaThreads + threadIdx.x) >> a.lanes_log2;
+  if (t >= a.num_indices) return;
+  const long long idx = load_index(a.indices, a.idx64, t);
+  const long long r = idx - a.row_lo;
+  const bool ok = (a.padding_idx < 0 || idx != a.padding_idx) && r >= 0 && r < a.num_rows;
+  if (!ok && keep_skipped) return;
+  const char* rp = a.table + (ok ? r : 0) * a.row_bytes_stride;
+  for (int chunk = lig; chunk < a.nchunks; chunk += lanes) {
+    float f[1][VE];
+    if (ok) {
+      V v = load_chunk<V>(rp + (long long)chunk * VE * (int)sizeof(TW));
+      unpack(v, f[0]);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) f[0][e] = 0.0f;
+    }
+    // store_row addresses chunk0 + lig; hand it the chunk minus this lane's slot
+    store_row<VE, 1>(a, t, chunk - lig, f);
+  }
+}
+
+// ---- helpers ---------------------------------------------------------------
+
+__host__ __device__ __forceinline__ unsigned long long mix64(unsigned long long z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+// Sum of eight 16-bit uniforms, centred and scaled to unit variance: integer
+// arithmetic up to the last two multiplies, so the host twin gives the same bits.
+__host__ __device__ __forceinline__ float table_value(unsigned long long seed, long long row,
+                                                      int col, float scale) {
+  unsigned long long a =
+      mix64(seed ^ mix64((unsigned long long)row * 0xD1342543DE82EF95ull + (unsigned)col));
+  unsigned long long b = mix64(a);
+  int s = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    s += (int)((a >> (16 * i)) & 0xFFFFu);
+    s += (int)((b >> (16 * i)) & 0xFFFFu);
+  }
+  s -= 4 * 65535;
+  const float inv_sigma = 1.0f / 53509.92f;
+#ifdef __CUDA_ARCH__
+  return __fmul_rn(__fmul_rn((float)s, inv_sigma), scale);
+#else
+  float unit = (float)s * inv_sigma;
+  return unit * scale;
+#endif
+}
+
+template <typename TW>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_fill_table_kernel(TW* table, long long num_rows, int dim, long long row_lo,
+                     unsigned long long seed, float scale) {
+  const long long total = num_rows * dim;
+  for (long long t = (long long)blockIdx.x * kCtaThreads + threadIdx.x; t < total;
+       t += (long long)gridDim.x * kCtaThreads) {
+    const long long r = t / dim;
+    const int c = (int)(t - r * dim);
+    const float v = table_value(seed, row_lo + r, c, scale);
+    if (sizeof(TW) == 2) {
+      reinterpret_cast<__half*>(table)[t] = __float2half_rn(v);
+    } else {
+      reinterpret_cast<float*>(table)[t] = v;
+    }
+  }
+}
+
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_combine_partials_kernel(const TP* parts, int num_parts, long long part_stride, long long count,
+                           TO* out) {
+  for (long long i = (long long)blockIdx.x * kCtaThreads + threadIdx.x; i < count;
+       i += (long long)gridDim.x * kCtaThreads) {
+    float s = 0.0f;
+    for (int r = 0; r < num_parts; ++r) {
+      float x;
+      if (sizeof(TP) == 2) {
+        x = __half2float(reinterpret_cast<const __half*>(parts)[r * part_stride + i]);
+      } else {
+        x = reinterpret_cast<const float*>(parts)[r * part_stride + i];
+      }
+      s = __fadd_rn(s, x);
+    }
+    if (sizeof(TO) == 2) {
+      reinterpret_cast<__half*>(out)[i] = __float2half_rn(s);
+    } else {
+      reinterpret_cast<float*>(out)[i] = s;
+    }
+  }
+}
+
+}  // namespace fwd_eb

@@ -1,0 +1,200 @@
+/*
+ * fwd_eb.h — C ABI of the B200 (sm_100a) EmbeddingBag gather-and-pool kernels.
+ *
+ * This is the boundary a host binds to: plain pointers and sizes, no C++ or
+ * torch types.  The TensorRT plugin (EmbeddingBag_TRT), the host session and
+ * the Python ctypes binding all call these entry points and nothing else.
+ *
+ * Reference interfaces replaced (paths inside the Tencent/Forward tree):
+ *   source/trt_engine/trt_network_crt/plugins/embedding_bag_plugin/
+ *     embedding_bag_plugin.h:40-49   free launchers Gather /
+ *                                    EmbeddingBagWithFixedOffset / EmbeddingBag
+ *     embedding_bag_plugin.cu:66-206 the three kernels and their launch code
+ *     embedding_bag_plugin.h:39      enum ReduceOperation (mode codes below)
+ *
+ * Conventions
+ *   - every pointer named `d_*` or documented "device" is device memory of the
+ *     current CUDA device; `stream` is a cudaStream_t passed as void*;
+ *   - launchers never allocate, never synchronise and launch only on `stream`;
+ *   - return value 0 = success, negative = FWD_EB_E* (bad arguments, checked on
+ *     the host before any launch), positive = a cudaError_t from the launch;
+ *   - nothing aborts the process; fwd_eb_last_error_string() describes the
+ *     last failure of the calling thread.
+ */
+#ifndef FWD_EB_H_
+#define FWD_EB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FWD_EB_ABI_VERSION 1
+
+/* Pooling modes: the values of the reference enum ReduceOperation
+ * (embedding_bag_plugin.h:39), which are also torch's `mode` integers for
+ * sum / mean / max. */
+enum {
+  FWD_EB_MODE_SUM = 0,
+  FWD_EB_MODE_MEAN = 1,
+  FWD_EB_MODE_MAX = 2,
+  FWD_EB_MODE_SQUARE_SUM = 3,
+  FWD_EB_MODE_GATHER = 999
+};
+
+enum { FWD_EB_F32 = 0, FWD_EB_F16 = 1 };  /* table / output element type   */
+enum { FWD_EB_I32 = 0, FWD_EB_I64 = 1 };  /* indices / offsets element type */
+
+/* Pooling strategies (fwd_eb_params.strategy). AUTO picks by shape. */
+enum {
+  FWD_EB_STRATEGY_AUTO = 0,
+  FWD_EB_STRATEGY_GROUP = 1, /* a sub-warp lane group (16 B per lane) per bag    */
+  FWD_EB_STRATEGY_CTA = 2,   /* one CTA per bag, lane groups split the bag       */
+  FWD_EB_STRATEGY_SPLIT = 3  /* several CTAs per bag + partials in `workspace`   */
+};
+
+/* Flags (fwd_eb_params.flags). */
+enum {
+  /* mean divides by the raw bag length, as embedding_bag_plugin.cu:112 does;
+   * default (flag clear) divides by the number of non-padding indices, as
+   * torch does.  Identical when padding_idx < 0. */
+  FWD_EB_FLAG_MEAN_RAW_LENGTH = 1,
+  /* GATHER leaves rows whose index falls outside the table window untouched,
+   * as embedding_bag_plugin.cu:177-179 does; default writes zeros there. */
+  FWD_EB_FLAG_GATHER_KEEP_SKIPPED = 2,
+  /* fp16 mean rounds the fp32 sum once after the division; default mimics
+   * torch CPU (round the sum to fp16, divide, round again). */
+  FWD_EB_FLAG_MEAN_SINGLE_ROUNDING = 4
+};
+
+/* Error codes. */
+enum {
+  FWD_EB_OK = 0,
+  FWD_EB_EINVAL = -1,      /* null pointer / negative size / unknown enum      */
+  FWD_EB_EUNSUPPORTED = -2,/* legal but not implemented combination            */
+  FWD_EB_EALIGN = -3,      /* pointer or stride not aligned as required        */
+  FWD_EB_EWORKSPACE = -4,  /* strategy needs more workspace than was given     */
+  FWD_EB_ENOGPU = -5,      /* no usable CUDA device                            */
+  FWD_EB_ETOOBIG = -6      /* size beyond a documented fixed limit             */
+};
+
+/*
+ * One gather-and-pool call.  Zero-initialise, then fill.
+ *
+ * Bags: with `fixed_len` > 0 the indices form a [num_bags, fixed_len] matrix
+ * (reference EmbeddingBagCudaWithFixedOffset, embedding_bag_plugin.cu:120-168)
+ * and `offsets` is ignored; otherwise bag b covers
+ * indices[offsets[b] .. offsets[b+1]) and the last bag ends at `num_indices`
+ * (embedding_bag_plugin.cu:80-86) unless `include_last_offset` is set, in which
+ * case `offsets` holds num_bags+1 entries.
+ *
+ * Table window: the device table holds rows [row_lo, row_lo + num_rows) of the
+ * logical table; an index outside the window is skipped silently
+ * (reference `data_offset` / `count`, embedding_bag_plugin.cu:94).  This is
+ * the row-shard filter.
+ */
+typedef struct fwd_eb_params {
+  const void* table;        /* device, row-major [num_rows, dim], 16 B aligned for the fast path */
+  int32_t table_dtype;      /* FWD_EB_F32 / FWD_EB_F16 */
+  int32_t dim;              /* columns per row (> 0) */
+  int64_t num_rows;         /* rows held on this device */
+  int64_t row_lo;           /* logical id of local row 0 */
+  int64_t table_stride;     /* elements between rows; 0 = dim */
+
+  const void* indices;      /* device, [num_indices] */
+  const void* offsets;      /* device, [num_bags] (+1 with include_last_offset); NULL iff fixed_len > 0 */
+  int32_t index_dtype;      /* FWD_EB_I32 / FWD_EB_I64, for indices and offsets */
+  int32_t fixed_len;        /* > 0: every bag has this many indices */
+  int64_t num_indices;
+  int64_t num_bags;
+
+  const float* per_sample_weights; /* device fp32 [num_indices] or NULL; SUM only */
+  int32_t mode;             /* FWD_EB_MODE_* */
+  int32_t include_last_offset;
+  int64_t padding_idx;      /* logical index to skip; < 0 = none */
+
+  void* out;                /* device, [num_bags, dim] (GATHER: [num_indices, dim]) */
+  int32_t out_dtype;        /* FWD_EB_F32 / FWD_EB_F16 */
+  int32_t strategy;         /* FWD_EB_STRATEGY_* */
+  int64_t out_stride;       /* elements between output rows; 0 = dim */
+
+  void* workspace;          /* device scratch for FWD_EB_STRATEGY_SPLIT, or NULL */
+  size_t workspace_bytes;
+  uint32_t flags;           /* FWD_EB_FLAG_* */
+  int32_t reserved;
+} fwd_eb_params;
+
+/* ABI version of the loaded library (FWD_EB_ABI_VERSION). */
+int fwd_eb_version(void);
+
+/* sizeof(fwd_eb_params) as the library was compiled: lets a foreign-language
+ * binding check its own mirror of the struct. */
+size_t fwd_eb_params_size(void);
+
+/* Text for the calling thread's last non-zero return value ("" if none). */
+const char* fwd_eb_last_error_string(void);
+
+/* General entry point: validates `p`, picks a strategy, launches on `stream`.
+ * Replaces the dispatch in EmbeddingBagPlugin::enqueue
+ * (embedding_bag_plugin.cpp:146-189) plus the launchers it calls. */
+int fwd_eb_forward(const fwd_eb_params* p, void* stream);
+
+/* Scratch bytes fwd_eb_forward needs for `p` (0 unless the SPLIT strategy is
+ * requested or AUTO would choose it when scratch is offered).  The reference
+ * plugin reports 0 (embedding_bag_plugin.cpp:129-133). */
+size_t fwd_eb_workspace_size(const fwd_eb_params* p);
+
+/* Which strategy AUTO resolves to for `p` (a FWD_EB_STRATEGY_* value, or a
+ * negative error).  `p->workspace_bytes` decides whether SPLIT is on offer. */
+int fwd_eb_pick_strategy(const fwd_eb_params* p);
+
+/* Number of kernels launched by this library in the calling process so far. */
+uint64_t fwd_eb_launch_count(void);
+
+/*
+ * Source-compatible forms of the reference's three launchers
+ * (embedding_bag_plugin.h:40-49): fp32 table, int32 indices, fp32 output,
+ * 32-bit sizes.  `op_type` is a FWD_EB_MODE_* value.
+ */
+/* Gather(input, output, batch_size, offset, data, count, dim, data_offset, stream)
+ * — embedding_bag_plugin.cu:182-188.  Rows are addressed relative to
+ * data_offset (the reference kernel forgot to subtract it, .cu:178). */
+int fwd_eb_gather_f32(const int* d_input, float* d_output, int batch_size, int offset,
+                      const float* d_data, int count, int dim, int data_offset, void* stream);
+
+/* EmbeddingBagWithFixedOffset(...) — embedding_bag_plugin.cu:190-196. */
+int fwd_eb_bag_fixed_f32(const int* d_input, float* d_output, int batch_size, int offset,
+                         const float* d_data, int count, int dim, int data_offset, int op_type,
+                         void* stream);
+
+/* EmbeddingBag(input, input_2, output, input_size, block_size, ...) —
+ * embedding_bag_plugin.cu:198-206; block_size is the number of bags. */
+int fwd_eb_bag_f32(const int* d_input, const int* d_offsets, float* d_output, int input_size,
+                   int block_size, const float* d_data, int count, int dim, int data_offset,
+                   int op_type, void* stream);
+
+/* ---- helpers for tables too large to stage through the host ---------------- */
+
+/*
+ * Fill rows [row_lo, row_lo+num_rows) of a logical table in place on the
+ * device with the counter-based generator  value(seed,row,col) =
+ * scale * N(0,1), Box-Muller over a 64-bit mix of (seed,row,col).  A host twin
+ * (same bits) lives in the test oracle so a CPU check can regenerate only the
+ * rows a sampled bag touches.
+ */
+int fwd_eb_fill_table(void* d_table, int32_t table_dtype, int64_t num_rows, int32_t dim,
+                      int64_t row_lo, uint64_t seed, float scale, void* stream);
+
+/* out[i] = sum over r < num_parts of parts[r][i] (fp32 or fp16 wire, fp32 math,
+ * added in r order), optionally cast to `out_dtype`.  Used after a row-shard
+ * exchange where each peer's partial lands in its own slot. */
+int fwd_eb_combine_partials(const void* d_parts, int32_t part_dtype, int32_t num_parts,
+                            int64_t part_stride_elems, int64_t count, void* d_out,
+                            int32_t out_dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FWD_EB_H_ */
