@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <cstring>
 
+#include "eb_internal.h"
 #include "eb_kernels.cuh"
 #include "fwd_eb.h"
 
@@ -19,7 +20,7 @@ namespace fwd_eb {
 static thread_local char g_err[512] = "";
 static std::atomic<uint64_t> g_launches{0};
 
-static int fail(int code, const char* fmt, ...) {
+int fail(int code, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
@@ -27,10 +28,13 @@ static int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-static int cuda_fail(cudaError_t e, const char* what) {
+int cuda_fail(cudaError_t e, const char* what) {
   snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
   return (int)e;
 }
+
+void clear_error() { g_err[0] = '\0'; }
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -169,6 +173,8 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
   pl->tiles = (a.nchunks + tile_chunks - 1) / tile_chunks;
 
   a.table = static_cast<const char*>(p->table);
+  if (tstride * tsize > 0xffffffffLL)
+    return fail(FWD_EB_ETOOBIG, "table row stride must stay below 4 GiB");
   a.row_bytes_stride = tstride * tsize;
   a.num_rows = p->num_rows;
   a.row_lo = p->row_lo;
@@ -275,7 +281,7 @@ static cudaError_t launch_op(const Plan& pl, cudaStream_t st) {
   }
 }
 
-// Row loads kept in flight per lane group: 8 x 16 B for one chunk per lane,
+// Row loads kept in flight per lane group: FWD_EB_U1 (4) x 16 B for one chunk per lane,
 // fewer when a lane owns several chunks so the register count stays put.
 template <typename TW>
 static cudaError_t launch_shape(const Plan& pl, cudaStream_t st) {
@@ -283,7 +289,7 @@ static cudaError_t launch_shape(const Plan& pl, cudaStream_t st) {
   if (!pl.vec) return launch_op<TW, 1, 4, 4>(pl, st);
   switch (pl.cpl) {
     case 1:
-      return launch_op<TW, VE, 1, 8>(pl, st);
+      return launch_op<TW, VE, 1, FWD_EB_U1>(pl, st);
     case 2:
       return launch_op<TW, VE, 2, 4>(pl, st);
     default:

@@ -33,6 +33,13 @@ namespace fwd_eb {
 
 constexpr unsigned kFull = 0xffffffffu;
 constexpr int kCtaThreads = 256;
+// Resident CTAs per SM the pooling kernels are compiled for (caps registers per thread).
+#ifndef FWD_EB_MIN_CTAS
+#define FWD_EB_MIN_CTAS 4
+#endif
+#ifndef FWD_EB_U1
+#define FWD_EB_U1 4
+#endif
 
 enum Op { kOpSum = 0, kOpWeighted = 1, kOpMax = 2, kOpSquareSum = 3 };
 
@@ -109,6 +116,60 @@ __device__ __forceinline__ void fold(float& acc, float x, float w, bool first) {
   }
 }
 
+// acc += float(h), one rounding: sm_100's mixed-precision add takes the half operand as is,
+// which saves the separate conversion (same result as convert-then-add: the conversion is
+// exact).
+__device__ __forceinline__ void add_half(float& acc, unsigned short h) {
+  asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc) : "h"(h));
+}
+
+// Two fp32 adds in one instruction (sm_100 packed fp32 pipe); each lane rounds on its own.
+__device__ __forceinline__ void add_pair(float& a0, float& a1, float x0, float x1) {
+  unsigned long long acc, x;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(acc) : "f"(a0), "f"(a1));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(x) : "f"(x0), "f"(x1));
+  asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc) : "l"(x));
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc));
+}
+
+// Fold one loaded chunk into the accumulators.
+template <int OP>
+__device__ __forceinline__ void fold_chunk(float (&acc)[8], const uint4& v, float w, bool first) {
+  if (OP == kOpSum) {
+    const unsigned wd[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      add_half(acc[2 * i], (unsigned short)(wd[i] & 0xffffu));
+      add_half(acc[2 * i + 1], (unsigned short)(wd[i] >> 16));
+    }
+  } else {
+    float f[8];
+    unpack(v, f);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) fold<OP>(acc[e], f[e], w, first);
+  }
+}
+template <int OP>
+__device__ __forceinline__ void fold_chunk(float (&acc)[4], const float4& v, float w, bool first) {
+  if (OP == kOpSum) {
+    add_pair(acc[0], acc[1], v.x, v.y);
+    add_pair(acc[2], acc[3], v.z, v.w);
+  } else {
+    float f[4];
+    unpack(v, f);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) fold<OP>(acc[e], f[e], w, first);
+  }
+}
+template <int OP>
+__device__ __forceinline__ void fold_chunk(float (&acc)[1], const float& v, float w, bool first) {
+  fold<OP>(acc[0], v, w, first);
+}
+template <int OP>
+__device__ __forceinline__ void fold_chunk(float (&acc)[1], const __half& v, float w, bool first) {
+  fold<OP>(acc[0], __half2float(v), w, first);
+}
+
 __device__ __forceinline__ long long load_index(const void* p, int idx64, long long i) {
   return idx64 ? __ldg(reinterpret_cast<const long long*>(p) + i)
                : static_cast<long long>(__ldg(reinterpret_cast<const int*>(p) + i));
@@ -151,6 +212,7 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
   const int gbase = lane & ~(lanes - 1);
   const unsigned gmask = lanes == 32 ? kFull : ((1u << lanes) - 1u);
   const int vbytes = VE * (int)sizeof(TW);
+  const unsigned stride32 = (unsigned)a.row_bytes_stride;  // checked on the host: < 2^32
 
   bool chunk_ok[CPL];
   int chunk_off[CPL];
@@ -179,6 +241,39 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
     }
   };
 
+  // Issue U row loads, then fold them in order.  src[u] names the lane of this group that
+  // holds the row number, ok[u] switches the slot off.
+  auto consume = [&](const int (&src)[U], const bool (&ok)[U], int cur_row, float cur_w) {
+    int row[U];
+    float w[U];
+    V val[U][CPL];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      row[u] = __shfl_sync(kFull, cur_row, gbase + src[u]);
+      if (OP == kOpWeighted) w[u] = __shfl_sync(kFull, cur_w, gbase + src[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (ok[u]) {
+        const char* rp = a.table + (unsigned long long)(unsigned)row[u] * stride32;
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+          if (chunk_ok[c]) val[u][c] = load_chunk<V>(rp + chunk_off[c]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (ok[u]) {
+#pragma unroll
+        for (int c = 0; c < CPL; ++c) {
+          if (chunk_ok[c]) fold_chunk<OP>(s.v[c], val[u][c], OP == kOpWeighted ? w[u] : 1.0f, !s.have);
+        }
+        s.have = true;
+      }
+    }
+  };
+
   long long base = start;
   int cur_row, nxt_row;
   float cur_w, nxt_w;
@@ -187,52 +282,33 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
 
   while (__any_sync(kFull, base < end)) {
     fetch(base + lanes + lig, nxt_row, nxt_w, nxt_counted);  // next block of indices, early
+    long long left = end - base;
+    const int n = left <= 0 ? 0 : (left < lanes ? (int)left : lanes);  // entries of this block
+    const unsigned want = n >= 32 ? kFull : ((1u << n) - 1u);
     unsigned m = (__ballot_sync(kFull, cur_row >= 0) >> gbase) & gmask;
-    s.counted += __popc((__ballot_sync(kFull, cur_counted) >> gbase) & gmask);
+    if (a.mean) s.counted += __popc((__ballot_sync(kFull, cur_counted) >> gbase) & gmask);
 
-    while (__any_sync(kFull, m != 0u)) {
+    // When every entry of every group's block survived the filters the block is walked in
+    // place (slot k of a pass is entry k); otherwise the set bits of the survivor mask are
+    // walked.  Either way one pass issues U row loads per group.
+    const bool dense = __all_sync(kFull, m == want);
+    const int nmax = __reduce_max_sync(kFull, n);
+    for (int k = 0;; k += U) {
+      if (dense ? (k >= nmax) : !__any_sync(kFull, m != 0u)) break;
       int src[U];
-      int row[U];
-      float w[U];
-      V val[U][CPL];
+      bool ok[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        src[u] = m ? (__ffs(m) - 1) : -1;
-        m &= (m - 1u);  // clears the lowest set bit; 0 stays 0
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        int from = gbase + (src[u] < 0 ? 0 : src[u]);
-        row[u] = __shfl_sync(kFull, cur_row, from);
-        if (OP == kOpWeighted) w[u] = __shfl_sync(kFull, cur_w, from);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (src[u] >= 0) {
-          const char* rp = a.table + (long long)row[u] * a.row_bytes_stride;
-#pragma unroll
-          for (int c = 0; c < CPL; ++c) {
-            if (chunk_ok[c]) val[u][c] = load_chunk<V>(rp + chunk_off[c]);
-          }
+        if (dense) {
+          src[u] = (k + u) & (lanes - 1);
+          ok[u] = (k + u) < n;
+        } else {
+          ok[u] = m != 0u;
+          src[u] = ok[u] ? (__ffs(m) - 1) : 0;
+          m &= (m - 1u);  // clears the lowest set bit; 0 stays 0
         }
       }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (src[u] >= 0) {
-#pragma unroll
-          for (int c = 0; c < CPL; ++c) {
-            if (chunk_ok[c]) {
-              float f[VE];
-              unpack(val[u][c], f);
-#pragma unroll
-              for (int e = 0; e < VE; ++e) {
-                fold<OP>(s.v[c][e], f[e], OP == kOpWeighted ? w[u] : 1.0f, !s.have);
-              }
-            }
-          }
-          s.have = true;
-        }
-      }
+      consume(src, ok, cur_row, cur_w);
     }
     cur_row = nxt_row;
     cur_w = nxt_w;
@@ -313,7 +389,7 @@ __device__ __forceinline__ void clear(Accum<CPL, VE>& s) {
 // grid.x covers bags (kCtaThreads / lanes bags per CTA), grid.y covers column
 // tiles of 32 * CPL chunks for rows wider than one tile.
 template <typename TW, int VE, int CPL, int OP, int U>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_group_kernel(const PoolArgs a) {
   const int lanes_log2 = a.lanes_log2;
   const long long bag =
@@ -344,7 +420,7 @@ eb_pool_group_kernel(const PoolArgs a) {
 // first-of-equals rule for max.  With splits > 1 the folded partial goes to the
 // scratch arrays instead of the output and eb_split_finish_kernel completes it.
 template <typename TW, int VE, int CPL, int OP, int U>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_cta_kernel(const PoolArgs a) {
   extern __shared__ float smem[];  // [groups][tile_cols] then int[groups][2]
   const int lanes_log2 = a.lanes_log2;

@@ -104,3 +104,19 @@ def test_strategy_choice_and_workspace():
     assert lib.fwd_eb_pick_strategy(C.byref(few_huge)) == capi.STRATEGY_SPLIT
     few_huge.workspace_bytes = need - 1
     assert lib.fwd_eb_pick_strategy(C.byref(few_huge)) == capi.STRATEGY_CTA
+
+
+def test_session_symbols_and_no_gpu_failure():
+    """Every session entry point is exported; without a CUDA device creation fails with
+    ENOGPU instead of falling back to anything."""
+    from forward_b200 import session
+    lib = session._lib()
+    declared = _declared_symbols()
+    for name in session.SIGNATURES:
+        assert name in declared and hasattr(lib, name)
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(capi.FwdEbError) as e:
+            session.Session(table_dtype=capi.F16, dim=8, num_rows=4, mode=capi.MODE_SUM,
+                            max_indices=4, max_bags=2)
+        assert e.value.code == capi.ENOGPU
