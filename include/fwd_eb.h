@@ -146,6 +146,39 @@ int fwd_eb_forward(const fwd_eb_params* p, void* stream);
  * plugin reports 0 (embedding_bag_plugin.cpp:129-133). */
 size_t fwd_eb_workspace_size(const fwd_eb_params* p);
 
+/*
+ * Split-bag pooling for callers that may not allocate device memory.  It has no
+ * counterpart in the reference (whose plugin asks TensorRT for no workspace,
+ * embedding_bag_plugin.cpp:129-133, and so can never split a long bag).
+ *
+ * Who needs it: a plugin or serving loop that was given its buffers up front
+ * and must not call cudaMalloc afterwards — for example a TensorRT plugin that
+ * reported getWorkspaceSize() == 0 and therefore receives no workspace in
+ * enqueue(), or a host whose memory pool is frozen once serving starts.
+ *
+ * Same arguments and results as fwd_eb_forward with
+ * strategy = FWD_EB_STRATEGY_SPLIT, except that `workspace`, `workspace_bytes`
+ * and `strategy` in `p` are ignored: the partial sums of the split bags go to
+ * an array of FWD_EB_STATIC_SCRATCH_BYTES built into the library's device
+ * image (every GPU that loads the library holds that much until the process
+ * exits).  The call allocates nothing and frees nothing.
+ *
+ *   - A call whose split needs more than FWD_EB_STATIC_SCRATCH_BYTES
+ *     (fwd_eb_workspace_size with strategy SPLIT tells) returns
+ *     FWD_EB_ETOOBIG before anything is launched.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it; make that
+ *     first call before starting any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous
+ *     call's contents.  Nothing has to be cleared between calls — every slot a
+ *     call reads it has written first — but two calls that overlap on the GPU
+ *     (different streams, no dependency) would overwrite each other's
+ *     partials: keep calls to this entry point ordered on one stream, or
+ *     serialise them with events.
+ */
+#define FWD_EB_STATIC_SCRATCH_BYTES (8u << 20)
+int fwd_eb_forward_static_scratch(const fwd_eb_params* p, void* stream);
+
 /* Which strategy AUTO resolves to for `p` (a FWD_EB_STRATEGY_* value, or a
  * negative error).  `p->workspace_bytes` decides whether SPLIT is on offer. */
 int fwd_eb_pick_strategy(const fwd_eb_params* p);
