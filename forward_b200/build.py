@@ -63,18 +63,36 @@ def _run(cmd: list[str], verbose: bool) -> None:
         sys.stdout.write(proc.stdout + proc.stderr)
 
 
+CORE_SOURCES = ("eb_api.cu", "eb_session.cu", "eb_noalloc.cu", "eb_shard.cu")
+
+
 def build_core(force: bool = False, verbose: bool = False) -> str:
+    """Compile each translation unit (in parallel) and link libfwd_eb.so."""
+    from concurrent.futures import ThreadPoolExecutor
+
     target = os.path.join(LIBDIR, "libfwd_eb.so")
-    srcs = [os.path.join(CSRC, f) for f in ("eb_api.cu", "eb_session.cu", "eb_noalloc.cu")]
-    srcs = [s for s in srcs if os.path.exists(s)]
-    deps = srcs + _walk(CSRC, (".cuh", ".h")) + _walk(INCLUDE, (".h",))
-    if force or _stale(target, deps):
-        os.makedirs(LIBDIR, exist_ok=True)
-        cmd = [_nvcc()] + ARCH + NVCC_FLAGS + ["-DFWD_EB_BUILD", "-I", INCLUDE, "-I", CSRC]
-        if verbose:
-            cmd += ["-Xptxas", "-v"]
-        cmd += ["-o", target] + srcs
-        _run(cmd, verbose)
+    srcs = [os.path.join(CSRC, f) for f in CORE_SOURCES]
+    headers = _walk(CSRC, (".cuh", ".h")) + _walk(INCLUDE, (".h",))
+    headers = [h for h in headers if os.sep + "plugin" + os.sep not in h]
+    objdir = os.path.join(ROOT, "build", "obj")
+    os.makedirs(objdir, exist_ok=True)
+    os.makedirs(LIBDIR, exist_ok=True)
+    compile_flags = [f for f in NVCC_FLAGS if f not in ("-shared", "-Xlinker", "--exclude-libs", "ALL")]
+    jobs = []
+    objs = []
+    for src in srcs:
+        obj = os.path.join(objdir, os.path.basename(src) + ".o")
+        objs.append(obj)
+        if force or _stale(obj, [src] + headers):
+            cmd = [_nvcc()] + ARCH + compile_flags + ["-DFWD_EB_BUILD", "-I", INCLUDE, "-I", CSRC]
+            if verbose:
+                cmd += ["-Xptxas", "-v"]
+            jobs.append(cmd + ["-c", "-o", obj, src])
+    if jobs:
+        with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
+            list(pool.map(lambda c: _run(c, verbose), jobs))
+    if force or jobs or _stale(target, objs):
+        _run([_nvcc()] + ARCH + NVCC_FLAGS + ["-o", target] + objs, verbose)
     return target
 
 

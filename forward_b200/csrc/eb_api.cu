@@ -234,6 +234,19 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
   return 0;
 }
 
+int plan_group(const fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* tiles) {
+  Plan pl;
+  fwd_eb_params q = *p;
+  q.strategy = FWD_EB_STRATEGY_GROUP;
+  int rc = make_plan(&q, &pl);
+  if (rc) return rc;
+  *args = pl.a;
+  *vec = pl.vec ? 1 : 0;
+  *cpl = pl.cpl;
+  *tiles = pl.tiles;
+  return 0;
+}
+
 // ---- kernel dispatch ---------------------------------------------------------
 
 template <typename TW, int VE, int CPL, int OP, int U>

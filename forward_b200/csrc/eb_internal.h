@@ -3,6 +3,8 @@
 
 #include <cuda_runtime.h>
 
+struct fwd_eb_params;
+
 namespace fwd_eb {
 
 // Record the calling thread's error text and hand back `code`.
@@ -10,5 +12,10 @@ int fail(int code, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 void clear_error();
 void count_launch();
+
+struct PoolArgs;
+// Validate `p` and fill the kernel arguments for the lane-group strategy (shared by the
+// single-GPU launcher and the row-shard push).  vec / cpl / tiles describe the chosen shape.
+int plan_group(const struct ::fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* tiles);
 
 }  // namespace fwd_eb

@@ -332,8 +332,8 @@ __device__ __forceinline__ float finish(const PoolArgs& a, float acc, int counte
 
 // Write this lane's chunks of one output row.
 template <int VE, int CPL>
-__device__ __forceinline__ void store_row(const PoolArgs& a, long long out_row, int chunk0,
-                                          const float (&v)[CPL][VE]) {
+__device__ __forceinline__ void store_row(const PoolArgs& a, char* out_base, long long out_row,
+                                          int chunk0, const float (&v)[CPL][VE]) {
   const int lanes = 1 << a.lanes_log2;
   const int lig = (threadIdx.x & 31u) & (lanes - 1);
 #pragma unroll
@@ -342,7 +342,7 @@ __device__ __forceinline__ void store_row(const PoolArgs& a, long long out_row, 
     if (chunk >= a.nchunks) continue;
     long long col = (long long)chunk * VE;
     if (a.out_f16) {
-      __half* o = reinterpret_cast<__half*>(a.out) + out_row * a.out_stride + col;
+      __half* o = reinterpret_cast<__half*>(out_base) + out_row * a.out_stride + col;
       if (VE == 8 && a.out_vec) {
         uint4 pk;
         __half2* h = reinterpret_cast<__half2*>(&pk);
@@ -360,7 +360,7 @@ __device__ __forceinline__ void store_row(const PoolArgs& a, long long out_row, 
         for (int e = 0; e < VE; ++e) o[e] = __float2half_rn(v[c][e]);
       }
     } else {
-      float* o = reinterpret_cast<float*>(a.out) + out_row * a.out_stride + col;
+      float* o = reinterpret_cast<float*>(out_base) + out_row * a.out_stride + col;
       if (VE >= 4 && a.out_vec) {
 #pragma unroll
         for (int e = 0; e < VE; e += 4) {
@@ -409,7 +409,7 @@ eb_pool_group_kernel(const PoolArgs a) {
     for (int c = 0; c < CPL; ++c)
 #pragma unroll
       for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
-    store_row<VE, CPL>(a, bag, chunk0, s.v);
+    store_row<VE, CPL>(a, a.out, bag, chunk0, s.v);
   }
 }
 
@@ -562,7 +562,7 @@ eb_gather_kernel(const PoolArgs a, int keep_skipped) {
       for (int e = 0; e < VE; ++e) f[0][e] = 0.0f;
     }
     // store_row addresses chunk0 + lig; hand it the chunk minus this lane's slot
-    store_row<VE, 1>(a, t, chunk - lig, f);
+    store_row<VE, 1>(a, a.out, t, chunk - lig, f);
   }
 }
 

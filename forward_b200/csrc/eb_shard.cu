@@ -1,0 +1,391 @@
+// Row-sharded pooling fused with its exchange (include/fwd_eb_shard.h).
+//
+// The pooling loop is the one every strategy shares (pool_range); what changes is the
+// epilogue: instead of a local output row, the lane group stores its partial row into the
+// owner rank's receive slot through a peer-mapped pointer, so the NVLink transfer of early
+// bags overlaps the HBM gathers of later ones and the partial never makes a round trip
+// through local memory.  The last CTA to finish raises this rank's flag on every peer.
+#include <climits>
+#include <cstring>
+
+#include "eb_internal.h"
+#include "eb_kernels.cuh"
+#include "fwd_eb_shard.h"
+
+namespace fwd_eb {
+
+struct PushArgs {
+  char* peer_slots[FWD_EB_MAX_PEERS];  // already offset to this call's buffer half
+  uint32_t* peer_flags[FWD_EB_MAX_PEERS];
+  uint32_t* counter;
+  long long bags_per_rank;
+  long long row_base;    // destination row of this rank's first bag inside the owner's buffer
+  long long col_offset;  // destination column of this call's first column
+  int world;
+  int rank;
+  int signal;            // raise the flags when the grid is done
+  uint32_t epoch;
+};
+
+__device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The CTA that finishes last tells every peer that this rank's partials have landed.
+__device__ __forceinline__ void signal_when_last(const PushArgs& x) {
+  if (!x.signal) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // this CTA's peer stores before the count
+    const unsigned total = gridDim.x * gridDim.y;
+    const unsigned done = atomicAdd(x.counter, 1u);
+    if (done == total - 1) {
+      *x.counter = 0;  // ready for the next call
+      __threadfence_system();
+      for (int r = 0; r < x.world; ++r) store_release_sys(x.peer_flags[r] + x.rank, x.epoch);
+    }
+  }
+}
+
+template <typename TW, int VE, int CPL, int OP, int U>
+__global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
+eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
+  const int lanes_log2 = a.lanes_log2;
+  const long long bag = ((long long)blockIdx.x * kCtaThreads + threadIdx.x) >> lanes_log2;
+  const int chunk0 = blockIdx.y * (CPL << lanes_log2);
+  const bool live = bag < a.num_bags;
+  long long start = 0, end = 0;
+  if (live) bag_bounds(a, bag, start, end);
+
+  Accum<CPL, VE> s;
+  clear(s);
+  pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
+
+  if (live) {
+    const bool tf16 = sizeof(TW) == 2;
+#pragma unroll
+    for (int c = 0; c < CPL; ++c)
+#pragma unroll
+      for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
+    long long owner = bag / x.bags_per_rank;
+    if (owner >= x.world) owner = x.world - 1;
+    const long long local_bag = bag - owner * x.bags_per_rank;
+    // this rank's slot (row shards) or this table's column block (table-wise) at the owner
+    char* base = x.peer_slots[owner] + x.col_offset * (a.out_f16 ? 2 : 4);
+    store_row<VE, CPL>(a, base, x.row_base + local_bag, chunk0, s.v);
+  }
+  signal_when_last(x);
+}
+
+__global__ void eb_shard_signal_kernel(const PushArgs x) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    __threadfence_system();
+    for (int r = 0; r < x.world; ++r) store_release_sys(x.peer_flags[r] + x.rank, x.epoch);
+  }
+}
+
+// Bounded wait for all flags; nothing else (table-wise layout needs no folding).
+__global__ void eb_shard_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, int* status,
+                                     long long max_spins) {
+  if (threadIdx.x < world) {
+    long long spins = 0;
+    while ((int)(load_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
+      if (++spins >= max_spins) {
+        atomicExch(status, FWD_EB_SHARD_TIMEOUT);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+// Wait (bounded) for every source rank's flag, then fold the slots in rank order.
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_shard_combine_kernel(const TP* slots, const uint32_t* flags, int world, uint32_t epoch,
+                        long long slot_stride, long long count, TO* out, int* status,
+                        long long max_spins) {
+  __shared__ int timed_out;
+  if (threadIdx.x == 0) timed_out = 0;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    long long spins = 0;
+    // flags only grow; a peer may already be one call ahead
+    while ((int)(load_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
+      if (++spins >= max_spins) {
+        atomicExch(&timed_out, 1);
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  if (timed_out) {
+    if (threadIdx.x == 0) atomicExch(status, FWD_EB_SHARD_TIMEOUT);
+    return;
+  }
+  for (long long i = (long long)blockIdx.x * kCtaThreads + threadIdx.x; i < count;
+       i += (long long)gridDim.x * kCtaThreads) {
+    float s = 0.0f;
+    for (int r = 0; r < world; ++r) {
+      float v;
+      if (sizeof(TP) == 2) {
+        v = __half2float(reinterpret_cast<const __half*>(slots)[r * slot_stride + i]);
+      } else {
+        v = reinterpret_cast<const float*>(slots)[r * slot_stride + i];
+      }
+      s = __fadd_rn(s, v);
+    }
+    if (sizeof(TO) == 2) {
+      reinterpret_cast<__half*>(out)[i] = __float2half_rn(s);
+    } else {
+      reinterpret_cast<float*>(out)[i] = s;
+    }
+  }
+}
+
+static int check_exchange(const fwd_eb_shard_exchange* x) {
+  if (!x) return fail(FWD_EB_EINVAL, "exchange description is null");
+  if (x->world < 1 || x->world > FWD_EB_MAX_PEERS)
+    return fail(FWD_EB_EINVAL, "world must be 1..%d (got %d)", FWD_EB_MAX_PEERS, x->world);
+  if (x->rank < 0 || x->rank >= x->world) return fail(FWD_EB_EINVAL, "rank %d outside the world", x->rank);
+  if (x->bags_per_rank <= 0) return fail(FWD_EB_EINVAL, "bags_per_rank must be positive");
+  if (x->wire_dtype != FWD_EB_F32 && x->wire_dtype != FWD_EB_F16)
+    return fail(FWD_EB_EINVAL, "unknown wire_dtype %d", x->wire_dtype);
+  if (x->epoch == 0) return fail(FWD_EB_EINVAL, "epoch starts at 1");
+  if (!x->counter || !x->status) return fail(FWD_EB_EINVAL, "counter / status word is null");
+  for (int r = 0; r < x->world; ++r) {
+    if (!x->peer_slots[r] || !x->peer_flags[r])
+      return fail(FWD_EB_EINVAL, "peer %d has no mapped slots / flags", r);
+  }
+  if (x->layout != FWD_EB_LAYOUT_ROW_SHARD && x->layout != FWD_EB_LAYOUT_TABLE_WISE)
+    return fail(FWD_EB_EINVAL, "unknown layout %d", x->layout);
+  if (x->layout == FWD_EB_LAYOUT_TABLE_WISE &&
+      (x->num_tables < 1 || x->table_index < 0 || x->table_index >= x->num_tables))
+    return fail(FWD_EB_EINVAL, "table_index %d outside %d tables", x->table_index, x->num_tables);
+  return 0;
+}
+
+static size_t half_bytes(const fwd_eb_shard_exchange* x, int dim) {
+  const size_t blocks = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (size_t)x->num_tables : (size_t)x->world;
+  return blocks * (size_t)x->bags_per_rank * (size_t)dim * (x->wire_dtype == FWD_EB_F16 ? 2u : 4u);
+}
+
+static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
+  memset(out, 0, sizeof(*out));
+  const size_t half = half_bytes(x, dim) * (x->epoch & 1u);
+  for (int r = 0; r < x->world; ++r) {
+    out->peer_slots[r] = static_cast<char*>(x->peer_slots[r]) + half;
+    out->peer_flags[r] = x->peer_flags[r];
+  }
+  out->counter = x->counter;
+  out->signal = x->hold_signal ? 0 : 1;
+  if (x->layout == FWD_EB_LAYOUT_TABLE_WISE) {
+    out->row_base = 0;
+    out->col_offset = (long long)x->table_index * dim;
+  } else {
+    out->row_base = (long long)x->rank * x->bags_per_rank;
+    out->col_offset = 0;
+  }
+  out->bags_per_rank = x->bags_per_rank;
+  out->world = x->world;
+  out->rank = x->rank;
+  out->epoch = x->epoch;
+}
+
+template <typename TW, int VE, int CPL, int U>
+static cudaError_t launch_push(const PoolArgs& a, const PushArgs& x, int tiles, bool weighted,
+                               cudaStream_t st) {
+  const long long threads = a.num_bags << a.lanes_log2;
+  long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+  if (blocks < 1) blocks = 1;  // the signal still has to go out
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  dim3 grid((unsigned)blocks, (unsigned)tiles);
+  if (weighted) {
+    eb_pool_push_kernel<TW, VE, CPL, kOpWeighted, U><<<grid, kCtaThreads, 0, st>>>(a, x);
+  } else {
+    eb_pool_push_kernel<TW, VE, CPL, kOpSum, U><<<grid, kCtaThreads, 0, st>>>(a, x);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+template <typename TW>
+static cudaError_t launch_push_shape(const PoolArgs& a, const PushArgs& x, bool vec, int cpl,
+                                     int tiles, bool weighted, cudaStream_t st) {
+  constexpr int VE = 16 / (int)sizeof(TW);
+  if (!vec) return launch_push<TW, 1, 4, 4>(a, x, tiles, weighted, st);
+  if (cpl == 1) return launch_push<TW, VE, 1, FWD_EB_U1>(a, x, tiles, weighted, st);
+  if (cpl == 2) return launch_push<TW, VE, 2, 4>(a, x, tiles, weighted, st);
+  return launch_push<TW, VE, 4, 2>(a, x, tiles, weighted, st);
+}
+
+}  // namespace fwd_eb
+
+using namespace fwd_eb;
+
+extern "C" {
+
+size_t fwd_eb_shard_slots_bytes(int32_t world, int64_t bags_per_rank, int32_t dim,
+                                int32_t wire_dtype) {
+  if (world < 1 || bags_per_rank < 1 || dim < 1) return 0;
+  return 2u * (size_t)world * (size_t)bags_per_rank * (size_t)dim * (wire_dtype == FWD_EB_F16 ? 2u : 4u);
+}
+
+int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream) {
+  int rc = check_exchange(x);
+  if (rc) return rc;
+  if (!p) return fail(FWD_EB_EINVAL, "params is null");
+  if (p->mode != FWD_EB_MODE_SUM && p->mode != FWD_EB_MODE_MEAN)
+    return fail(FWD_EB_EUNSUPPORTED, "pushed pooling supports SUM and MEAN (got mode %d)", p->mode);
+  if (p->num_bags > x->bags_per_rank * x->world)
+    return fail(FWD_EB_EINVAL, "%lld bags do not fit %d ranks x %lld bags", (long long)p->num_bags,
+                x->world, (long long)x->bags_per_rank);
+  // Reuse the single-GPU planner for shapes and checks; the output it plans for is replaced.
+  fwd_eb_params q = *p;
+  q.strategy = FWD_EB_STRATEGY_GROUP;
+  q.out = x->peer_slots[x->rank];
+  q.out_dtype = x->wire_dtype;
+  q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean torch would round
+  q.out_stride = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (int64_t)x->num_tables * p->dim : 0;
+  PoolArgs a;
+  int vec = 0, cpl = 0, tiles = 0;
+  rc = plan_group(&q, &a, &vec, &cpl, &tiles);
+  if (rc) return rc;
+  PushArgs px;
+  fill_push(x, p->dim, &px);
+  const bool weighted = p->per_sample_weights != nullptr;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = p->table_dtype == FWD_EB_F16
+                      ? launch_push_shape<__half>(a, px, vec != 0, cpl, tiles, weighted, st)
+                      : launch_push_shape<float>(a, px, vec != 0, cpl, tiles, weighted, st);
+  if (e != cudaSuccess) return cuda_fail(e, "push kernel launch");
+  clear_error();
+  return 0;
+}
+
+size_t fwd_eb_shard_tablewise_bytes(int64_t bags_per_rank, int32_t num_tables, int32_t dim,
+                                    int32_t wire_dtype) {
+  if (num_tables < 1 || bags_per_rank < 1 || dim < 1) return 0;
+  return 2u * (size_t)num_tables * (size_t)bags_per_rank * (size_t)dim * (wire_dtype == FWD_EB_F16 ? 2u : 4u);
+}
+
+int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_result, void* stream) {
+  int rc = check_exchange(x);
+  if (rc) return rc;
+  if (dim <= 0) return fail(FWD_EB_EINVAL, "dim must be positive");
+  const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
+  eb_shard_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      x->peer_flags[x->rank], x->world, x->epoch, x->status, spins);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "wait kernel launch");
+  if (d_result)
+    *d_result = static_cast<char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch & 1u);
+  return 0;
+}
+
+int fwd_eb_shard_signal(const fwd_eb_shard_exchange* x, void* stream) {
+  int rc = check_exchange(x);
+  if (rc) return rc;
+  PushArgs px;
+  fill_push(x, 1, &px);
+  eb_shard_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(px);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "signal kernel launch");
+  return 0;
+}
+
+int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                         void* d_out, int32_t out_dtype, void* stream) {
+  int rc = check_exchange(x);
+  if (rc) return rc;
+  if (dim <= 0 || num_bags < 0 || num_bags > x->bags_per_rank || (num_bags > 0 && !d_out))
+    return fail(FWD_EB_EINVAL, "bad combine arguments");
+  if (out_dtype != FWD_EB_F32 && out_dtype != FWD_EB_F16)
+    return fail(FWD_EB_EINVAL, "unknown out_dtype %d", out_dtype);
+  const long long count = (long long)num_bags * dim;
+  const long long slot_stride = (long long)x->bags_per_rank * dim;
+  const char* slots = static_cast<const char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch & 1u);
+  const uint32_t* flags = x->peer_flags[x->rank];
+  const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
+  long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  const unsigned g = (unsigned)blocks;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
+  if (!wire16 && !out16) {
+    eb_shard_combine_kernel<float, float><<<g, kCtaThreads, 0, st>>>(
+        reinterpret_cast<const float*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        static_cast<float*>(d_out), x->status, spins);
+  } else if (!wire16 && out16) {
+    eb_shard_combine_kernel<float, __half><<<g, kCtaThreads, 0, st>>>(
+        reinterpret_cast<const float*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        static_cast<__half*>(d_out), x->status, spins);
+  } else if (wire16 && !out16) {
+    eb_shard_combine_kernel<__half, float><<<g, kCtaThreads, 0, st>>>(
+        reinterpret_cast<const __half*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        static_cast<float*>(d_out), x->status, spins);
+  } else {
+    eb_shard_combine_kernel<__half, __half><<<g, kCtaThreads, 0, st>>>(
+        reinterpret_cast<const __half*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        static_cast<__half*>(d_out), x->status, spins);
+  }
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "combine kernel launch");
+  clear_error();
+  return 0;
+}
+
+// ---- CUDA IPC ----------------------------------------------------------------------------------
+
+int fwd_eb_ipc_alloc(size_t bytes, void** d_ptr, unsigned char handle[FWD_EB_IPC_HANDLE_BYTES]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == FWD_EB_IPC_HANDLE_BYTES, "handle size");
+  if (!d_ptr || !handle || bytes == 0) return fail(FWD_EB_EINVAL, "bad ipc_alloc arguments");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc (ipc)");
+  e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) {
+    cudaIpcMemHandle_t h;
+    e = cudaIpcGetMemHandle(&h, p);
+    if (e == cudaSuccess) memcpy(handle, &h, sizeof(h));
+  }
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail(e, "cudaIpcGetMemHandle");
+  }
+  *d_ptr = p;
+  return 0;
+}
+
+int fwd_eb_ipc_open(const unsigned char handle[FWD_EB_IPC_HANDLE_BYTES], void** d_peer_ptr) {
+  if (!handle || !d_peer_ptr) return fail(FWD_EB_EINVAL, "bad ipc_open arguments");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(d_peer_ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaIpcOpenMemHandle");
+  return 0;
+}
+
+int fwd_eb_ipc_close(void* d_peer_ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(d_peer_ptr);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaIpcCloseMemHandle");
+  return 0;
+}
+
+int fwd_eb_ipc_free(void* d_ptr) {
+  cudaError_t e = cudaFree(d_ptr);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFree (ipc)");
+  return 0;
+}
+
+}  // extern "C"

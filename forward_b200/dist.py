@@ -1,0 +1,406 @@
+"""Multi-GPU EmbeddingBag: row-sharded tables and table-wise placement.
+
+One process per GPU.  `torch.distributed` carries the rendezvous (IPC handle exchange) and, for
+the plain variants, the collective; the fused variants move data with the pooling kernels' own
+peer stores (include/fwd_eb_shard.h).
+
+Row shards (one huge table): rank r holds rows [r*rows/G, (r+1)*rows/G); every rank gets the whole
+batch, pools what it owns into partial bags, and bag b ends up, summed, on rank b // bags_per_rank.
+  exchange="nccl"  partial [B, D] fp32 in local memory, then ncclReduceScatter
+  exchange="a2a"   all-to-all of the partial slices, then a fixed-order fold (deterministic)
+  exchange="push"  fwd_eb_shard_push / fwd_eb_shard_combine: partial rows go straight into the
+                   owner's slots over NVLink from inside the pooling kernel
+
+Table-wise (many tables): whole tables are assigned to ranks; each rank pools the full batch for
+its tables and the pooled outputs are exchanged so that rank g ends with [B/G, T, D].
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+MAX_PEERS = 16
+LAYOUT_ROW_SHARD, LAYOUT_TABLE_WISE = 0, 1
+SHARD_TIMEOUT = 1
+
+
+# ---- host-side geometry (pure Python; covered by CPU tests) ---------------------------------------
+
+def shard_rows(num_rows: int, world: int, rank: int) -> tuple[int, int]:
+    """(first logical row, row count) of `rank`: equal windows, the last takes the remainder."""
+    per = -(-num_rows // world)
+    lo = min(rank * per, num_rows)
+    return lo, min(per, num_rows - lo)
+
+
+def bags_per_rank(num_bags: int, world: int) -> int:
+    return max(1, -(-num_bags // world))
+
+
+def owned_bags(num_bags: int, world: int, rank: int) -> tuple[int, int]:
+    per = bags_per_rank(num_bags, world)
+    lo = min(rank * per, num_bags)
+    return lo, min(per, num_bags - lo)
+
+
+def place_tables(table_bytes: list[int], world: int, lookups: list[int] | None = None) -> list[int]:
+    """Owner rank of every table.  Greedy longest-processing-time on the per-call cost (lookups per
+    table; equal when None) with ties broken towards the rank holding fewer bytes, so both time
+    and capacity stay balanced.  Deterministic."""
+    n = len(table_bytes)
+    cost = list(lookups) if lookups is not None else [1] * n
+    order = sorted(range(n), key=lambda t: (-cost[t], -table_bytes[t], t))
+    load = [0] * world
+    held = [0] * world
+    owner = [0] * n
+    for t in order:
+        r = min(range(world), key=lambda k: (load[k], held[k], k))
+        owner[t] = r
+        load[r] += cost[t]
+        held[r] += table_bytes[t]
+    return owner
+
+
+# ---- C structs -----------------------------------------------------------------------------------
+
+class ShardExchange(C.Structure):
+    """Mirror of struct fwd_eb_shard_exchange."""
+    _fields_ = [
+        ("world", C.c_int32), ("rank", C.c_int32), ("bags_per_rank", C.c_int64),
+        ("wire_dtype", C.c_int32), ("epoch", C.c_uint32),
+        ("peer_slots", C.c_void_p * MAX_PEERS), ("peer_flags", C.c_void_p * MAX_PEERS),
+        ("counter", C.c_void_p), ("status", C.c_void_p), ("max_spins", C.c_int64),
+        ("layout", C.c_int32), ("num_tables", C.c_int32), ("table_index", C.c_int32),
+        ("hold_signal", C.c_int32),
+    ]
+
+
+SIGNATURES = {
+    "fwd_eb_shard_slots_bytes": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int32, C.c_int32]),
+    "fwd_eb_shard_tablewise_bytes": (C.c_size_t, [C.c_int64, C.c_int32, C.c_int32, C.c_int32]),
+    "fwd_eb_shard_push": (C.c_int, [C.POINTER(capi.Params), C.POINTER(ShardExchange), C.c_void_p]),
+    "fwd_eb_shard_combine": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.c_int64, C.c_void_p,
+                                       C.c_int32, C.c_void_p]),
+    "fwd_eb_shard_wait": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.POINTER(C.c_void_p),
+                                    C.c_void_p]),
+    "fwd_eb_shard_signal": (C.c_int, [C.POINTER(ShardExchange), C.c_void_p]),
+    "fwd_eb_ipc_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "fwd_eb_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "fwd_eb_ipc_close": (C.c_int, [C.c_void_p]),
+    "fwd_eb_ipc_free": (C.c_int, [C.c_void_p]),
+}
+
+_bound = False
+
+
+def _lib():
+    global _bound
+    lib = capi.lib()
+    if not _bound:
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _bound = True
+    return lib
+
+
+# ---- peer-mapped buffers ---------------------------------------------------------------------------
+
+class PeerBuffers:
+    """This rank's receive slots + flag words, and every peer's view of theirs.
+
+    With a process group the buffers are cudaMalloc'ed here, their CUDA IPC handles all-gathered
+    and the peers' buffers opened.  Without one (`local_world` given) all "ranks" live on this GPU
+    and the peer pointers are ordinary local pointers — used to test the kernels on one GPU by
+    running the ranks' launches one after another."""
+
+    def __init__(self, slot_bytes: int, world: int, rank: int, group=None, local_world=None):
+        import torch
+        lib = _lib()
+        self.world, self.rank = world, rank
+        self.slots = [0] * world
+        self.flags = [0] * world
+        self._opened = []
+        self._own = []
+        self._keep = []
+        if local_world is not None:
+            for r in range(world):
+                s = torch.zeros(slot_bytes, dtype=torch.uint8, device="cuda")
+                f = torch.zeros(MAX_PEERS, dtype=torch.int32, device="cuda")
+                self._keep += [s, f]
+                self.slots[r], self.flags[r] = s.data_ptr(), f.data_ptr()
+            return
+        import torch.distributed as dist
+        handles = []
+        for nbytes in (slot_bytes, MAX_PEERS * 4):
+            ptr = C.c_void_p()
+            h = C.create_string_buffer(64)
+            capi.check(lib.fwd_eb_ipc_alloc(nbytes, C.byref(ptr), h))
+            self._own.append(ptr.value)
+            handles.append(h.raw)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, handles, group=group)
+        for r in range(world):
+            if r == rank:
+                self.slots[r], self.flags[r] = self._own
+                continue
+            got = []
+            for raw in gathered[r]:
+                ptr = C.c_void_p()
+                capi.check(lib.fwd_eb_ipc_open(raw, C.byref(ptr)))
+                self._opened.append(ptr.value)
+                got.append(ptr.value)
+            self.slots[r], self.flags[r] = got
+        dist.barrier(group=group)
+
+    def close(self):
+        lib = _lib()
+        for p in self._opened:
+            lib.fwd_eb_ipc_close(C.c_void_p(p))
+        for p in self._own:
+            lib.fwd_eb_ipc_free(C.c_void_p(p))
+        self._opened, self._own, self._keep = [], [], []
+
+
+def make_exchange(buffers: PeerBuffers, rank: int, per_rank_bags: int, wire_dtype: int, counter,
+                  status, *, layout=LAYOUT_ROW_SHARD, num_tables=0, max_spins=0) -> ShardExchange:
+    x = ShardExchange()
+    x.world, x.rank = buffers.world, rank
+    x.bags_per_rank = per_rank_bags
+    x.wire_dtype = wire_dtype
+    x.epoch = 0
+    for r in range(buffers.world):
+        x.peer_slots[r] = buffers.slots[r]
+        x.peer_flags[r] = buffers.flags[r]
+    x.counter = counter.data_ptr()
+    x.status = status.data_ptr()
+    x.max_spins = max_spins
+    x.layout = layout
+    x.num_tables = num_tables
+    return x
+
+
+# ---- row-sharded table -------------------------------------------------------------------------------
+
+class RowShardedBag:
+    """EmbeddingBag over a table split by rows across the ranks of `group`."""
+
+    def __init__(self, table_local, row_lo: int, *, mode: int, max_bags: int, group=None,
+                 exchange: str = "push", wire_dtype: int = capi.F32, padding_idx: int = -1,
+                 out_dtype=None):
+        import torch
+        import torch.distributed as dist
+        if mode not in (capi.MODE_SUM, capi.MODE_MEAN):
+            raise ValueError("row-sharded pooling supports sum and mean")
+        self.table, self.row_lo, self.mode, self.padding_idx = table_local, row_lo, mode, padding_idx
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.exchange = exchange
+        self.dim = table_local.shape[1]
+        self.max_bags = max_bags
+        self.per = bags_per_rank(max_bags, self.world)
+        self.out_dtype = out_dtype or torch.float32
+        dev = table_local.device
+        self.out = torch.empty((self.per, self.dim), dtype=self.out_dtype, device=dev)
+        self.epoch = 0
+        if exchange == "push":
+            nbytes = _lib().fwd_eb_shard_slots_bytes(self.world, self.per, self.dim, wire_dtype)
+            self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
+            self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.counter,
+                                   self.status)
+        elif exchange in ("nccl", "a2a"):
+            self.partial = torch.empty((self.per * self.world, self.dim), dtype=torch.float32,
+                                       device=dev)
+            if exchange == "a2a":
+                self.recv = torch.empty_like(self.partial)
+            self.out32 = (self.out if self.out_dtype == torch.float32 else
+                          torch.empty((self.per, self.dim), dtype=torch.float32, device=dev))
+        else:
+            raise ValueError(exchange)
+
+    def params(self, indices, offsets, out):
+        return capi.make_params(self.table, indices, offsets, out=out, mode=self.mode,
+                                padding_idx=self.padding_idx, row_lo=self.row_lo)
+
+    def forward(self, indices, offsets):
+        """Returns this rank's [bags_owned, dim] slice of the pooled output (a view reused by the
+        next call)."""
+        import torch
+        import torch.distributed as dist
+        num_bags = offsets.numel()
+        if num_bags > self.max_bags:
+            raise ValueError("batch larger than max_bags")
+        stream = capi.current_stream_ptr()
+        _, mine = owned_bags(self.per * self.world, self.world, self.rank)
+        mine = max(0, min(mine, num_bags - self.rank * self.per))
+        if self.exchange == "push":
+            self.epoch += 1
+            self.x.epoch = self.epoch
+            p = self.params(indices, offsets, self.out)
+            capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
+            capi.check(_lib().fwd_eb_shard_combine(C.byref(self.x), self.dim, mine,
+                                                   self.out.data_ptr(),
+                                                   capi._torch_dtype_code(self.out),
+                                                   C.c_void_p(stream)))
+            return self.out[:mine]
+        if num_bags < self.per * self.world:
+            self.partial[num_bags:].zero_()
+        p = self.params(indices, offsets, self.partial)
+        capi.forward(p, stream)
+        if self.exchange == "nccl":
+            dist.reduce_scatter_tensor(self.out32, self.partial, group=self.group)
+        else:
+            dist.all_to_all_single(self.recv, self.partial, group=self.group)
+            capi.combine_partials(self.recv.view(self.world, self.per, self.dim), self.out32)
+        if self.out32 is not self.out:
+            self.out.copy_(self.out32)
+        return self.out[:mine]
+
+    def check_status(self) -> int:
+        """Non-zero when a bounded wait gave up (reads one device word; synchronises)."""
+        return int(self.status.item()) if self.exchange == "push" else 0
+
+    def close(self):
+        if self.exchange == "push":
+            self.buffers.close()
+
+
+def exchange_partials(partial, world: int, per: int, group=None, method: str = "a2a", fold=None):
+    """Combine per-rank partial bags [world*per, dim] into this rank's [per, dim] slice.
+
+    "nccl": reduce-scatter (the library picks the order of the additions).  "a2a": all-to-all of
+    the slices, then `fold` adds the `world` received slices in source-rank order (default: the
+    CUDA fold kernel; CPU tensors need a caller-supplied fold, there is no CPU path here)."""
+    import torch
+    import torch.distributed as dist
+    dim = partial.shape[1]
+    if method == "nccl":
+        out = torch.empty((per, dim), dtype=partial.dtype, device=partial.device)
+        dist.reduce_scatter_tensor(out, partial, group=group)
+        return out
+    recv = torch.empty_like(partial)
+    dist.all_to_all_single(recv, partial, group=group)
+    recv = recv.view(world, per, dim)
+    if fold is not None:
+        return fold(recv)
+    if not partial.is_cuda:
+        raise RuntimeError("exchange_partials: folding on the host needs an explicit `fold`")
+    out = torch.empty((per, dim), dtype=partial.dtype, device=partial.device)
+    capi.combine_partials(recv, out)
+    return out
+
+
+class _DeviceView:
+    """Lets torch wrap device memory this library allocated (CUDA array interface)."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr,
+                                         "data": (ptr, False), "version": 2}
+
+
+class TableWiseBags:
+    """Many tables, each held whole by one rank; pooled outputs land as [bags_owned, T, dim].
+
+    exchange="push": each pooling kernel writes its table's column block of every owner's result
+    buffer over NVLink (no staging copy, no separate all-to-all kernel).  exchange="nccl": pooled
+    [B, T_local, dim] then ncclAllToAll and a local re-layout."""
+
+    def __init__(self, local_tables: dict, owner: list[int], *, dim: int, max_bags: int, group=None,
+                 exchange: str = "push", wire_dtype: int = capi.F32, mode: int = capi.MODE_SUM,
+                 fixed_len: int = 0, padding_idx: int = -1):
+        import torch
+        import torch.distributed as dist
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.owner = list(owner)
+        self.num_tables = len(owner)
+        self.mine = [t for t, r in enumerate(owner) if r == self.rank]
+        if sorted(local_tables) != self.mine:
+            raise ValueError("local_tables must hold exactly the tables this rank owns")
+        self.tables = local_tables
+        self.dim, self.mode, self.fixed_len, self.padding_idx = dim, mode, fixed_len, padding_idx
+        self.per = bags_per_rank(max_bags, self.world)
+        self.exchange = exchange
+        self.wire_dtype = wire_dtype
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.epoch = 0
+        if exchange == "push":
+            nbytes = _lib().fwd_eb_shard_tablewise_bytes(self.per, self.num_tables, dim, wire_dtype)
+            self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
+            self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.counter,
+                                   self.status, layout=LAYOUT_TABLE_WISE, num_tables=self.num_tables)
+        else:
+            tl = max(1, len(self.mine))
+            self.send = torch.zeros((self.per * self.world, tl, dim), dtype=torch.float32, device=dev)
+            self.recv = torch.empty((self.per * self.num_tables, dim), dtype=torch.float32, device=dev)
+            self.result = torch.empty((self.per, self.num_tables, dim), dtype=torch.float32, device=dev)
+            counts = [sum(1 for r in owner if r == src) for src in range(self.world)]
+            self.in_splits = [self.per * len(self.mine)] * self.world
+            self.out_splits = [self.per * c for c in counts]
+            self.by_src = [[t for t, r in enumerate(owner) if r == src] for src in range(self.world)]
+
+    def forward(self, inputs: dict):
+        """inputs[t] = (indices, offsets_or_None, weights_or_None) for every table this rank owns.
+        Returns [per, T, dim] (rows past the bags this rank owns are unspecified)."""
+        import torch
+        import torch.distributed as dist
+        stream = capi.current_stream_ptr()
+        if self.exchange == "push":
+            self.epoch += 1
+            self.x.epoch = self.epoch
+            if not self.mine:
+                capi.check(_lib().fwd_eb_shard_signal(C.byref(self.x), C.c_void_p(stream)))
+            for k, t in enumerate(self.mine):
+                idx, off, w = inputs[t]
+                # `out` is ignored by the push entry point; any CUDA tensor satisfies the binding
+                p = capi.make_params(self.tables[t], idx, off, out=self.tables[t][:1], mode=self.mode,
+                                     fixed_len=self.fixed_len, per_sample_weights=w,
+                                     padding_idx=self.padding_idx)
+                self.x.table_index = t
+                self.x.hold_signal = 0 if k == len(self.mine) - 1 else 1
+                capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
+            res = C.c_void_p()
+            capi.check(_lib().fwd_eb_shard_wait(C.byref(self.x), self.dim, C.byref(res),
+                                                C.c_void_p(stream)))
+            typestr = "<f2" if self.wire_dtype == capi.F16 else "<f4"
+            return torch.as_tensor(_DeviceView(res.value, (self.per, self.num_tables, self.dim), typestr),
+                                   device="cuda")
+        tl = len(self.mine)
+        for k, t in enumerate(self.mine):
+            idx, off, w = inputs[t]
+            out = self.send[:, k, :]
+            p = capi.make_params(self.tables[t], idx, off, out=out, mode=self.mode,
+                                 fixed_len=self.fixed_len, per_sample_weights=w,
+                                 padding_idx=self.padding_idx)
+            capi.forward(p, stream)
+        send = self.send.view(self.per * self.world * max(1, tl), self.dim) if tl else \
+            self.send.view(-1, self.dim)[:0]
+        dist.all_to_all_single(self.recv, send, output_split_sizes=self.out_splits,
+                               input_split_sizes=self.in_splits if tl else [0] * self.world,
+                               group=self.group)
+        pos = 0
+        for src in range(self.world):
+            ts = self.by_src[src]
+            if not ts:
+                continue
+            block = self.recv[pos:pos + self.per * len(ts)].view(self.per, len(ts), self.dim)
+            self.result[:, ts, :] = block
+            pos += self.per * len(ts)
+        return self.result
+
+    def check_status(self) -> int:
+        return int(self.status.item()) if self.exchange == "push" else 0
+
+    def close(self):
+        if self.exchange == "push":
+            self.buffers.close()

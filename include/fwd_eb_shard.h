@@ -1,0 +1,108 @@
+/*
+ * fwd_eb_shard.h — row-sharded EmbeddingBag: pool the rows this GPU owns and hand
+ * the partial bags to their owners over NVLink, in the same kernel (C ABI).
+ *
+ * The reference has no multi-GPU code; its only hook is the plugin's row window
+ * (`data_offset_` / `count_`, "reserved for a possible multi-machine search",
+ * source/trt_engine/trt_network_crt/plugins/embedding_bag_plugin/
+ * embedding_bag_plugin.h:121-124, honoured at embedding_bag_plugin.cu:94).  This
+ * header extends that seam: G ranks each hold a row window of one logical table,
+ * every rank scans the whole batch, and bag b's pooled value is the sum of the G
+ * partial bags.
+ *
+ * Exchange layout.  Bags are owned in contiguous runs of `bags_per_rank`: rank o
+ * owns bags [o*bags_per_rank, (o+1)*bags_per_rank).  Each rank exposes a receive
+ * buffer of 2 x G x bags_per_rank x dim elements (two halves used alternately by
+ * call parity, one slot per source rank) and G flag words, all mapped into every
+ * peer (CUDA IPC below, or any other peer mapping).  fwd_eb_shard_push pools, and
+ * writes bag b's partial row straight into slot [parity][rank] of b's owner with
+ * plain peer stores; its last CTA publishes `epoch` in every peer's flag word.
+ * fwd_eb_shard_combine waits (bounded) until all G flags have reached `epoch`,
+ * then folds the G slots in rank order — a fixed order, so results do not depend
+ * on timing.  No multicast loads, no library kernels on peer memory.
+ *
+ * Every wait is bounded: after `max_spins` polls the waiting kernel writes
+ * FWD_EB_SHARD_TIMEOUT to `status` and returns without touching the output.
+ */
+#ifndef FWD_EB_SHARD_H_
+#define FWD_EB_SHARD_H_
+
+#include "fwd_eb.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FWD_EB_MAX_PEERS 16
+#define FWD_EB_SHARD_TIMEOUT 1
+#define FWD_EB_IPC_HANDLE_BYTES 64
+
+/* Receive-buffer layouts (fwd_eb_shard_exchange.layout). */
+enum {
+  /* Row shards of one table: [2 halves][G source ranks][bags_per_rank][dim];
+   * the owner folds the G slots with fwd_eb_shard_combine. */
+  FWD_EB_LAYOUT_ROW_SHARD = 0,
+  /* Whole tables placed on different ranks: [2 halves][bags_per_rank][num_tables][dim];
+   * the rank holding table t pools the whole batch and writes column block
+   * `table_index` of every owner's buffer.  Nothing is folded: after
+   * fwd_eb_shard_wait the buffer half IS the result (the all-to-all of pooled
+   * outputs, done by the pooling kernels' own stores). */
+  FWD_EB_LAYOUT_TABLE_WISE = 1
+};
+
+typedef struct fwd_eb_shard_exchange {
+  int32_t world;              /* G, 1..FWD_EB_MAX_PEERS */
+  int32_t rank;
+  int64_t bags_per_rank;      /* owner of bag b is b / bags_per_rank */
+  int32_t wire_dtype;         /* FWD_EB_F32, or FWD_EB_F16 to halve the NVLink bytes */
+  uint32_t epoch;             /* call number, starting at 1; parity picks the buffer half */
+  void* peer_slots[FWD_EB_MAX_PEERS];      /* rank r's receive buffer as mapped here */
+  uint32_t* peer_flags[FWD_EB_MAX_PEERS];  /* rank r's G flag words as mapped here */
+  uint32_t* counter;          /* one zeroed device word of this rank (CTA countdown) */
+  int32_t* status;            /* one device word of this rank; 0 = fine */
+  int64_t max_spins;          /* bound of the flag wait; 0 = default (about a second) */
+  int32_t layout;             /* FWD_EB_LAYOUT_* */
+  int32_t num_tables;         /* TABLE_WISE: tables in the whole model */
+  int32_t table_index;        /* TABLE_WISE: which of them this call pools */
+  int32_t hold_signal;        /* 1: do not raise the flags after this call (more tables follow) */
+} fwd_eb_shard_exchange;
+
+/* Bytes of one rank's receive buffer: row-shard layout for `world` sources, or, with
+ * num_tables > 0, table-wise layout. */
+size_t fwd_eb_shard_slots_bytes(int32_t world, int64_t bags_per_rank, int32_t dim,
+                                int32_t wire_dtype);
+size_t fwd_eb_shard_tablewise_bytes(int64_t bags_per_rank, int32_t num_tables, int32_t dim,
+                                    int32_t wire_dtype);
+
+/* Pool the local row window of `p` (modes SUM or MEAN, optional weights) and push
+ * each bag's partial row to its owner; `p->out` is ignored.  MEAN partials are
+ * already divided by the bag's full count, so the owner only adds. */
+int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream);
+
+/* Wait for all peers' flags, then out[b, :] = sum over r of slot[r][b, :] for the
+ * `num_bags` bags this rank owns. */
+int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                         void* d_out, int32_t out_dtype, void* stream);
+
+/* TABLE_WISE: wait (bounded) until every rank has raised `epoch`; on success
+ * *d_result (if not NULL) receives the address of this call's buffer half, laid out
+ * [num_bags owned][num_tables][dim]. */
+int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_result, void* stream);
+
+/* Publish `epoch` to every peer without pooling (used to keep epochs in step when a
+ * rank has nothing to send, and by tests). */
+int fwd_eb_shard_signal(const fwd_eb_shard_exchange* x, void* stream);
+
+/* ---- peer mapping through CUDA IPC (one process per GPU on one node) ---------- */
+
+/* cudaMalloc + zero-fill `bytes` and produce the 64-byte handle peers open. */
+int fwd_eb_ipc_alloc(size_t bytes, void** d_ptr, unsigned char handle[FWD_EB_IPC_HANDLE_BYTES]);
+/* Map a peer's allocation into this process (peer access enabled lazily). */
+int fwd_eb_ipc_open(const unsigned char handle[FWD_EB_IPC_HANDLE_BYTES], void** d_peer_ptr);
+int fwd_eb_ipc_close(void* d_peer_ptr);
+int fwd_eb_ipc_free(void* d_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FWD_EB_SHARD_H_ */

@@ -1,0 +1,98 @@
+"""Row shards and table-wise placement across real GPUs (one process per GPU, NCCL for the
+rendezvous and the plain variants, peer stores for the fused ones).  Skipped on a single GPU."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    import torch.distributed as dist
+
+    from forward_b200 import capi, workloads
+    from forward_b200 import dist as fd
+    from oracle import eb_oracle as O
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    failures = []
+    rng = np.random.default_rng(13)
+    rows, dim, nb = 40_000, 128, 4096
+    table = rng.standard_normal((rows, dim)).astype(np.float16)
+    lo, n = fd.shard_rows(rows, world, rank)
+    local = torch.from_numpy(table[lo:lo + n]).to(dev)
+    shards = [fd.shard_rows(rows, world, r) for r in range(world)]
+    for exchange, wire in (("push", capi.F32), ("push", capi.F16), ("a2a", capi.F32), ("nccl", capi.F32)):
+        for mode in (capi.MODE_SUM, capi.MODE_MEAN):
+            bag = fd.RowShardedBag(local, lo, mode=mode, max_bags=nb, exchange=exchange,
+                                   wire_dtype=wire, padding_idx=3)
+            for step in range(3):
+                brng = np.random.default_rng(100 + step)
+                bags = workloads.ragged_bags(rows, brng.integers(0, 80, nb), brng)
+                bags.indices[::11] = 3
+                got = bag.forward(torch.from_numpy(bags.indices).to(dev),
+                                  torch.from_numpy(bags.offsets).to(dev))
+                torch.cuda.synchronize()
+                parts = np.stack([O.pool(table[a:a + c], bags.indices, bags.offsets, mode=mode,
+                                         padding_idx=3, row_lo=a, out_dtype=np.float32)
+                                  for a, c in shards])
+                if wire == capi.F16:
+                    parts = parts.astype(np.float16)
+                expect = O.combine_partials(parts, np.float32)
+                blo, mine = fd.owned_bags(nb, world, rank)
+                g = got.cpu().numpy()
+                if exchange == "nccl":
+                    ok = np.allclose(g, expect[blo:blo + mine], rtol=1e-5, atol=1e-5)
+                else:
+                    ok = np.array_equal(g, expect[blo:blo + mine])
+                if not ok or bag.check_status() != 0:
+                    failures.append(f"rowshard {exchange} wire{wire} mode{mode} step{step}")
+            dist.barrier()
+            bag.close()
+    # table-wise: 5 tables over the ranks, fixed pooling factor, weights
+    ntab, L, dim2, nb2 = 5, 8, 64, 1024
+    owner = fd.place_tables([1] * ntab, world)
+    trng = np.random.default_rng(17)
+    tables = [trng.standard_normal((3000 + 100 * t, dim2)).astype(np.float32) for t in range(ntab)]
+    for exchange in ("push", "nccl"):
+        mine_t = [t for t in range(ntab) if owner[t] == rank]
+        tw = fd.TableWiseBags({t: torch.from_numpy(tables[t]).to(dev) for t in mine_t}, owner,
+                              dim=dim2, max_bags=nb2, exchange=exchange, fixed_len=L)
+        for step in range(2):
+            irng = np.random.default_rng(200 + step)
+            idx = [irng.integers(0, tables[t].shape[0], (nb2, L)).astype(np.int32) for t in range(ntab)]
+            w = [irng.random(nb2 * L).astype(np.float32) for _ in range(ntab)]
+            inputs = {t: (torch.from_numpy(idx[t]).to(dev), None, torch.from_numpy(w[t]).to(dev))
+                      for t in mine_t}
+            res = tw.forward(inputs)
+            torch.cuda.synchronize()
+            expect = np.stack([O.pool(tables[t], idx[t], fixed_len=L, per_sample_weights=w[t])
+                               for t in range(ntab)], axis=1)
+            per = fd.bags_per_rank(nb2, world)
+            if not np.array_equal(res.cpu().numpy(), expect[rank * per:(rank + 1) * per]) or \
+                    tw.check_status() != 0:
+                failures.append(f"tablewise {exchange} step{step}")
+        dist.barrier()
+        tw.close()
+    with open(os.path.join(tmp, f"rank{rank}.txt"), "w") as f:
+        f.write("\n".join(failures))
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_row_shards_and_table_wise_across_gpus(tmp_path):
+    import torch.multiprocessing as mp
+    world = min(4, torch.cuda.device_count())
+    port = 29800 + os.getpid() % 100
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        text = (tmp_path / f"rank{r}.txt").read_text()
+        assert text == "", f"rank {r}: {text}"

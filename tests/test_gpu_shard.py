@@ -1,0 +1,140 @@
+"""The fused pool-and-push kernels on ONE GPU: every "rank" is a set of buffers on the same
+device and the ranks' launches run one after another on one stream, so no kernel ever waits
+for another (all flags are already raised when a wait starts).  Real multi-GPU runs are in
+test_gpu_multi.py."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from forward_b200 import capi, workloads  # noqa: E402
+from forward_b200 import dist as fd  # noqa: E402
+from oracle import eb_oracle as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _cuda(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def _setup(world, per, dim, wire, layout=fd.LAYOUT_ROW_SHARD, num_tables=0, max_spins=0):
+    lib = fd._lib()
+    nbytes = (lib.fwd_eb_shard_tablewise_bytes(per, num_tables, dim, wire) if num_tables else
+              lib.fwd_eb_shard_slots_bytes(world, per, dim, wire))
+    bufs = fd.PeerBuffers(nbytes, world, 0, local_world=world)
+    xs, keep = [], []
+    for r in range(world):
+        counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        keep += [counter, status]
+        xs.append(fd.make_exchange(bufs, r, per, wire, counter, status, layout=layout,
+                                   num_tables=num_tables, max_spins=max_spins))
+    return lib, bufs, xs, keep
+
+
+@pytest.mark.parametrize("wire", [capi.F32, capi.F16])
+@pytest.mark.parametrize("mode", [capi.MODE_SUM, capi.MODE_MEAN])
+def test_row_shard_push_and_combine_four_ranks(wire, mode):
+    rng = np.random.default_rng(8)
+    world, rows, dim, nb = 4, 8000, 64, 1000          # 1000 bags: the last rank owns fewer
+    table = rng.standard_normal((rows, dim)).astype(np.float16)
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, wire)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    shards = [fd.shard_rows(rows, world, r) for r in range(world)]
+    tabs = [_cuda(table[lo:lo + n]) for lo, n in shards]
+    for epoch in (1, 2, 3):                            # both buffer halves, fresh inputs each call
+        bags = workloads.ragged_bags(rows, rng.integers(0, 60, nb), rng)
+        bags.indices[::7] = 5
+        i, o = _cuda(bags.indices), _cuda(bags.offsets)
+        for r in range(world):
+            xs[r].epoch = epoch
+            p = capi.make_params(tabs[r], i, o, out=tabs[r][:1], mode=mode, padding_idx=5,
+                                 row_lo=shards[r][0])
+            capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+        parts = np.stack([O.pool(table[lo:lo + n], bags.indices, bags.offsets, mode=mode,
+                                 padding_idx=5, row_lo=lo, out_dtype=np.float32)
+                          for lo, n in shards])
+        if wire == capi.F16:
+            parts = parts.astype(np.float16)
+        expect = O.combine_partials(parts, np.float32)
+        for r in range(world):
+            lo, mine = fd.owned_bags(nb, world, r)
+            out = torch.full((per, dim), float("nan"), device=DEV)
+            capi.check(lib.fwd_eb_shard_combine(C.byref(xs[r]), dim, mine, out.data_ptr(), capi.F32,
+                                                stream))
+            torch.cuda.synchronize()
+            assert np.array_equal(out[:mine].cpu().numpy(), expect[lo:lo + mine])
+            assert torch.isnan(out[mine:]).all()
+    assert all(int(k.item()) == 0 for k in keep)       # counters back to zero, no timeouts
+    whole = O.pool(table, bags.indices, bags.offsets, mode=mode, padding_idx=5, out_dtype=np.float32)
+    np.testing.assert_allclose(expect, whole, rtol=1e-3, atol=2e-2 if wire == capi.F16 else 1e-4)
+
+
+def test_table_wise_push_lands_in_result_layout():
+    rng = np.random.default_rng(9)
+    world, ntab, dim, nb, L = 2, 5, 32, 96, 4
+    owner = fd.place_tables([1] * ntab, world)
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, capi.F32, layout=fd.LAYOUT_TABLE_WISE,
+                                 num_tables=ntab)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    tables = [rng.standard_normal((200 + 10 * t, dim)).astype(np.float32) for t in range(ntab)]
+    idx = [rng.integers(0, tables[t].shape[0], (nb, L)).astype(np.int32) for t in range(ntab)]
+    w = [rng.random(nb * L).astype(np.float32) for _ in range(ntab)]
+    keepalive = []
+    for r in range(world):
+        mine = [t for t in range(ntab) if owner[t] == r]
+        xs[r].epoch = 1
+        for k, t in enumerate(mine):
+            tt, ii, ww = _cuda(tables[t]), _cuda(idx[t]), _cuda(w[t])
+            keepalive += [tt, ii, ww]
+            p = capi.make_params(tt, ii, None, out=tt[:1], mode=capi.MODE_SUM, fixed_len=L,
+                                 per_sample_weights=ww)
+            xs[r].table_index = t
+            xs[r].hold_signal = 0 if k == len(mine) - 1 else 1
+            capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+    expect = np.stack([O.pool(tables[t], idx[t], mode=O.MODE_SUM, fixed_len=L, per_sample_weights=w[t])
+                       for t in range(ntab)], axis=1)                      # [nb, T, dim]
+    for r in range(world):
+        res = C.c_void_p()
+        capi.check(lib.fwd_eb_shard_wait(C.byref(xs[r]), dim, C.byref(res), stream))
+        torch.cuda.synchronize()
+        got = torch.as_tensor(fd._DeviceView(res.value, (per, ntab, dim), "<f4"), device="cuda")
+        assert np.array_equal(got.cpu().numpy(), expect[r * per:(r + 1) * per])
+    assert all(int(k.item()) == 0 for k in keep)
+
+
+def test_wait_gives_up_and_reports_instead_of_hanging():
+    """Nothing raises rank 1's flag: the bounded wait runs out after a few thousand polls, sets
+    the status word and leaves the output alone; the context stays usable."""
+    world, per, dim = 2, 8, 16
+    lib, bufs, xs, keep = _setup(world, per, dim, capi.F32, max_spins=2000)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    xs[0].epoch = 1
+    capi.check(lib.fwd_eb_shard_signal(C.byref(xs[0]), stream))   # rank 0 signals, rank 1 never does
+    out = torch.full((per, dim), 7.0, device=DEV)
+    capi.check(lib.fwd_eb_shard_combine(C.byref(xs[0]), dim, per, out.data_ptr(), capi.F32, stream))
+    torch.cuda.synchronize()
+    status0 = keep[1]
+    assert int(status0.item()) == fd.SHARD_TIMEOUT
+    assert torch.all(out == 7.0)
+    assert float((out + 1).sum().item()) == per * dim * 8.0       # device still answers
+
+
+def test_argument_errors():
+    lib, bufs, xs, keep = _setup(2, 8, 16, capi.F32)
+    t = torch.zeros((4, 16), device=DEV)
+    i = torch.zeros(4, dtype=torch.int32, device=DEV)
+    p = capi.make_params(t, i, i, out=t, mode=capi.MODE_MAX)
+    xs[0].epoch = 1
+    assert lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[0]), None) == capi.EUNSUPPORTED
+    p.mode = capi.MODE_SUM
+    xs[0].epoch = 0
+    assert lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[0]), None) == capi.EINVAL
+    xs[0].epoch, xs[0].world = 1, 99
+    assert lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[0]), None) == capi.EINVAL
