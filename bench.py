@@ -214,8 +214,8 @@ def workload_config(world: int):
                 "l2_policy": "no flush: 256 MB table (> 126 MB L2) and 8 rotating index batches",
                 "parallelism": "single"}
     return {"workload": f"rowshard: c2 shape grown x{world}: table {world}x1000000x128 fp16 split "
-                        f"by rows, {world}x16384 bags/step scanned by every rank, fp32 partial "
-                        "bags combined by reduce-scatter",
+                        f"by rows, {world}x16384 bags/step scanned by every rank, partial bags "
+                        "pushed to their owner ranks over NVLink and folded there",
             "bags_per_step": C2["bags"] * world, "table_rows": C2["rows"] * world,
             "dim": C2["dim"],
             "l2_policy": "no flush: 256 MB table shard per GPU (> 126 MB L2), 8 rotating batches",
@@ -228,12 +228,14 @@ def run_ours(args, world: int, rank: int, local_rank: int):
     import torch
 
     from forward_b200 import capi
+    from forward_b200 import dist as fd
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the package has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
-    if world > 1:
+    sharded = world > 1
+    if sharded:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
@@ -249,65 +251,103 @@ def run_ours(args, world: int, rank: int, local_rank: int):
     lookups_global = [b.num_indices for b in batches]
     gathered_local = [int(np.count_nonzero((b.indices >= row_lo) & (b.indices < row_lo + rows_local)))
                       for b in batches]
-
-    sharded = world > 1
-    out_dtype = torch.float32 if sharded else torch.float16
-    out = torch.empty((total_bags, dim), dtype=out_dtype, device=dev)
-    params = [capi.make_params(table, i, o, out=out, mode=capi.MODE_MEAN, row_lo=row_lo)
-              for i, o in d_batches]
-    shard_out = torch.empty((total_bags // world, dim), dtype=torch.float32, device=dev) if sharded else None
     stream = torch.cuda.current_stream()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps)]
 
-    def step(k: int):
-        capi.forward(params[k % NUM_BATCHES], stream.cuda_stream)
-        if sharded:
-            dist.reduce_scatter_tensor(shard_out, out)
+    if sharded:
+        wire = capi.F16 if args.wire == "f16" else capi.F32
+        bag = fd.RowShardedBag(table, row_lo, mode=capi.MODE_MEAN, max_bags=total_bags,
+                               exchange=args.exchange, wire_dtype=wire)
+        local_out = torch.empty((total_bags, dim), dtype=torch.float32, device=dev)
+        local_params = [capi.make_params(table, i, o, out=local_out, mode=capi.MODE_MEAN, row_lo=row_lo)
+                        for i, o in d_batches]
+
+        def step(k: int, timed: bool = False):
+            i, o = d_batches[k % NUM_BATCHES]
+            bag.forward(i, o, pool_events=(ev[2 * k], ev[2 * k + 1]) if timed else None)
+    else:
+        out = torch.empty((total_bags, dim), dtype=torch.float16, device=dev)
+        params = [capi.make_params(table, i, o, out=out, mode=capi.MODE_MEAN) for i, o in d_batches]
+
+        def step(k: int, timed: bool = False):
+            if timed:
+                ev[2 * k].record()
+            capi.forward(params[k % NUM_BATCHES], stream.cuda_stream)
+            if timed:
+                ev[2 * k + 1].record()
 
     def barrier():
         if sharded:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # bring clocks up before the counted warm-up
-    t_end = time.perf_counter() + args.preheat_ms * 1e-3
-    k = 0
-    while time.perf_counter() < t_end:
-        step(k)
-        k += 1
-        if k % 64 == 0:
-            torch.cuda.synchronize()
+    # bring clocks up before the counted warm-up; a fixed count when ranks must stay in step
+    if sharded:
+        for k in range(int(args.preheat_ms * 5)):      # ~80 us a step: about the same duration
+            step(k)
+            if k % 64 == 63:
+                torch.cuda.synchronize()
+    else:
+        t_end = time.perf_counter() + args.preheat_ms * 1e-3
+        k = 0
+        while time.perf_counter() < t_end:
+            step(k)
+            k += 1
+            if k % 64 == 0:
+                torch.cuda.synchronize()
+    pool_only_us = None
+    if sharded:
+        # the same pooling without any exchange, for the overhead figure
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for k in range(20):
+            capi.forward(local_params[k % NUM_BATCHES], stream.cuda_stream)
+        n_po = max(20, min(args.steps, 200))
+        a.record()
+        for k in range(n_po):
+            capi.forward(local_params[k % NUM_BATCHES], stream.cuda_stream)
+        b.record()
+        torch.cuda.synchronize()
+        pool_only_us = a.elapsed_time(b) * 1e3 / n_po
     for k in range(args.warmup):
         step(k)
     barrier()
 
     sampler = ClockSampler(local_rank)
     launches0 = capi.lib().fwd_eb_launch_count()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps)]
     t_begin, t_finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler.start()
     t_begin.record()
     for k in range(args.steps):
-        ev[2 * k].record()
-        capi.forward(params[k % NUM_BATCHES], stream.cuda_stream)
-        ev[2 * k + 1].record()
-        if sharded:
-            dist.reduce_scatter_tensor(shard_out, out)
+        step(k, timed=True)
     t_finish.record()
     barrier()
     clocks = sampler.stop()
     launches = capi.lib().fwd_eb_launch_count() - launches0
     total_ms = t_begin.elapsed_time(t_finish)
     kernel_ms = np.array([ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps)])
+    exchange = None
     if sharded:
-        tt = torch.tensor([total_ms], dtype=torch.float64, device=dev)
+        if bag.check_status() != 0:
+            raise RuntimeError("a bounded flag wait gave up during the timed region")
+        tt = torch.tensor([total_ms, pool_only_us], dtype=torch.float64, device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        total_ms = float(tt.item())
+        total_ms, pool_only_us = float(tt[0].item()), float(tt[1].item())
+        step_us = total_ms * 1e3 / args.steps
+        wire_bytes = 2 if (args.exchange == "push" and args.wire == "f16") else 4
+        egress = C2["bags"] * (world - 1) * dim * wire_bytes      # per rank per step
+        exchange = {"method": args.exchange, "wire": args.wire if args.exchange == "push" else "f32",
+                    "pool_only_us": pool_only_us, "step_us": step_us,
+                    "overhead_frac": (step_us - pool_only_us) / pool_only_us,
+                    "nvlink_egress_bytes_per_rank": egress,
+                    "nvlink_floor_us_at_770GBs": egress / 770e9 * 1e6}
     lookups = sum(lookups_global[k % NUM_BATCHES] for k in range(args.steps))
     value = lookups / (total_ms * 1e-3)
 
     # roofline of the pooling kernel on this rank
+    out_item = (2 if (sharded and args.exchange == "push" and args.wire == "f16") else 4) if sharded else 2
     alg = np.mean([algorithmic_bytes(batches[k % NUM_BATCHES], dim, gathered_local[k % NUM_BATCHES],
-                                     4 if sharded else 2) for k in range(args.steps)])
+                                     out_item) for k in range(args.steps)])
     peak, peak_kind = measured_peak()
     achieved = alg / (kernel_ms.mean() * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -319,17 +359,15 @@ def run_ours(args, world: int, rank: int, local_rank: int):
 
     e2e = None
     cpu = None
-    if not sharded and not args.no_e2e:
-        e2e = run_e2e(args, batches, table)
+    if not args.no_e2e:
+        e2e = run_e2e_sharded(args, batches, bag, rank, world, dev) if sharded else \
+            run_e2e(args, batches, table)
     if rank == 0 and not sharded and not args.no_cpu_baseline:
         tab = host_table(rows_local, dim)
         rate, cores, reps, secs = cpu_embedding_bag_rate(tab, batches, budget_s=args.cpu_seconds)
         cpu = {"value": rate, "unit": "lookups/s", "cores": cores, "kind": "port",
                "sample": f"torch CPU EmbeddingBag (mean, fp16 table) on whole c2 batches: {reps} "
                          f"calls, {secs:.1f} s"}
-    if sharded:
-        e2e = {"value": None, "unit": "lookups/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
-               "note": "host-buffer path is measured at N=1"}
 
     if rank == 0:
         line = {
@@ -340,9 +378,50 @@ def run_ours(args, world: int, rank: int, local_rank: int):
             "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         }
+        if exchange:
+            line["exchange"] = exchange
         print(json.dumps(line), flush=True)
     if sharded:
+        bag.close()
         dist.destroy_process_group()
+
+
+def run_e2e_sharded(args, batches, bag, rank, world, dev):
+    """N > 1: every step copies the whole batch from pinned host memory to this rank's GPU, runs
+    the sharded call and copies this rank's slice of the result back to pinned memory."""
+    import torch
+    import torch.distributed as dist
+    host = [(torch.from_numpy(b.indices).pin_memory(), torch.from_numpy(b.offsets).pin_memory())
+            for b in batches]
+    d_idx = [torch.empty_like(i, device=dev) for i, _ in host]
+    d_off = [torch.empty_like(o, device=dev) for _, o in host]
+    per = C2["bags"]
+    h_out = [torch.empty((per, C2["dim"]), dtype=torch.float32).pin_memory() for _ in range(NUM_BATCHES)]
+
+    def step(k):
+        j = k % NUM_BATCHES
+        d_idx[j].copy_(host[j][0], non_blocking=True)
+        d_off[j].copy_(host[j][1], non_blocking=True)
+        res = bag.forward(d_idx[j], d_off[j])
+        h_out[j][:res.shape[0]].copy_(res, non_blocking=True)
+
+    for k in range(max(args.warmup, 3)):
+        step(k)
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for k in range(args.steps):
+        step(k)
+    torch.cuda.synchronize()
+    dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+    dt = float(dt.item())
+    lookups = sum(batches[k % NUM_BATCHES].num_indices for k in range(args.steps))
+    h2d = int(np.mean([b.num_indices * 4 + b.num_bags * 4 for b in batches]))
+    return {"value": lookups / dt, "unit": "lookups/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": per * C2["dim"] * 4, "ms_per_step": dt / args.steps * 1e3,
+            "note": "bytes are per rank; every rank receives the whole batch",
+            "api": "forward_b200.dist.RowShardedBag.forward"}
 
 
 def run_e2e(args, batches, table):
@@ -398,6 +477,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--exchange", default="push", choices=["push", "a2a", "nccl"],
+                    help="N>1: how partial bags reach their owners")
+    ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
+                    help="N>1 with --exchange push: element type of the partials on NVLink")
     ap.add_argument("--preheat-ms", type=float, default=400.0,
                     help="untimed launches before the counted warm-up, to bring clocks up")
     args = ap.parse_args()

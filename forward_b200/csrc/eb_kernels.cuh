@@ -331,15 +331,32 @@ __device__ __forceinline__ float finish(const PoolArgs& a, float acc, int counte
 }
 
 // Write this lane's chunks of one output row.
-template <int VE, int CPL>
+//
+// With EXCHANGE (pooling kernels) the call must be made by all 32 lanes of the warp — lanes
+// with nothing to write pass live = false — because 32-byte-per-lane fp32 rows are written
+// through a neighbour swap: a lane holds 8 floats = 32 B, and storing them as two 16-byte
+// halves would have every lane touch half a sector twice.  Neighbouring lanes swap one quad
+// so each store instruction writes whole 32-byte sectors (even lane: its quad 0, then the odd
+// lane's quad 0; odd lane: the even lane's quad 1, then its own quad 1).  This matters most
+// for stores that cross NVLink.
+template <int VE, int CPL, bool EXCHANGE>
 __device__ __forceinline__ void store_row(const PoolArgs& a, char* out_base, long long out_row,
-                                          int chunk0, const float (&v)[CPL][VE]) {
+                                          int chunk0, const float (&v)[CPL][VE], bool live) {
   const int lanes = 1 << a.lanes_log2;
   const int lig = (threadIdx.x & 31u) & (lanes - 1);
 #pragma unroll
   for (int c = 0; c < CPL; ++c) {
-    int chunk = chunk0 + c * lanes + lig;
-    if (chunk >= a.nchunks) continue;
+    const int chunk = chunk0 + c * lanes + lig;
+    const bool swap = EXCHANGE && VE == 8 && !a.out_f16 && a.out_vec && lanes >= 2;
+    float x4[4];
+    if (swap) {  // warp-uniform condition: every lane takes part in the shuffles
+      const bool odd = lig & 1;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        x4[e] = __shfl_xor_sync(kFull, odd ? v[c][e < VE ? e : 0] : v[c][4 + e < VE ? 4 + e : 0], 1);
+      }
+    }
+    if (!live || chunk >= a.nchunks) continue;
     long long col = (long long)chunk * VE;
     if (a.out_f16) {
       __half* o = reinterpret_cast<__half*>(out_base) + out_row * a.out_stride + col;
@@ -347,13 +364,13 @@ __device__ __forceinline__ void store_row(const PoolArgs& a, char* out_base, lon
         uint4 pk;
         __half2* h = reinterpret_cast<__half2*>(&pk);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[c][2 * e], v[c][2 * e + 1]);
+        for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(v[c][(2 * e) % VE], v[c][(2 * e + 1) % VE]);
         *reinterpret_cast<uint4*>(o) = pk;
       } else if (VE == 4 && a.out_vec) {
         uint2 pk;
         __half2* h = reinterpret_cast<__half2*>(&pk);
-        h[0] = __floats2half2_rn(v[c][0], v[c][1]);
-        h[1] = __floats2half2_rn(v[c][2], v[c][3]);
+        h[0] = __floats2half2_rn(v[c][0], v[c][1 % VE]);
+        h[1] = __floats2half2_rn(v[c][2 % VE], v[c][3 % VE]);
         *reinterpret_cast<uint2*>(o) = pk;
       } else {
 #pragma unroll
@@ -361,11 +378,22 @@ __device__ __forceinline__ void store_row(const PoolArgs& a, char* out_base, lon
       }
     } else {
       float* o = reinterpret_cast<float*>(out_base) + out_row * a.out_stride + col;
-      if (VE >= 4 && a.out_vec) {
+      if (swap && ((chunk | 1) < a.nchunks)) {
+        const bool odd = lig & 1;
+        float* pair = o - (odd ? 8 : 0);  // first float of the lane pair's 16
+        if (!odd) {
+          *reinterpret_cast<float4*>(pair) = make_float4(v[c][0], v[c][1 % VE], v[c][2 % VE], v[c][3 % VE]);
+          *reinterpret_cast<float4*>(pair + 8) = make_float4(x4[0], x4[1], x4[2], x4[3]);
+        } else {
+          *reinterpret_cast<float4*>(pair + 4) = make_float4(x4[0], x4[1], x4[2], x4[3]);
+          *reinterpret_cast<float4*>(pair + 12) =
+              make_float4(v[c][4 % VE], v[c][5 % VE], v[c][6 % VE], v[c][7 % VE]);
+        }
+      } else if (VE >= 4 && a.out_vec) {
 #pragma unroll
         for (int e = 0; e < VE; e += 4) {
-          *reinterpret_cast<float4*>(o + e) =
-              make_float4(v[c][e], v[c][e + 1], v[c][e + 2], v[c][e + 3]);
+          *reinterpret_cast<float4*>(o + e) = make_float4(v[c][e], v[c][(e + 1) % VE],
+                                                          v[c][(e + 2) % VE], v[c][(e + 3) % VE]);
         }
       } else {
 #pragma unroll
@@ -403,14 +431,12 @@ eb_pool_group_kernel(const PoolArgs a) {
   clear(s);
   pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
 
-  if (live) {
-    const bool tf16 = sizeof(TW) == 2;
+  const bool tf16 = sizeof(TW) == 2;
 #pragma unroll
-    for (int c = 0; c < CPL; ++c)
+  for (int c = 0; c < CPL; ++c)
 #pragma unroll
-      for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
-    store_row<VE, CPL>(a, a.out, bag, chunk0, s.v);
-  }
+    for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
+  store_row<VE, CPL, true>(a, a.out, bag, chunk0, s.v, live);
 }
 
 // ---- strategies 2 and 3: a CTA (or `splits` CTAs) per bag --------------------
@@ -562,7 +588,7 @@ eb_gather_kernel(const PoolArgs a, int keep_skipped) {
       for (int e = 0; e < VE; ++e) f[0][e] = 0.0f;
     }
     // store_row addresses chunk0 + lig; hand it the chunk minus this lane's slot
-    store_row<VE, 1>(a, a.out, t, chunk - lig, f);
+    store_row<VE, 1, false>(a, a.out, t, chunk - lig, f, true);
   }
 }
 

@@ -4,7 +4,10 @@
 // epilogue: instead of a local output row, the lane group stores its partial row into the
 // owner rank's receive slot through a peer-mapped pointer, so the NVLink transfer of early
 // bags overlaps the HBM gathers of later ones and the partial never makes a round trip
-// through local memory.  The last CTA to finish raises this rank's flag on every peer.
+// through local memory.  The kernel that follows on the same stream (the fold, or the bare wait
+// of the table-wise layout) starts by raising this rank's flag on every peer — by then the
+// pooling grid has completed, so all of its peer stores have been performed — and then waits,
+// with a bound, for the peers' flags.
 #include <climits>
 #include <cstring>
 
@@ -17,13 +20,11 @@ namespace fwd_eb {
 struct PushArgs {
   char* peer_slots[FWD_EB_MAX_PEERS];  // already offset to this call's buffer half
   uint32_t* peer_flags[FWD_EB_MAX_PEERS];
-  uint32_t* counter;
   long long bags_per_rank;
   long long row_base;    // destination row of this rank's first bag inside the owner's buffer
   long long col_offset;  // destination column of this call's first column
   int world;
   int rank;
-  int signal;            // raise the flags when the grid is done
   uint32_t epoch;
 };
 
@@ -36,21 +37,17 @@ __device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
   return v;
 }
 
-// The CTA that finishes last tells every peer that this rank's partials have landed.
-__device__ __forceinline__ void signal_when_last(const PushArgs& x) {
-  if (!x.signal) return;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence_system();  // this CTA's peer stores before the count
-    const unsigned total = gridDim.x * gridDim.y;
-    const unsigned done = atomicAdd(x.counter, 1u);
-    if (done == total - 1) {
-      *x.counter = 0;  // ready for the next call
-      __threadfence_system();
-      for (int r = 0; r < x.world; ++r) store_release_sys(x.peer_flags[r] + x.rank, x.epoch);
-    }
-  }
+// Raise this rank's flag on every peer (one thread).  Callers run it at the start of a kernel
+// that follows the pooling grid on the same stream.
+__device__ __forceinline__ void raise_flags(uint32_t* const* peer_flags, int world, int rank,
+                                            uint32_t epoch) {
+  __threadfence_system();
+  for (int r = 0; r < world; ++r) store_release_sys(peer_flags[r] + rank, epoch);
 }
+
+struct FlagSet {
+  uint32_t* peer_flags[FWD_EB_MAX_PEERS];
+};
 
 template <typename TW, int VE, int CPL, int OP, int U>
 __global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
@@ -66,32 +63,28 @@ eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
   clear(s);
   pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
 
-  if (live) {
-    const bool tf16 = sizeof(TW) == 2;
+  const bool tf16 = sizeof(TW) == 2;
 #pragma unroll
-    for (int c = 0; c < CPL; ++c)
+  for (int c = 0; c < CPL; ++c)
 #pragma unroll
-      for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
-    long long owner = bag / x.bags_per_rank;
-    if (owner >= x.world) owner = x.world - 1;
-    const long long local_bag = bag - owner * x.bags_per_rank;
-    // this rank's slot (row shards) or this table's column block (table-wise) at the owner
-    char* base = x.peer_slots[owner] + x.col_offset * (a.out_f16 ? 2 : 4);
-    store_row<VE, CPL>(a, base, x.row_base + local_bag, chunk0, s.v);
-  }
-  signal_when_last(x);
+    for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
+  long long owner = live ? bag / x.bags_per_rank : 0;
+  if (owner >= x.world) owner = x.world - 1;
+  const long long local_bag = bag - owner * x.bags_per_rank;
+  // this rank's slot (row shards) or this table's column block (table-wise) at the owner
+  char* base = x.peer_slots[owner] + x.col_offset * (a.out_f16 ? 2 : 4);
+  store_row<VE, CPL, true>(a, base, x.row_base + local_bag, chunk0, s.v, live);
 }
 
-__global__ void eb_shard_signal_kernel(const PushArgs x) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    __threadfence_system();
-    for (int r = 0; r < x.world; ++r) store_release_sys(x.peer_flags[r] + x.rank, x.epoch);
-  }
+__global__ void eb_shard_signal_kernel(const FlagSet f, int world, int rank, uint32_t epoch) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) raise_flags(f.peer_flags, world, rank, epoch);
 }
 
 // Bounded wait for all flags; nothing else (table-wise layout needs no folding).
-__global__ void eb_shard_wait_kernel(const uint32_t* flags, int world, uint32_t epoch, int* status,
-                                     long long max_spins) {
+__global__ void eb_shard_wait_kernel(const FlagSet f, int rank, int world, uint32_t epoch,
+                                     int* status, long long max_spins) {
+  if (threadIdx.x == 0) raise_flags(f.peer_flags, world, rank, epoch);
+  const uint32_t* flags = f.peer_flags[rank];
   if (threadIdx.x < world) {
     long long spins = 0;
     while ((int)(load_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
@@ -107,11 +100,16 @@ __global__ void eb_shard_wait_kernel(const uint32_t* flags, int world, uint32_t 
 // Wait (bounded) for every source rank's flag, then fold the slots in rank order.
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kCtaThreads)
-eb_shard_combine_kernel(const TP* slots, const uint32_t* flags, int world, uint32_t epoch,
+eb_shard_combine_kernel(const TP* slots, const FlagSet f, int rank, int world, uint32_t epoch,
                         long long slot_stride, long long count, TO* out, int* status,
                         long long max_spins) {
   __shared__ int timed_out;
-  if (threadIdx.x == 0) timed_out = 0;
+  if (threadIdx.x == 0) {
+    timed_out = 0;
+    // The pooling grid that ran before this kernel on the stream has completed: publish.
+    if (blockIdx.x == 0) raise_flags(f.peer_flags, world, rank, epoch);
+  }
+  const uint32_t* flags = f.peer_flags[rank];
   __syncthreads();
   if (threadIdx.x < world) {
     long long spins = 0;
@@ -158,7 +156,7 @@ static int check_exchange(const fwd_eb_shard_exchange* x) {
   if (x->wire_dtype != FWD_EB_F32 && x->wire_dtype != FWD_EB_F16)
     return fail(FWD_EB_EINVAL, "unknown wire_dtype %d", x->wire_dtype);
   if (x->epoch == 0) return fail(FWD_EB_EINVAL, "epoch starts at 1");
-  if (!x->counter || !x->status) return fail(FWD_EB_EINVAL, "counter / status word is null");
+  if (!x->status) return fail(FWD_EB_EINVAL, "status word is null");
   for (int r = 0; r < x->world; ++r) {
     if (!x->peer_slots[r] || !x->peer_flags[r])
       return fail(FWD_EB_EINVAL, "peer %d has no mapped slots / flags", r);
@@ -183,8 +181,6 @@ static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
     out->peer_slots[r] = static_cast<char*>(x->peer_slots[r]) + half;
     out->peer_flags[r] = x->peer_flags[r];
   }
-  out->counter = x->counter;
-  out->signal = x->hold_signal ? 0 : 1;
   if (x->layout == FWD_EB_LAYOUT_TABLE_WISE) {
     out->row_base = 0;
     out->col_offset = (long long)x->table_index * dim;
@@ -198,12 +194,19 @@ static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
   out->epoch = x->epoch;
 }
 
+static FlagSet flag_set(const fwd_eb_shard_exchange* x) {
+  FlagSet f;
+  memset(&f, 0, sizeof(f));
+  for (int r = 0; r < x->world; ++r) f.peer_flags[r] = x->peer_flags[r];
+  return f;
+}
+
 template <typename TW, int VE, int CPL, int U>
 static cudaError_t launch_push(const PoolArgs& a, const PushArgs& x, int tiles, bool weighted,
                                cudaStream_t st) {
   const long long threads = a.num_bags << a.lanes_log2;
-  long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
-  if (blocks < 1) blocks = 1;  // the signal still has to go out
+  const long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+  if (blocks == 0) return cudaSuccess;
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)blocks, (unsigned)tiles);
   if (weighted) {
@@ -281,7 +284,7 @@ int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_resu
   if (dim <= 0) return fail(FWD_EB_EINVAL, "dim must be positive");
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
   eb_shard_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      x->peer_flags[x->rank], x->world, x->epoch, x->status, spins);
+      flag_set(x), x->rank, x->world, x->epoch, x->status, spins);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "wait kernel launch");
@@ -293,9 +296,8 @@ int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_resu
 int fwd_eb_shard_signal(const fwd_eb_shard_exchange* x, void* stream) {
   int rc = check_exchange(x);
   if (rc) return rc;
-  PushArgs px;
-  fill_push(x, 1, &px);
-  eb_shard_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(px);
+  eb_shard_signal_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(flag_set(x), x->world,
+                                                                          x->rank, x->epoch);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "signal kernel launch");
@@ -313,7 +315,7 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
   const long long count = (long long)num_bags * dim;
   const long long slot_stride = (long long)x->bags_per_rank * dim;
   const char* slots = static_cast<const char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch & 1u);
-  const uint32_t* flags = x->peer_flags[x->rank];
+  const FlagSet flags = flag_set(x);
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
   long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
   if (blocks > 148 * 8) blocks = 148 * 8;
@@ -323,19 +325,19 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
   const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
   if (!wire16 && !out16) {
     eb_shard_combine_kernel<float, float><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const float*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        reinterpret_cast<const float*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
         static_cast<float*>(d_out), x->status, spins);
   } else if (!wire16 && out16) {
     eb_shard_combine_kernel<float, __half><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const float*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        reinterpret_cast<const float*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
         static_cast<__half*>(d_out), x->status, spins);
   } else if (wire16 && !out16) {
     eb_shard_combine_kernel<__half, float><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const __half*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        reinterpret_cast<const __half*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
         static_cast<float*>(d_out), x->status, spins);
   } else {
     eb_shard_combine_kernel<__half, __half><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const __half*>(slots), flags, x->world, x->epoch, slot_stride, count,
+        reinterpret_cast<const __half*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
         static_cast<__half*>(d_out), x->status, spins);
   }
   count_launch();

@@ -72,9 +72,9 @@ class ShardExchange(C.Structure):
         ("world", C.c_int32), ("rank", C.c_int32), ("bags_per_rank", C.c_int64),
         ("wire_dtype", C.c_int32), ("epoch", C.c_uint32),
         ("peer_slots", C.c_void_p * MAX_PEERS), ("peer_flags", C.c_void_p * MAX_PEERS),
-        ("counter", C.c_void_p), ("status", C.c_void_p), ("max_spins", C.c_int64),
+        ("status", C.c_void_p), ("max_spins", C.c_int64),
         ("layout", C.c_int32), ("num_tables", C.c_int32), ("table_index", C.c_int32),
-        ("hold_signal", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -166,7 +166,7 @@ class PeerBuffers:
         self._opened, self._own, self._keep = [], [], []
 
 
-def make_exchange(buffers: PeerBuffers, rank: int, per_rank_bags: int, wire_dtype: int, counter,
+def make_exchange(buffers: PeerBuffers, rank: int, per_rank_bags: int, wire_dtype: int,
                   status, *, layout=LAYOUT_ROW_SHARD, num_tables=0, max_spins=0) -> ShardExchange:
     x = ShardExchange()
     x.world, x.rank = buffers.world, rank
@@ -176,7 +176,6 @@ def make_exchange(buffers: PeerBuffers, rank: int, per_rank_bags: int, wire_dtyp
     for r in range(buffers.world):
         x.peer_slots[r] = buffers.slots[r]
         x.peer_flags[r] = buffers.flags[r]
-    x.counter = counter.data_ptr()
     x.status = status.data_ptr()
     x.max_spins = max_spins
     x.layout = layout
@@ -211,10 +210,8 @@ class RowShardedBag:
         if exchange == "push":
             nbytes = _lib().fwd_eb_shard_slots_bytes(self.world, self.per, self.dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
-            self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.counter,
-                                   self.status)
+            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status)
         elif exchange in ("nccl", "a2a"):
             self.partial = torch.empty((self.per * self.world, self.dim), dtype=torch.float32,
                                        device=dev)
@@ -229,9 +226,9 @@ class RowShardedBag:
         return capi.make_params(self.table, indices, offsets, out=out, mode=self.mode,
                                 padding_idx=self.padding_idx, row_lo=self.row_lo)
 
-    def forward(self, indices, offsets):
+    def forward(self, indices, offsets, pool_events=None):
         """Returns this rank's [bags_owned, dim] slice of the pooled output (a view reused by the
-        next call)."""
+        next call).  `pool_events` = (start, end) CUDA events recorded around the pooling launch."""
         import torch
         import torch.distributed as dist
         num_bags = offsets.numel()
@@ -244,7 +241,11 @@ class RowShardedBag:
             self.epoch += 1
             self.x.epoch = self.epoch
             p = self.params(indices, offsets, self.out)
+            if pool_events:
+                pool_events[0].record()
             capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
+            if pool_events:
+                pool_events[1].record()
             capi.check(_lib().fwd_eb_shard_combine(C.byref(self.x), self.dim, mine,
                                                    self.out.data_ptr(),
                                                    capi._torch_dtype_code(self.out),
@@ -253,7 +254,11 @@ class RowShardedBag:
         if num_bags < self.per * self.world:
             self.partial[num_bags:].zero_()
         p = self.params(indices, offsets, self.partial)
+        if pool_events:
+            pool_events[0].record()
         capi.forward(p, stream)
+        if pool_events:
+            pool_events[1].record()
         if self.exchange == "nccl":
             dist.reduce_scatter_tensor(self.out32, self.partial, group=self.group)
         else:
@@ -335,10 +340,9 @@ class TableWiseBags:
         if exchange == "push":
             nbytes = _lib().fwd_eb_shard_tablewise_bytes(self.per, self.num_tables, dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
-            self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.counter,
-                                   self.status, layout=LAYOUT_TABLE_WISE, num_tables=self.num_tables)
+            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status,
+                                   layout=LAYOUT_TABLE_WISE, num_tables=self.num_tables)
         else:
             tl = max(1, len(self.mine))
             self.send = torch.zeros((self.per * self.world, tl, dim), dtype=torch.float32, device=dev)
@@ -358,8 +362,6 @@ class TableWiseBags:
         if self.exchange == "push":
             self.epoch += 1
             self.x.epoch = self.epoch
-            if not self.mine:
-                capi.check(_lib().fwd_eb_shard_signal(C.byref(self.x), C.c_void_p(stream)))
             for k, t in enumerate(self.mine):
                 idx, off, w = inputs[t]
                 # `out` is ignored by the push entry point; any CUDA tensor satisfies the binding
@@ -367,7 +369,6 @@ class TableWiseBags:
                                      fixed_len=self.fixed_len, per_sample_weights=w,
                                      padding_idx=self.padding_idx)
                 self.x.table_index = t
-                self.x.hold_signal = 0 if k == len(self.mine) - 1 else 1
                 capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
             res = C.c_void_p()
             capi.check(_lib().fwd_eb_shard_wait(C.byref(self.x), self.dim, C.byref(res),

@@ -16,10 +16,12 @@
  * call parity, one slot per source rank) and G flag words, all mapped into every
  * peer (CUDA IPC below, or any other peer mapping).  fwd_eb_shard_push pools, and
  * writes bag b's partial row straight into slot [parity][rank] of b's owner with
- * plain peer stores; its last CTA publishes `epoch` in every peer's flag word.
- * fwd_eb_shard_combine waits (bounded) until all G flags have reached `epoch`,
- * then folds the G slots in rank order — a fixed order, so results do not depend
- * on timing.  No multicast loads, no library kernels on peer memory.
+ * plain peer stores.  fwd_eb_shard_combine, queued behind it on the same stream,
+ * first publishes `epoch` in every peer's flag word (the pooling grid has
+ * completed by then, so its peer stores have been performed), then waits
+ * (bounded) until all G flags have reached `epoch` and folds the G slots in rank
+ * order — a fixed order, so results do not depend on timing.  No multicast
+ * loads, no library kernels on peer memory.
  *
  * Every wait is bounded: after `max_spins` polls the waiting kernel writes
  * FWD_EB_SHARD_TIMEOUT to `status` and returns without touching the output.
@@ -58,13 +60,12 @@ typedef struct fwd_eb_shard_exchange {
   uint32_t epoch;             /* call number, starting at 1; parity picks the buffer half */
   void* peer_slots[FWD_EB_MAX_PEERS];      /* rank r's receive buffer as mapped here */
   uint32_t* peer_flags[FWD_EB_MAX_PEERS];  /* rank r's G flag words as mapped here */
-  uint32_t* counter;          /* one zeroed device word of this rank (CTA countdown) */
   int32_t* status;            /* one device word of this rank; 0 = fine */
   int64_t max_spins;          /* bound of the flag wait; 0 = default (about a second) */
   int32_t layout;             /* FWD_EB_LAYOUT_* */
   int32_t num_tables;         /* TABLE_WISE: tables in the whole model */
   int32_t table_index;        /* TABLE_WISE: which of them this call pools */
-  int32_t hold_signal;        /* 1: do not raise the flags after this call (more tables follow) */
+  int32_t reserved;
 } fwd_eb_shard_exchange;
 
 /* Bytes of one rank's receive buffer: row-shard layout for `world` sources, or, with
@@ -79,18 +80,20 @@ size_t fwd_eb_shard_tablewise_bytes(int64_t bags_per_rank, int32_t num_tables, i
  * already divided by the bag's full count, so the owner only adds. */
 int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream);
 
-/* Wait for all peers' flags, then out[b, :] = sum over r of slot[r][b, :] for the
- * `num_bags` bags this rank owns. */
+/* Raise this rank's flag everywhere, wait for all peers' flags, then
+ * out[b, :] = sum over r of slot[r][b, :] for the `num_bags` bags this rank owns.
+ * Must follow this call's fwd_eb_shard_push on the same stream. */
 int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
                          void* d_out, int32_t out_dtype, void* stream);
 
-/* TABLE_WISE: wait (bounded) until every rank has raised `epoch`; on success
+/* TABLE_WISE: after the last fwd_eb_shard_push of this call on the same stream: raise
+ * this rank's flag, wait (bounded) until every rank has raised `epoch`; on success
  * *d_result (if not NULL) receives the address of this call's buffer half, laid out
  * [num_bags owned][num_tables][dim]. */
 int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_result, void* stream);
 
-/* Publish `epoch` to every peer without pooling (used to keep epochs in step when a
- * rank has nothing to send, and by tests). */
+/* Publish `epoch` to every peer without pooling or waiting (tests; a rank that leaves a
+ * call early). */
 int fwd_eb_shard_signal(const fwd_eb_shard_exchange* x, void* stream);
 
 /* ---- peer mapping through CUDA IPC (one process per GPU on one node) ---------- */

@@ -1,7 +1,8 @@
 """The fused pool-and-push kernels on ONE GPU: every "rank" is a set of buffers on the same
-device and the ranks' launches run one after another on one stream, so no kernel ever waits
-for another (all flags are already raised when a wait starts).  Real multi-GPU runs are in
-test_gpu_multi.py."""
+device and the ranks' launches run one after another on one stream.  A fold / wait kernel
+raises its own rank's flag and then waits for the others', so here every rank's flag is raised
+explicitly (fwd_eb_shard_signal) before the first fold runs: no kernel ever waits for a kernel
+queued behind it.  Real multi-GPU runs are in test_gpu_multi.py."""
 import ctypes as C
 
 import numpy as np
@@ -28,10 +29,9 @@ def _setup(world, per, dim, wire, layout=fd.LAYOUT_ROW_SHARD, num_tables=0, max_
     bufs = fd.PeerBuffers(nbytes, world, 0, local_world=world)
     xs, keep = [], []
     for r in range(world):
-        counter = torch.zeros(1, dtype=torch.int32, device=DEV)
         status = torch.zeros(1, dtype=torch.int32, device=DEV)
-        keep += [counter, status]
-        xs.append(fd.make_exchange(bufs, r, per, wire, counter, status, layout=layout,
+        keep += [status]
+        xs.append(fd.make_exchange(bufs, r, per, wire, status, layout=layout,
                                    num_tables=num_tables, max_spins=max_spins))
     return lib, bufs, xs, keep
 
@@ -56,6 +56,8 @@ def test_row_shard_push_and_combine_four_ranks(wire, mode):
             p = capi.make_params(tabs[r], i, o, out=tabs[r][:1], mode=mode, padding_idx=5,
                                  row_lo=shards[r][0])
             capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+        for r in range(world):
+            capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
         parts = np.stack([O.pool(table[lo:lo + n], bags.indices, bags.offsets, mode=mode,
                                  padding_idx=5, row_lo=lo, out_dtype=np.float32)
                           for lo, n in shards])
@@ -70,7 +72,7 @@ def test_row_shard_push_and_combine_four_ranks(wire, mode):
             torch.cuda.synchronize()
             assert np.array_equal(out[:mine].cpu().numpy(), expect[lo:lo + mine])
             assert torch.isnan(out[mine:]).all()
-    assert all(int(k.item()) == 0 for k in keep)       # counters back to zero, no timeouts
+    assert all(int(k.item()) == 0 for k in keep)       # no timeouts
     whole = O.pool(table, bags.indices, bags.offsets, mode=mode, padding_idx=5, out_dtype=np.float32)
     np.testing.assert_allclose(expect, whole, rtol=1e-3, atol=2e-2 if wire == capi.F16 else 1e-4)
 
@@ -96,8 +98,9 @@ def test_table_wise_push_lands_in_result_layout():
             p = capi.make_params(tt, ii, None, out=tt[:1], mode=capi.MODE_SUM, fixed_len=L,
                                  per_sample_weights=ww)
             xs[r].table_index = t
-            xs[r].hold_signal = 0 if k == len(mine) - 1 else 1
             capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+    for r in range(world):
+        capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
     expect = np.stack([O.pool(tables[t], idx[t], mode=O.MODE_SUM, fixed_len=L, per_sample_weights=w[t])
                        for t in range(ntab)], axis=1)                      # [nb, T, dim]
     for r in range(world):
@@ -115,12 +118,12 @@ def test_wait_gives_up_and_reports_instead_of_hanging():
     world, per, dim = 2, 8, 16
     lib, bufs, xs, keep = _setup(world, per, dim, capi.F32, max_spins=2000)
     stream = C.c_void_p(capi.current_stream_ptr())
-    xs[0].epoch = 1
-    capi.check(lib.fwd_eb_shard_signal(C.byref(xs[0]), stream))   # rank 0 signals, rank 1 never does
+    xs[0].epoch = 1                                              # rank 0's fold raises its own flag;
+                                                                 # rank 1 never raises its
     out = torch.full((per, dim), 7.0, device=DEV)
     capi.check(lib.fwd_eb_shard_combine(C.byref(xs[0]), dim, per, out.data_ptr(), capi.F32, stream))
     torch.cuda.synchronize()
-    status0 = keep[1]
+    status0 = keep[0]
     assert int(status0.item()) == fd.SHARD_TIMEOUT
     assert torch.all(out == 7.0)
     assert float((out + 1).sum().item()) == per * dim * 8.0       # device still answers
@@ -138,3 +141,32 @@ def test_argument_errors():
     assert lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[0]), None) == capi.EINVAL
     xs[0].epoch, xs[0].world = 1, 99
     assert lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[0]), None) == capi.EINVAL
+
+
+def test_row_shard_push_wide_rows_span_column_tiles():
+    """2304 fp16 columns = 288 chunks: three column tiles per bag tile through the work dispenser."""
+    rng = np.random.default_rng(10)
+    world, rows, dim, nb = 2, 600, 2304, 70
+    table = rng.standard_normal((rows, dim)).astype(np.float16)
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, capi.F32)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    bags = workloads.ragged_bags(rows, rng.integers(0, 20, nb), rng)
+    i, o = _cuda(bags.indices), _cuda(bags.offsets)
+    shards = [fd.shard_rows(rows, world, r) for r in range(world)]
+    tabs = [_cuda(table[lo:lo + n]) for lo, n in shards]
+    for r in range(world):
+        xs[r].epoch = 1
+        p = capi.make_params(tabs[r], i, o, out=tabs[r][:1], mode=capi.MODE_SUM, row_lo=shards[r][0])
+        capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+    for r in range(world):
+        capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
+    parts = np.stack([O.pool(table[lo:lo + n], bags.indices, bags.offsets, row_lo=lo,
+                             out_dtype=np.float32) for lo, n in shards])
+    expect = O.combine_partials(parts, np.float32)
+    for r in range(world):
+        lo, mine = fd.owned_bags(nb, world, r)
+        out = torch.empty((per, dim), device=DEV)
+        capi.check(lib.fwd_eb_shard_combine(C.byref(xs[r]), dim, mine, out.data_ptr(), capi.F32, stream))
+        torch.cuda.synchronize()
+        assert np.array_equal(out[:mine].cpu().numpy(), expect[lo:lo + mine])
