@@ -249,7 +249,7 @@ int plan_group(const fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* 
 
 // ---- kernel dispatch ---------------------------------------------------------
 
-template <typename TW, int VE, int CPL, int OP, int U>
+template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 static cudaError_t launch_pool(const Plan& pl, cudaStream_t st) {
   const PoolArgs& a = pl.a;
   if (pl.strategy == FWD_EB_STRATEGY_GROUP) {
@@ -258,7 +258,7 @@ static cudaError_t launch_pool(const Plan& pl, cudaStream_t st) {
     if (blocks == 0) return cudaSuccess;
     if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
     dim3 grid((unsigned)blocks, (unsigned)pl.tiles);
-    eb_pool_group_kernel<TW, VE, CPL, OP, U><<<grid, kCtaThreads, 0, st>>>(a);
+    eb_pool_group_kernel<TW, VE, CPL, OP, U, IPL><<<grid, kCtaThreads, 0, st>>>(a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError();
   }
@@ -268,7 +268,7 @@ static cudaError_t launch_pool(const Plan& pl, cudaStream_t st) {
   const int groups = kCtaThreads >> a.lanes_log2;
   const size_t smem = (size_t)kCtaThreads * CPL * VE * sizeof(float) + (size_t)groups * 2 * sizeof(int);
   dim3 grid((unsigned)blocks, (unsigned)pl.tiles);
-  eb_pool_cta_kernel<TW, VE, CPL, OP, U><<<grid, kCtaThreads, smem, st>>>(a);
+  eb_pool_cta_kernel<TW, VE, CPL, OP, U, IPL><<<grid, kCtaThreads, smem, st>>>(a);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess || a.splits <= 1) return e;
@@ -280,17 +280,17 @@ static cudaError_t launch_pool(const Plan& pl, cudaStream_t st) {
   return cudaGetLastError();
 }
 
-template <typename TW, int VE, int CPL, int U>
+template <typename TW, int VE, int CPL, int U, int IPL>
 static cudaError_t launch_op(const Plan& pl, cudaStream_t st) {
   switch (pl.op) {
     case kOpSum:
-      return launch_pool<TW, VE, CPL, kOpSum, U>(pl, st);
+      return launch_pool<TW, VE, CPL, kOpSum, U, IPL>(pl, st);
     case kOpWeighted:
-      return launch_pool<TW, VE, CPL, kOpWeighted, U>(pl, st);
+      return launch_pool<TW, VE, CPL, kOpWeighted, U, IPL>(pl, st);
     case kOpMax:
-      return launch_pool<TW, VE, CPL, kOpMax, U>(pl, st);
+      return launch_pool<TW, VE, CPL, kOpMax, U, IPL>(pl, st);
     default:
-      return launch_pool<TW, VE, CPL, kOpSquareSum, U>(pl, st);
+      return launch_pool<TW, VE, CPL, kOpSquareSum, U, IPL>(pl, st);
   }
 }
 
@@ -299,14 +299,17 @@ static cudaError_t launch_op(const Plan& pl, cudaStream_t st) {
 template <typename TW>
 static cudaError_t launch_shape(const Plan& pl, cudaStream_t st) {
   constexpr int VE = 16 / (int)sizeof(TW);
-  if (!pl.vec) return launch_op<TW, 1, 4, 4>(pl, st);
+  if (!pl.vec) return launch_op<TW, 1, 4, 4, 1>(pl, st);
   switch (pl.cpl) {
     case 1:
-      return launch_op<TW, VE, 1, FWD_EB_U1>(pl, st);
+      // rows of 256 B / 128 B: blocks of 32 indices (two / four index loads per lane)
+      if (pl.a.lanes_log2 == 4) return launch_op<TW, VE, 1, FWD_EB_U1, 2>(pl, st);
+      if (pl.a.lanes_log2 == 3) return launch_op<TW, VE, 1, FWD_EB_U1, 4>(pl, st);
+      return launch_op<TW, VE, 1, FWD_EB_U1, 1>(pl, st);
     case 2:
-      return launch_op<TW, VE, 2, 4>(pl, st);
+      return launch_op<TW, VE, 2, 4, 1>(pl, st);
     default:
-      return launch_op<TW, VE, 4, 2>(pl, st);
+      return launch_op<TW, VE, 4, 2, 1>(pl, st);
   }
 }
 

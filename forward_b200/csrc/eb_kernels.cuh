@@ -202,7 +202,11 @@ struct Accum {
 // One lane's share of walking indices [start, end) of a bag.  All 32 lanes of
 // the warp must call this together (the loops are warp-uniform; a group with
 // nothing left simply has its predicates off).
-template <typename TW, int VE, int CPL, int OP, int U>
+//
+// IPL = index loads per lane and block.  A block is lanes * IPL consecutive indices of the
+// bag; with IPL = 32 / lanes (groups of 16 or 8 lanes) every block is 32 indices, so a bag of
+// 50 indices costs two index round trips whatever the row width.
+template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, long long end,
                                            int chunk0, Accum<CPL, VE>& s) {
   using V = typename Chunk<TW, VE>::type;
@@ -213,6 +217,7 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
   const unsigned gmask = lanes == 32 ? kFull : ((1u << lanes) - 1u);
   const int vbytes = VE * (int)sizeof(TW);
   const unsigned stride32 = (unsigned)a.row_bytes_stride;  // checked on the host: < 2^32
+  const int block = lanes * IPL;
 
   bool chunk_ok[CPL];
   int chunk_off[CPL];
@@ -223,7 +228,7 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
     chunk_off[c] = chunk * vbytes;
   }
 
-  // fetch one index per lane: local row (>= 0) or -1 for "skip"
+  // fetch one index: local row (>= 0) or -1 for "skip"
   auto fetch = [&](long long pos, int& row, float& w, bool& counted) {
     row = -1;
     w = 1.0f;
@@ -241,17 +246,9 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
     }
   };
 
-  // Issue U row loads, then fold them in order.  src[u] names the lane of this group that
-  // holds the row number, ok[u] switches the slot off.
-  auto consume = [&](const int (&src)[U], const bool (&ok)[U], int cur_row, float cur_w) {
-    int row[U];
-    float w[U];
+  // Issue U row loads, then fold them in order; ok[u] switches a slot off.
+  auto consume = [&](const int (&row)[U], const float (&w)[U], const bool (&ok)[U]) {
     V val[U][CPL];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      row[u] = __shfl_sync(kFull, cur_row, gbase + src[u]);
-      if (OP == kOpWeighted) w[u] = __shfl_sync(kFull, cur_w, gbase + src[u]);
-    }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       if (ok[u]) {
@@ -274,46 +271,109 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
     }
   };
 
+  // Survivors of a block (everything that is not padding and lies inside the table window)
+  // wait in a per-group ring in shared memory until U of them are there, so a row-load pass
+  // is as full for a 1-in-8 window as for a dense bag, and blocks without enough survivors
+  // cost no row round trip of their own.  Capacity 2 * block per group.  Groups narrower than
+  // 8 lanes (rows under 128 B) keep their survivors in registers and walk the mask instead.
+  constexpr int kRingPerWarp = 64 * (IPL > 1 ? IPL : 1);
+  __shared__ int ring_row[(kCtaThreads / 32) * kRingPerWarp];
+  __shared__ float ring_w[OP == kOpWeighted ? (kCtaThreads / 32) * kRingPerWarp : 1];
+  const bool use_ring = IPL > 1 || lanes >= 8;
+  const int ring_cap = 2 * block;
+  const int ring_base = (threadIdx.x >> 5) * kRingPerWarp + 2 * IPL * gbase;
+  int ring_head = 0, ring_tail = 0;  // same value in every lane of a group
+
   long long base = start;
-  int cur_row, nxt_row;
-  float cur_w, nxt_w;
-  bool cur_counted, nxt_counted;
-  fetch(base + lig, cur_row, cur_w, cur_counted);
+  int cur_row[IPL], nxt_row[IPL];
+  float cur_w[IPL], nxt_w[IPL];
+  bool cur_counted[IPL], nxt_counted[IPL];
+#pragma unroll
+  for (int j = 0; j < IPL; ++j) fetch(base + j * lanes + lig, cur_row[j], cur_w[j], cur_counted[j]);
 
   while (__any_sync(kFull, base < end)) {
-    fetch(base + lanes + lig, nxt_row, nxt_w, nxt_counted);  // next block of indices, early
+#pragma unroll
+    for (int j = 0; j < IPL; ++j)  // next block of indices, early
+      fetch(base + block + j * lanes + lig, nxt_row[j], nxt_w[j], nxt_counted[j]);
     long long left = end - base;
-    const int n = left <= 0 ? 0 : (left < lanes ? (int)left : lanes);  // entries of this block
+    const int n = left <= 0 ? 0 : (left < block ? (int)left : block);  // entries of this block
+    const bool last_block = left <= block;
     const unsigned want = n >= 32 ? kFull : ((1u << n) - 1u);
-    unsigned m = (__ballot_sync(kFull, cur_row >= 0) >> gbase) & gmask;
-    if (a.mean) s.counted += __popc((__ballot_sync(kFull, cur_counted) >> gbase) & gmask);
+    unsigned m = 0;  // bit e = entry e of the block survived; e = j * lanes + lane-in-group
+#pragma unroll
+    for (int j = 0; j < IPL; ++j) {
+      m |= ((__ballot_sync(kFull, cur_row[j] >= 0) >> gbase) & gmask) << (j * lanes);
+      if (a.mean) s.counted += __popc((__ballot_sync(kFull, cur_counted[j]) >> gbase) & gmask);
+    }
 
-    // When every entry of every group's block survived the filters the block is walked in
-    // place (slot k of a pass is entry k); otherwise the set bits of the survivor mask are
-    // walked.  Either way one pass issues U row loads per group.
-    const bool dense = __all_sync(kFull, m == want);
+    // Three ways to feed a pass of U row loads per group:
+    //   dense  (IPL == 1) every entry of every group's block survived and no ring holds older
+    //          rows: slot k of a pass is entry k of the block, fetched by shuffle;
+    //   ring   survivors are appended to the group's ring and passes run while a ring holds
+    //          U rows (or anything at all, on the group's last block);
+    //   walk   narrow groups: the set bits of the survivor mask are walked directly.
+    const bool dense = IPL == 1 && __all_sync(kFull, m == want && ring_head == ring_tail);
+    const bool ring = !dense && use_ring;
+    if (ring) {
+#pragma unroll
+      for (int j = 0; j < IPL; ++j) {
+        if (cur_row[j] >= 0) {
+          const int e = j * lanes + lig;
+          const int at = ring_base + ((ring_tail + __popc(m & ((1u << e) - 1u))) & (ring_cap - 1));
+          ring_row[at] = cur_row[j];
+          if (OP == kOpWeighted) ring_w[at] = cur_w[j];
+        }
+      }
+      ring_tail += __popc(m);
+      __syncwarp();
+    }
     const int nmax = __reduce_max_sync(kFull, n);
     for (int k = 0;; k += U) {
-      if (dense ? (k >= nmax) : !__any_sync(kFull, m != 0u)) break;
-      int src[U];
+      const int pending = ring_tail - ring_head;
+      bool more;
+      if (dense) {
+        more = k < nmax;
+      } else if (ring) {
+        more = __any_sync(kFull, last_block ? pending > 0 : pending >= U);
+      } else {
+        more = __any_sync(kFull, m != 0u);
+      }
+      if (!more) break;
+      int row[U];
+      float w[U];
       bool ok[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        if (dense) {
-          src[u] = (k + u) & (lanes - 1);
-          ok[u] = (k + u) < n;
+        if (ring) {
+          ok[u] = u < pending;
+          const int at = ring_base + ((ring_head + u) & (ring_cap - 1));
+          row[u] = ring_row[at];
+          if (OP == kOpWeighted) w[u] = ring_w[at];
         } else {
-          ok[u] = m != 0u;
-          src[u] = ok[u] ? (__ffs(m) - 1) : 0;
-          m &= (m - 1u);  // clears the lowest set bit; 0 stays 0
+          int src;
+          if (dense) {
+            src = (k + u) & (lanes - 1);
+            ok[u] = (k + u) < n;
+          } else {
+            ok[u] = m != 0u;
+            src = ok[u] ? (__ffs(m) - 1) : 0;
+            m &= (m - 1u);  // clears the lowest set bit; 0 stays 0
+          }
+          row[u] = __shfl_sync(kFull, cur_row[0], gbase + src);
+          if (OP == kOpWeighted) w[u] = __shfl_sync(kFull, cur_w[0], gbase + src);
         }
       }
-      consume(src, ok, cur_row, cur_w);
+      if (ring) ring_head += pending < U ? pending : U;
+      consume(row, w, ok);
     }
-    cur_row = nxt_row;
-    cur_w = nxt_w;
-    cur_counted = nxt_counted;
-    base += lanes;
+    if (ring) __syncwarp();  // all reads of the ring are done before the next block is appended
+#pragma unroll
+    for (int j = 0; j < IPL; ++j) {
+      cur_row[j] = nxt_row[j];
+      cur_w[j] = nxt_w[j];
+      cur_counted[j] = nxt_counted[j];
+    }
+    base += block;
   }
 }
 
@@ -416,7 +476,7 @@ __device__ __forceinline__ void clear(Accum<CPL, VE>& s) {
 // ---- strategy 1: one lane group per bag -------------------------------------
 // grid.x covers bags (kCtaThreads / lanes bags per CTA), grid.y covers column
 // tiles of 32 * CPL chunks for rows wider than one tile.
-template <typename TW, int VE, int CPL, int OP, int U>
+template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 __global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_group_kernel(const PoolArgs a) {
   const int lanes_log2 = a.lanes_log2;
@@ -429,7 +489,7 @@ eb_pool_group_kernel(const PoolArgs a) {
 
   Accum<CPL, VE> s;
   clear(s);
-  pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
+  pool_range<TW, VE, CPL, OP, U, IPL>(a, start, end, chunk0, s);
 
   const bool tf16 = sizeof(TW) == 2;
 #pragma unroll
@@ -445,7 +505,7 @@ eb_pool_group_kernel(const PoolArgs a) {
 // the groups in slice order, which keeps both the summation order fixed and the
 // first-of-equals rule for max.  With splits > 1 the folded partial goes to the
 // scratch arrays instead of the output and eb_split_finish_kernel completes it.
-template <typename TW, int VE, int CPL, int OP, int U>
+template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 __global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_cta_kernel(const PoolArgs a) {
   extern __shared__ float smem[];  // [groups][tile_cols] then int[groups][2]
@@ -475,7 +535,7 @@ eb_pool_cta_kernel(const PoolArgs a) {
 
   Accum<CPL, VE> s;
   clear(s);
-  pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
+  pool_range<TW, VE, CPL, OP, U, IPL>(a, start, end, chunk0, s);
 
   float* part = smem;
   int* meta = reinterpret_cast<int*>(smem + (size_t)groups * tile_cols);

@@ -49,7 +49,7 @@ struct FlagSet {
   uint32_t* peer_flags[FWD_EB_MAX_PEERS];
 };
 
-template <typename TW, int VE, int CPL, int OP, int U>
+template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 __global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
   const int lanes_log2 = a.lanes_log2;
@@ -61,7 +61,7 @@ eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
 
   Accum<CPL, VE> s;
   clear(s);
-  pool_range<TW, VE, CPL, OP, U>(a, start, end, chunk0, s);
+  pool_range<TW, VE, CPL, OP, U, IPL>(a, start, end, chunk0, s);
 
   const bool tf16 = sizeof(TW) == 2;
 #pragma unroll
@@ -98,7 +98,8 @@ __global__ void eb_shard_wait_kernel(const FlagSet f, int rank, int world, uint3
 }
 
 // Wait (bounded) for every source rank's flag, then fold the slots in rank order.
-template <typename TP, typename TO>
+// Threads fold 16-byte packets (4 floats or 8 halves per slot) when the geometry allows.
+template <typename TP, typename TO, bool VEC>
 __global__ void __launch_bounds__(kCtaThreads)
 eb_shard_combine_kernel(const TP* slots, const FlagSet f, int rank, int world, uint32_t epoch,
                         long long slot_stride, long long count, TO* out, int* status,
@@ -127,22 +128,56 @@ eb_shard_combine_kernel(const TP* slots, const FlagSet f, int rank, int world, u
     if (threadIdx.x == 0) atomicExch(status, FWD_EB_SHARD_TIMEOUT);
     return;
   }
-  for (long long i = (long long)blockIdx.x * kCtaThreads + threadIdx.x; i < count;
+  constexpr int PK = VEC ? 16 / (int)sizeof(TP) : 1;  // elements per packet
+  const long long packets = count / PK;
+  for (long long i = (long long)blockIdx.x * kCtaThreads + threadIdx.x; i < packets;
        i += (long long)gridDim.x * kCtaThreads) {
-    float s = 0.0f;
+    float acc[PK];
+#pragma unroll
+    for (int e = 0; e < PK; ++e) acc[e] = 0.0f;
     for (int r = 0; r < world; ++r) {
-      float v;
-      if (sizeof(TP) == 2) {
-        v = __half2float(reinterpret_cast<const __half*>(slots)[r * slot_stride + i]);
+      const TP* src = slots + r * slot_stride + i * PK;
+      float v[PK];
+      if (VEC && sizeof(TP) == 2) {
+        uint4 raw = *reinterpret_cast<const uint4*>(src);
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 t = __half22float2(h[e]);
+          v[(2 * e) % PK] = t.x;
+          v[(2 * e + 1) % PK] = t.y;
+        }
+      } else if (VEC) {
+        float4 raw = *reinterpret_cast<const float4*>(src);
+        v[0] = raw.x; v[1 % PK] = raw.y; v[2 % PK] = raw.z; v[3 % PK] = raw.w;
+      } else if (sizeof(TP) == 2) {
+        v[0] = __half2float(*reinterpret_cast<const __half*>(src));
       } else {
-        v = reinterpret_cast<const float*>(slots)[r * slot_stride + i];
+        v[0] = *reinterpret_cast<const float*>(src);
       }
-      s = __fadd_rn(s, v);
+#pragma unroll
+      for (int e = 0; e < PK; ++e) acc[e] = __fadd_rn(acc[e], v[e]);
     }
-    if (sizeof(TO) == 2) {
-      reinterpret_cast<__half*>(out)[i] = __float2half_rn(s);
+    TO* dst = out + i * PK;
+    if (VEC && sizeof(TO) == 4) {
+#pragma unroll
+      for (int e = 0; e < PK; e += 4) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(dst) + e) =
+            make_float4(acc[e], acc[(e + 1) % PK], acc[(e + 2) % PK], acc[(e + 3) % PK]);
+      }
+    } else if (VEC) {
+      __half2 pk2[PK / 2 > 0 ? PK / 2 : 1];
+#pragma unroll
+      for (int e = 0; e < PK / 2; ++e) pk2[e] = __floats2half2_rn(acc[2 * e], acc[(2 * e + 1) % PK]);
+      if (PK == 8) {
+        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(pk2);
+      } else {
+        *reinterpret_cast<uint2*>(dst) = *reinterpret_cast<const uint2*>(pk2);
+      }
+    } else if (sizeof(TO) == 2) {
+      reinterpret_cast<__half*>(dst)[0] = __float2half_rn(acc[0]);
     } else {
-      reinterpret_cast<float*>(out)[i] = s;
+      reinterpret_cast<float*>(dst)[0] = acc[0];
     }
   }
 }
@@ -201,7 +236,7 @@ static FlagSet flag_set(const fwd_eb_shard_exchange* x) {
   return f;
 }
 
-template <typename TW, int VE, int CPL, int U>
+template <typename TW, int VE, int CPL, int U, int IPL>
 static cudaError_t launch_push(const PoolArgs& a, const PushArgs& x, int tiles, bool weighted,
                                cudaStream_t st) {
   const long long threads = a.num_bags << a.lanes_log2;
@@ -210,9 +245,9 @@ static cudaError_t launch_push(const PoolArgs& a, const PushArgs& x, int tiles, 
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)blocks, (unsigned)tiles);
   if (weighted) {
-    eb_pool_push_kernel<TW, VE, CPL, kOpWeighted, U><<<grid, kCtaThreads, 0, st>>>(a, x);
+    eb_pool_push_kernel<TW, VE, CPL, kOpWeighted, U, IPL><<<grid, kCtaThreads, 0, st>>>(a, x);
   } else {
-    eb_pool_push_kernel<TW, VE, CPL, kOpSum, U><<<grid, kCtaThreads, 0, st>>>(a, x);
+    eb_pool_push_kernel<TW, VE, CPL, kOpSum, U, IPL><<<grid, kCtaThreads, 0, st>>>(a, x);
   }
   count_launch();
   return cudaGetLastError();
@@ -222,10 +257,12 @@ template <typename TW>
 static cudaError_t launch_push_shape(const PoolArgs& a, const PushArgs& x, bool vec, int cpl,
                                      int tiles, bool weighted, cudaStream_t st) {
   constexpr int VE = 16 / (int)sizeof(TW);
-  if (!vec) return launch_push<TW, 1, 4, 4>(a, x, tiles, weighted, st);
-  if (cpl == 1) return launch_push<TW, VE, 1, FWD_EB_U1>(a, x, tiles, weighted, st);
-  if (cpl == 2) return launch_push<TW, VE, 2, 4>(a, x, tiles, weighted, st);
-  return launch_push<TW, VE, 4, 2>(a, x, tiles, weighted, st);
+  if (!vec) return launch_push<TW, 1, 4, 4, 1>(a, x, tiles, weighted, st);
+  if (cpl == 1 && a.lanes_log2 == 4) return launch_push<TW, VE, 1, FWD_EB_U1, 2>(a, x, tiles, weighted, st);
+  if (cpl == 1 && a.lanes_log2 == 3) return launch_push<TW, VE, 1, FWD_EB_U1, 4>(a, x, tiles, weighted, st);
+  if (cpl == 1) return launch_push<TW, VE, 1, FWD_EB_U1, 1>(a, x, tiles, weighted, st);
+  if (cpl == 2) return launch_push<TW, VE, 2, 4, 1>(a, x, tiles, weighted, st);
+  return launch_push<TW, VE, 4, 2, 1>(a, x, tiles, weighted, st);
 }
 
 }  // namespace fwd_eb
@@ -317,29 +354,33 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
   const char* slots = static_cast<const char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch & 1u);
   const FlagSet flags = flag_set(x);
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
-  long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
+  const int pk = wire16 ? 8 : 4;
+  const bool vec = count % pk == 0 && slot_stride % pk == 0 &&
+                   (reinterpret_cast<uintptr_t>(slots) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(d_out) & 15u) == 0;
+  const long long packets = vec ? count / pk : count;
+  long long blocks = (packets + kCtaThreads - 1) / kCtaThreads;
+  if (blocks > 148 * 4) blocks = 148 * 4;
   if (blocks < 1) blocks = 1;
   const unsigned g = (unsigned)blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
-  if (!wire16 && !out16) {
-    eb_shard_combine_kernel<float, float><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const float*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
-        static_cast<float*>(d_out), x->status, spins);
-  } else if (!wire16 && out16) {
-    eb_shard_combine_kernel<float, __half><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const float*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
-        static_cast<__half*>(d_out), x->status, spins);
-  } else if (wire16 && !out16) {
-    eb_shard_combine_kernel<__half, float><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const __half*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
-        static_cast<float*>(d_out), x->status, spins);
+#define FWD_EB_COMBINE(TP, TO, V)                                                               \
+  eb_shard_combine_kernel<TP, TO, V><<<g, kCtaThreads, 0, st>>>(                                \
+      reinterpret_cast<const TP*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count, \
+      static_cast<TO*>(d_out), x->status, spins)
+  if (vec) {
+    if (!wire16 && !out16) FWD_EB_COMBINE(float, float, true);
+    else if (!wire16 && out16) FWD_EB_COMBINE(float, __half, true);
+    else if (wire16 && !out16) FWD_EB_COMBINE(__half, float, true);
+    else FWD_EB_COMBINE(__half, __half, true);
   } else {
-    eb_shard_combine_kernel<__half, __half><<<g, kCtaThreads, 0, st>>>(
-        reinterpret_cast<const __half*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count,
-        static_cast<__half*>(d_out), x->status, spins);
+    if (!wire16 && !out16) FWD_EB_COMBINE(float, float, false);
+    else if (!wire16 && out16) FWD_EB_COMBINE(float, __half, false);
+    else if (wire16 && !out16) FWD_EB_COMBINE(__half, float, false);
+    else FWD_EB_COMBINE(__half, __half, false);
   }
+#undef FWD_EB_COMBINE
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "combine kernel launch");
