@@ -2,23 +2,32 @@
 """Throughput of the EmbeddingBag gather-and-pool path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c3|c5|rowshard] [--exchange nccl|push]
+                    [--workload auto|c2|tablewise|rowshard|c5|c3] [--exchange push|a2a|nccl]
+                    [--wire f32|f16]
 
 One "step" is one pooled call over one synthetic batch.  Rank 0 prints ONE JSON line.
 
-N = 1   workload c2: table 1,000,000 x 128 fp16, 16384 bags, bag lengths Poisson(40)
-        clipped to [1,200], Zipf(1.05) indices, mean pooling.  `value` times K back-to-back
-        kernel launches over 8 rotating index batches resident in HBM; `e2e` times the same
-        calls through the host-buffer session (pinned host inputs copied in, result copied
-        out, every step); `roofline` is algorithmic bytes over the mean per-launch time;
-        `cpu_baseline` is torch CPU EmbeddingBag on the same batch on this host's cores.
-N > 1   workload rowshard (launched under torchrun, one rank per GPU): the c2 shape grown
-        with N — a table of N x 1,000,000 rows split by rows, rank r holding rows
-        [r*1e6, (r+1)*1e6), a global batch of N x 16384 bags that every rank scans, each
-        rank pooling the rows it owns into fp32 partial bags, partials combined by
-        reduce-scatter over NVLink (weak scaling: per-rank rows and per-rank lookups fixed).
---impl reference   times torch CPU EmbeddingBag (the ground truth of the reference's own
-        unit test and the CPU baseline the metric names) on the same workload, on rank 0.
+Workloads (all synthetic: shapes and distributions only, rotating index batches per table)
+  c2         N = 1.  Table 1,000,000 x 128 fp16, 16384 bags, lengths Poisson(40) clipped to
+             [1,200], Zipf(1.05) indices, mean pooling, fp16 output.
+  tablewise  N > 1 (launch under torchrun, one rank per GPU).  The c2 family grown with N: N
+             tables of the c2 shape, one per GPU, each looked up by its own c2 batch of 16384
+             bags; every rank pools its table for the whole batch and the pooled rows are
+             exchanged so that rank g ends with [16384/N, N, 128] (the all-to-all of pooled
+             outputs of table-wise placement).  Weak scaling: one table and one batch per GPU.
+  rowshard   N > 1.  ONE table of N x 1,000,000 rows split by rows, N x 16384 bags per step that
+             every rank scans; partial bags go to their owner ranks and are folded there.
+  c5         N >= 1.  Table 1,000,000,000 x 64 fp16 (128 GB) split by rows over N GPUs, 131072
+             bags of 1..100 uniform indices, sum.  Strong scaling.
+  c3         N = 1.  Table 4,000,000 x 256 fp16, 8192 bags of 0..64 uniform indices, 5 % of the
+             indices are padding_idx 0, max pooling.
+  auto       c2 at N = 1, tablewise at N > 1.
+
+`value` times K steps on data resident in HBM (CUDA events, barrier + synchronize on both sides,
+max over ranks); `roofline` is the pooling kernel's algorithmic bytes over its mean event time;
+`e2e` repeats the steps with inputs copied from pinned host memory and results copied back every
+step; `cpu_baseline` / `--impl reference` time torch CPU EmbeddingBag (the ground truth of the
+reference's own unit test and the CPU baseline the metric names) on the same workload.
 """
 from __future__ import annotations
 
@@ -38,8 +47,10 @@ if ROOT not in sys.path:
 NUM_BATCHES = 8
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the pooling kernel, from the ncu
 # captures summarised under profiles/ (None where no capture of that workload exists yet).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 35.9e6, "rowshard": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 35.9e6, "tablewise": None, "rowshard": None, "c5": None, "c3": None}
 C2 = dict(rows=1_000_000, dim=128, bags=16384)
+C5 = dict(rows=1_000_000_000, dim=64, bags=131072)
+C3 = dict(rows=4_000_000, dim=256, bags=8192)
 
 
 # ---- clocks --------------------------------------------------------------------------
@@ -48,7 +59,6 @@ class ClockSampler:
     """Polls NVML for SM clock and throttle reasons while the timed region runs."""
 
     def __init__(self, index: int):
-        self.index = index
         self.samples = []
         self.reasons = set()
         self.max_mhz = None
@@ -102,9 +112,8 @@ class ClockSampler:
 
 
 def measured_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
-        with open(path) as f:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
@@ -112,7 +121,17 @@ def measured_peak():
 
 # ---- workload construction -------------------------------------------------------------
 
-def make_batches(total_rows: int, total_bags: int, seed: int):
+def resolve_workload(name: str, world: int) -> str:
+    if name == "auto":
+        return "c2" if world == 1 else "tablewise"
+    if name in ("c2", "c3") and world != 1:
+        raise SystemExit(f"workload {name} is a single-GPU workload")
+    if name in ("tablewise", "rowshard") and world == 1:
+        raise SystemExit(f"workload {name} needs more than one GPU (launch under torchrun)")
+    return name
+
+
+def c2_batches(total_rows: int, total_bags: int, seed: int):
     from forward_b200 import workloads
     rng = np.random.default_rng(seed)
     sampler = workloads.ZipfSampler(total_rows, 1.05, rng)
@@ -120,85 +139,168 @@ def make_batches(total_rows: int, total_bags: int, seed: int):
                                    rng=rng) for _ in range(NUM_BATCHES)]
 
 
-def algorithmic_bytes(bags, dim, gathered, out_itemsize, table_itemsize=2):
+def make_batches(workload: str, world: int, table_id: int = 0):
+    """The batches one table sees.  Every rank draws the same batches for a shared table."""
     from forward_b200 import workloads
-    return workloads.algorithmic_bytes(
-        gathered_rows=gathered, dim=dim, table_itemsize=table_itemsize,
-        num_indices=bags.num_indices, num_offsets=bags.num_bags, index_itemsize=4,
-        num_bags=bags.num_bags, out_itemsize=out_itemsize)
+    if workload == "c2":
+        return c2_batches(C2["rows"], C2["bags"], seed=1)
+    if workload == "tablewise":
+        return c2_batches(C2["rows"], C2["bags"], seed=1 + 7919 * table_id)
+    if workload == "rowshard":
+        return c2_batches(C2["rows"] * world, C2["bags"] * world, seed=1)
+    if workload == "c5":
+        return [workloads.config5_bags(seed=4 + b) for b in range(4)]
+    if workload == "c3":
+        return [workloads.config3_bags(seed=2 + b) for b in range(NUM_BATCHES)]
+    raise ValueError(workload)
+
+
+def table_seed(workload: str, table_id: int) -> tuple[int, float]:
+    """(seed, scale) of the counter-generated table."""
+    if workload in ("c2", "tablewise"):
+        return 1 + table_id, 0.1
+    if workload == "rowshard":
+        return 1, 0.1
+    if workload == "c5":
+        return 4, 0.05
+    return 2, 0.1
+
+
+def describe(workload: str, world: int, args):
+    base = {"l2_policy": "no flush: table (shard) larger than the 126 MB L2 and rotating index "
+                         "batches; skewed laws keep their hot rows cached, which is a property "
+                         "of the workload"}
+    if workload == "c2":
+        base.update(workload="c2: EmbeddingBag mean, table 1000000x128 fp16, 16384 bags/step, lengths "
+                             "Poisson(40) clipped [1,200], Zipf(1.05) indices",
+                    bags_per_step=C2["bags"], table_rows=C2["rows"], dim=C2["dim"], parallelism="single")
+    elif workload == "tablewise":
+        base.update(workload=f"tablewise: {world} tables of the c2 shape (1000000x128 fp16, mean), one "
+                             f"per GPU, each with its own 16384-bag c2 batch per step; pooled rows "
+                             f"exchanged to [16384/{world}, {world}, 128] per rank",
+                    bags_per_step=C2["bags"] * world, table_rows=C2["rows"] * world, dim=C2["dim"],
+                    parallelism=f"tablewise{world}", exchange=args.exchange)
+    elif workload == "rowshard":
+        base.update(workload=f"rowshard: one table {world}x1000000x128 fp16 split by rows, {world}x16384 "
+                             "bags/step scanned by every rank, partial bags folded at their owners",
+                    bags_per_step=C2["bags"] * world, table_rows=C2["rows"] * world, dim=C2["dim"],
+                    parallelism=f"rowshard{world}", exchange=args.exchange, wire=args.wire)
+    elif workload == "c5":
+        base.update(workload="c5: EmbeddingBag sum, table 1000000000x64 fp16 (128 GB) split by rows, "
+                             "131072 bags/step of 1..100 uniform indices",
+                    bags_per_step=C5["bags"], table_rows=C5["rows"], dim=C5["dim"],
+                    parallelism=f"rowshard{world}" if world > 1 else "single",
+                    exchange=args.exchange if world > 1 else None, wire=args.wire)
+    elif workload == "c3":
+        base.update(workload="c3: EmbeddingBag max, table 4000000x256 fp16, 8192 bags/step of 0..64 "
+                             "uniform indices, 5% padding_idx=0",
+                    bags_per_step=C3["bags"], table_rows=C3["rows"], dim=C3["dim"], parallelism="single")
+    return base
+
+
+def scaling_kind(workload: str) -> str:
+    return "strong" if workload == "c5" else "weak"
 
 
 # ---- CPU arms ----------------------------------------------------------------------------
 
-def cpu_embedding_bag_rate(table_np, batches, budget_s: float, min_reps: int = 3):
-    """torch CPU EmbeddingBag (mean, fp16 table) on whole batches; lookups per second."""
-    import torch
-
-    from oracle import eb_oracle as O
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    t = torch.from_numpy(table_np)
-    prepared = [(torch.from_numpy(b.indices.astype(np.int64)),
-                 torch.from_numpy(b.offsets.astype(np.int64)), b.num_indices) for b in batches]
-    import torch.nn.functional as F
-    for i, o, _ in prepared[:2]:
-        F.embedding_bag(i, t, o, mode="mean")
-    assert O.MODE_MEAN == 1
-    done, lookups, reps = 0.0, 0, 0
-    while reps < min_reps or done < budget_s:
-        i, o, n = prepared[reps % len(prepared)]
-        t0 = time.perf_counter()
-        F.embedding_bag(i, t, o, mode="mean")
-        done += time.perf_counter() - t0
-        lookups += n
-        reps += 1
-    return lookups / done, cores, reps, done
-
-
-def host_table(rows: int, dim: int, row_lo: int = 0):
+def host_table(rows: int, dim: int, row_lo: int, seed: int, scale: float):
     """The counter-generated table on the host (same bits as the device fill)."""
     from oracle import eb_oracle as O
     out = np.empty((rows, dim), dtype=np.float16)
     step = 1 << 16
     for lo in range(0, rows, step):
         n = min(step, rows - lo)
-        out[lo:lo + n] = O.table_rows(np.arange(lo, lo + n, dtype=np.int64) + row_lo, dim, seed=1,
-                                      scale=0.1, dtype=np.float16)
+        out[lo:lo + n] = O.table_rows(np.arange(lo, lo + n, dtype=np.int64) + row_lo, dim, seed=seed,
+                                      scale=scale, dtype=np.float16)
     return out
+
+
+class CpuWorkload:
+    """torch CPU EmbeddingBag over the same tables and batches; one call of `step` = one bench
+    step (all tables).  A table too large for host memory is replaced by a 2**27-row stand-in
+    with the indices folded into it (same lookups; said so in `sample`)."""
+
+    def __init__(self, workload: str, world: int):
+        import torch
+        import torch.nn.functional as F
+        self.F = F
+        self.cores = os.cpu_count() or 1
+        torch.set_num_threads(self.cores)
+        self.note = ""
+        self.mode, self.pad = "mean", None
+        if workload in ("c2", "tablewise"):
+            n_tab = 1 if workload == "c2" else world
+            self.tables = [torch.from_numpy(host_table(C2["rows"], C2["dim"], 0, *table_seed(workload, t)))
+                           for t in range(n_tab)]
+            self.batches = [make_batches(workload, world, t) for t in range(n_tab)]
+        elif workload == "rowshard":
+            self.tables = [torch.from_numpy(host_table(C2["rows"] * world, C2["dim"], 0, 1, 0.1))]
+            self.batches = [make_batches(workload, world)]
+        elif workload == "c5":
+            rows = 1 << 27
+            self.tables = [torch.from_numpy(host_table(rows, C5["dim"], 0, 4, 0.05))]
+            bs = make_batches(workload, world)
+            for b in bs:
+                b.indices %= rows
+            self.batches = [bs]
+            self.mode = "sum"
+            self.note = " (table cut to 2^27 rows, indices folded into it: same lookups)"
+        elif workload == "c3":
+            self.tables = [torch.from_numpy(host_table(C3["rows"], C3["dim"], 0, 2, 0.1))]
+            self.batches = [make_batches(workload, world)]
+            self.mode, self.pad = "max", 0
+        self.prepared = [[(torch.from_numpy(b.indices.astype(np.int64)),
+                           torch.from_numpy(b.offsets.astype(np.int64))) for b in bs]
+                         for bs in self.batches]
+
+    def step(self, k: int) -> int:
+        done = 0
+        for t, table in enumerate(self.tables):
+            nb = len(self.prepared[t])
+            i, o = self.prepared[t][k % nb]
+            self.F.embedding_bag(i, table, o, mode=self.mode, padding_idx=self.pad)
+            done += self.batches[t][k % nb].num_indices
+        return done
+
+
+def cpu_baseline(workload: str, world: int, budget_s: float):
+    cw = CpuWorkload(workload, world)
+    for k in range(2):
+        cw.step(k)
+    secs, lookups, reps = 0.0, 0, 0
+    while reps < 3 or secs < budget_s:
+        t0 = time.perf_counter()
+        n = cw.step(reps)
+        secs += time.perf_counter() - t0
+        lookups += n
+        reps += 1
+    return {"value": lookups / secs, "unit": "lookups/s", "cores": cw.cores, "kind": "port",
+            "sample": f"torch CPU EmbeddingBag on whole {workload} steps{cw.note}: {reps} steps, "
+                      f"{secs:.1f} s"}
 
 
 def run_reference(args, world: int, rank: int):
     if rank != 0:
         return
-    total_rows, total_bags = C2["rows"] * world, C2["bags"] * world
-    batches = make_batches(total_rows, total_bags, seed=1)
-    import torch
-    table = host_table(total_rows, C2["dim"])
-    import torch.nn.functional as F
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    t = torch.from_numpy(table)
-    prepared = [(torch.from_numpy(b.indices.astype(np.int64)),
-                 torch.from_numpy(b.offsets.astype(np.int64)), b.num_indices) for b in batches]
+    workload = resolve_workload(args.workload, world)
+    cw = CpuWorkload(workload, world)
     for k in range(args.warmup):
-        i, o, _ = prepared[k % NUM_BATCHES]
-        F.embedding_bag(i, t, o, mode="mean")
+        cw.step(k)
     lookups = 0
     t0 = time.perf_counter()
     for k in range(args.steps):
-        i, o, n = prepared[k % NUM_BATCHES]
-        F.embedding_bag(i, t, o, mode="mean")
-        lookups += n
+        lookups += cw.step(k)
     dt = time.perf_counter() - t0
     value = lookups / dt
     line = {
         "impl": "reference", "metric": "pooled_lookups_per_sec", "value": value,
         "unit": "lookups/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": workload_config(world),
-        "cpu_baseline": {"value": value, "unit": "lookups/s", "cores": cores, "kind": "port",
-                         "sample": "torch CPU EmbeddingBag (mean, fp16 table), whole batches, "
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": scaling_kind(workload), "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": describe(workload, world, args),
+        "cpu_baseline": {"value": value, "unit": "lookups/s", "cores": cw.cores, "kind": "port",
+                         "sample": f"torch CPU EmbeddingBag on whole {workload} steps{cw.note}, "
                                    f"{args.steps} steps"},
         "e2e": {"value": value, "unit": "lookups/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
@@ -206,111 +308,194 @@ def run_reference(args, world: int, rank: int):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(world: int):
-    if world == 1:
-        return {"workload": "c2: EmbeddingBag mean, table 1000000x128 fp16, 16384 bags/step, "
-                            "lengths Poisson(40) clipped [1,200], Zipf(1.05) indices",
-                "bags_per_step": C2["bags"], "table_rows": C2["rows"], "dim": C2["dim"],
-                "l2_policy": "no flush: 256 MB table (> 126 MB L2) and 8 rotating index batches",
-                "parallelism": "single"}
-    return {"workload": f"rowshard: c2 shape grown x{world}: table {world}x1000000x128 fp16 split "
-                        f"by rows, {world}x16384 bags/step scanned by every rank, partial bags "
-                        "pushed to their owner ranks over NVLink and folded there",
-            "bags_per_step": C2["bags"] * world, "table_rows": C2["rows"] * world,
-            "dim": C2["dim"],
-            "l2_policy": "no flush: 256 MB table shard per GPU (> 126 MB L2), 8 rotating batches",
-            "parallelism": f"rowshard{world}"}
-
-
 # ---- GPU arm ------------------------------------------------------------------------------
+
+class GpuWorkload:
+    """Device-resident table, batches and the step closure of one workload on this rank."""
+
+    def __init__(self, workload: str, world: int, rank: int, dev, args):
+        import torch
+
+        from forward_b200 import capi
+        from forward_b200 import dist as fd
+        self.workload, self.world, self.rank, self.dev, self.args = workload, world, rank, dev, args
+        self.capi, self.fd, self.torch = capi, fd, torch
+        self.bag = None
+        self.pool_only = None
+        self.out_itemsize = 2
+        self.row_lo = 0
+        local_filter = None
+        if workload in ("c2", "tablewise"):
+            self.dim, rows, self.mode, self.pad = C2["dim"], C2["rows"], capi.MODE_MEAN, -1
+            self.batches = make_batches(workload, world, rank)
+        elif workload == "rowshard":
+            self.dim, rows, self.mode, self.pad = C2["dim"], C2["rows"], capi.MODE_MEAN, -1
+            self.row_lo = rank * rows
+            self.batches = make_batches(workload, world)
+            local_filter = (self.row_lo, self.row_lo + rows)
+        elif workload == "c5":
+            self.dim, self.mode, self.pad = C5["dim"], capi.MODE_SUM, -1
+            self.row_lo, rows = fd.shard_rows(C5["rows"], world, rank)
+            self.batches = make_batches(workload, world)
+            local_filter = (self.row_lo, self.row_lo + rows) if world > 1 else None
+        else:
+            self.dim, rows, self.mode, self.pad = C3["dim"], C3["rows"], capi.MODE_MAX, 0
+            self.batches = make_batches(workload, world)
+        seed, scale = table_seed(workload, rank)
+        self.table = torch.empty((rows, self.dim), dtype=torch.float16, device=dev)
+        capi.fill_table(self.table, self.row_lo, seed=seed, scale=scale)
+        self.nb = len(self.batches)
+        self.d_batches = [(torch.from_numpy(b.indices).to(dev), torch.from_numpy(b.offsets).to(dev))
+                          for b in self.batches]
+        self.gathered = []
+        for b in self.batches:
+            keep = np.ones(b.num_indices, dtype=bool)
+            if self.pad >= 0:
+                keep &= b.indices != self.pad
+            if local_filter:
+                keep &= (b.indices >= local_filter[0]) & (b.indices < local_filter[1])
+            self.gathered.append(int(np.count_nonzero(keep)))
+        self._last = None
+        self._build_step()
+
+    def _build_step(self):
+        torch, capi, fd, args = self.torch, self.capi, self.fd, self.args
+        dev = self.dev
+        stream = torch.cuda.current_stream()
+        bags_n = self.batches[0].num_bags
+        if self.world == 1:
+            out = torch.empty((bags_n, self.dim), dtype=torch.float16, device=dev)
+            params = [capi.make_params(self.table, i, o, out=out, mode=self.mode, padding_idx=self.pad)
+                      for i, o in self.d_batches]
+            self._params = params
+
+            def step(k, events=None):
+                if events:
+                    events[0].record()
+                capi.forward(self._params[k % self.nb], stream.cuda_stream)
+                if events:
+                    events[1].record()
+                self._last = out
+            self.step = step
+            return
+        if self.workload == "tablewise":
+            self.bag = fd.TableWiseBags({self.rank: self.table}, list(range(self.world)), dim=self.dim,
+                                        max_bags=bags_n, exchange=args.exchange, wire_dtype=capi.F16,
+                                        mode=self.mode)
+            self.out_itemsize = 2 if args.exchange == "push" else 4
+
+            def step(k, events=None):
+                i, o = self.d_batches[k % self.nb]
+                self._last = self.bag.forward({self.rank: (i, o, None)}, pool_events=events)
+        else:
+            wire = capi.F16 if args.wire == "f16" else capi.F32
+            self.bag = fd.RowShardedBag(self.table, self.row_lo, mode=self.mode, max_bags=bags_n,
+                                        exchange=args.exchange, wire_dtype=wire)
+            self.out_itemsize = 2 if (args.exchange == "push" and args.wire == "f16") else 4
+
+            def step(k, events=None):
+                i, o = self.d_batches[k % self.nb]
+                self._last = self.bag.forward(i, o, pool_events=events)
+        self.step = step
+        # the same pooling without any exchange, for the overhead figure
+        local_dtype = torch.float16 if self.workload == "tablewise" else torch.float32
+        local_out = torch.empty((bags_n, self.dim), dtype=local_dtype, device=dev)
+
+        def pool_only(k):
+            i, o = self.d_batches[k % self.nb]
+            p = capi.make_params(self.table, i, o, out=local_out, mode=self.mode,
+                                 padding_idx=self.pad, row_lo=self.row_lo)
+            capi.forward(p, stream.cuda_stream)
+        self.pool_only = pool_only
+
+    def set_device_batches(self, d_batches):
+        """Point the step at other device copies of the same batches (the e2e loop's)."""
+        self.d_batches = d_batches
+        if self.world == 1:
+            out = self._last if self._last is not None else self.torch.empty(
+                (self.batches[0].num_bags, self.dim), dtype=self.torch.float16, device=self.dev)
+            self._params = [self.capi.make_params(self.table, i, o, out=out, mode=self.mode,
+                                                  padding_idx=self.pad) for i, o in d_batches]
+
+    def result(self):
+        return self._last
+
+    def lookups(self, k: int) -> int:
+        """Lookups of step k on the table(s) this rank's batches address."""
+        return self.batches[k % self.nb].num_indices
+
+    def algorithmic_bytes(self, k: int) -> float:
+        from forward_b200 import workloads
+        b = self.batches[k % self.nb]
+        return workloads.algorithmic_bytes(
+            gathered_rows=self.gathered[k % self.nb], dim=self.dim, table_itemsize=2,
+            num_indices=b.num_indices, num_offsets=b.num_bags, index_itemsize=4,
+            num_bags=b.num_bags, out_itemsize=self.out_itemsize)
+
+
+def total_lookups(wl, steps: int, dev) -> float:
+    """Whole-job lookups over `steps` steps: table-wise ranks each look up their own table."""
+    n = float(sum(wl.lookups(k) for k in range(steps)))
+    if wl.world > 1 and wl.workload == "tablewise":
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([n], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        n = float(t.item())
+    return n
+
 
 def run_ours(args, world: int, rank: int, local_rank: int):
     import torch
 
     from forward_b200 import capi
-    from forward_b200 import dist as fd
     if not torch.cuda.is_available():
         raise RuntimeError("bench.py needs a CUDA device: the package has no CPU path")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     dist = None
-    sharded = world > 1
-    if sharded:
+    multi = world > 1
+    if multi:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-
-    dim = C2["dim"]
-    rows_local = C2["rows"]
-    row_lo = rank * rows_local
-    total_rows, total_bags = rows_local * world, C2["bags"] * world
-    batches = make_batches(total_rows, total_bags, seed=1)
-    table = torch.empty((rows_local, dim), dtype=torch.float16, device=dev)
-    capi.fill_table(table, row_lo, seed=1, scale=0.1)
-    d_batches = [(torch.from_numpy(b.indices).to(dev), torch.from_numpy(b.offsets).to(dev))
-                 for b in batches]
-    lookups_global = [b.num_indices for b in batches]
-    gathered_local = [int(np.count_nonzero((b.indices >= row_lo) & (b.indices < row_lo + rows_local)))
-                      for b in batches]
-    stream = torch.cuda.current_stream()
+    workload = resolve_workload(args.workload, world)
+    wl = GpuWorkload(workload, world, rank, dev, args)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps)]
 
-    if sharded:
-        wire = capi.F16 if args.wire == "f16" else capi.F32
-        bag = fd.RowShardedBag(table, row_lo, mode=capi.MODE_MEAN, max_bags=total_bags,
-                               exchange=args.exchange, wire_dtype=wire)
-        local_out = torch.empty((total_bags, dim), dtype=torch.float32, device=dev)
-        local_params = [capi.make_params(table, i, o, out=local_out, mode=capi.MODE_MEAN, row_lo=row_lo)
-                        for i, o in d_batches]
-
-        def step(k: int, timed: bool = False):
-            i, o = d_batches[k % NUM_BATCHES]
-            bag.forward(i, o, pool_events=(ev[2 * k], ev[2 * k + 1]) if timed else None)
-    else:
-        out = torch.empty((total_bags, dim), dtype=torch.float16, device=dev)
-        params = [capi.make_params(table, i, o, out=out, mode=capi.MODE_MEAN) for i, o in d_batches]
-
-        def step(k: int, timed: bool = False):
-            if timed:
-                ev[2 * k].record()
-            capi.forward(params[k % NUM_BATCHES], stream.cuda_stream)
-            if timed:
-                ev[2 * k + 1].record()
-
     def barrier():
-        if sharded:
+        if multi:
             dist.barrier()
         torch.cuda.synchronize()
 
     # bring clocks up before the counted warm-up; a fixed count when ranks must stay in step
-    if sharded:
-        for k in range(int(args.preheat_ms * 5)):      # ~80 us a step: about the same duration
-            step(k)
+    if multi:
+        for k in range(int(args.preheat_ms * 4)):
+            wl.step(k)
             if k % 64 == 63:
                 torch.cuda.synchronize()
     else:
         t_end = time.perf_counter() + args.preheat_ms * 1e-3
         k = 0
         while time.perf_counter() < t_end:
-            step(k)
+            wl.step(k)
             k += 1
             if k % 64 == 0:
                 torch.cuda.synchronize()
     pool_only_us = None
-    if sharded:
-        # the same pooling without any exchange, for the overhead figure
+    if wl.pool_only:
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for k in range(20):
-            capi.forward(local_params[k % NUM_BATCHES], stream.cuda_stream)
+            wl.pool_only(k)
         n_po = max(20, min(args.steps, 200))
         a.record()
         for k in range(n_po):
-            capi.forward(local_params[k % NUM_BATCHES], stream.cuda_stream)
+            wl.pool_only(k)
         b.record()
         torch.cuda.synchronize()
         pool_only_us = a.elapsed_time(b) * 1e3 / n_po
     for k in range(args.warmup):
-        step(k)
+        wl.step(k)
     barrier()
 
     sampler = ClockSampler(local_rank)
@@ -319,126 +504,128 @@ def run_ours(args, world: int, rank: int, local_rank: int):
     sampler.start()
     t_begin.record()
     for k in range(args.steps):
-        step(k, timed=True)
+        wl.step(k, events=(ev[2 * k], ev[2 * k + 1]))
     t_finish.record()
     barrier()
     clocks = sampler.stop()
     launches = capi.lib().fwd_eb_launch_count() - launches0
     total_ms = t_begin.elapsed_time(t_finish)
     kernel_ms = np.array([ev[2 * k].elapsed_time(ev[2 * k + 1]) for k in range(args.steps)])
+    lookups = total_lookups(wl, args.steps, dev)
     exchange = None
-    if sharded:
-        if bag.check_status() != 0:
+    if multi:
+        if wl.bag.check_status() != 0:
             raise RuntimeError("a bounded flag wait gave up during the timed region")
         tt = torch.tensor([total_ms, pool_only_us], dtype=torch.float64, device=dev)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         total_ms, pool_only_us = float(tt[0].item()), float(tt[1].item())
         step_us = total_ms * 1e3 / args.steps
-        wire_bytes = 2 if (args.exchange == "push" and args.wire == "f16") else 4
-        egress = C2["bags"] * (world - 1) * dim * wire_bytes      # per rank per step
-        exchange = {"method": args.exchange, "wire": args.wire if args.exchange == "push" else "f32",
+        bags_n = wl.batches[0].num_bags
+        egress = bags_n * (world - 1) // world * wl.dim * wl.out_itemsize
+        exchange = {"method": args.exchange, "wire": "f16" if wl.out_itemsize == 2 else "f32",
                     "pool_only_us": pool_only_us, "step_us": step_us,
                     "overhead_frac": (step_us - pool_only_us) / pool_only_us,
-                    "nvlink_egress_bytes_per_rank": egress,
+                    "nvlink_egress_bytes_per_rank": int(egress),
                     "nvlink_floor_us_at_770GBs": egress / 770e9 * 1e6}
-    lookups = sum(lookups_global[k % NUM_BATCHES] for k in range(args.steps))
     value = lookups / (total_ms * 1e-3)
 
-    # roofline of the pooling kernel on this rank
-    out_item = (2 if (sharded and args.exchange == "push" and args.wire == "f16") else 4) if sharded else 2
-    alg = np.mean([algorithmic_bytes(batches[k % NUM_BATCHES], dim, gathered_local[k % NUM_BATCHES],
-                                     out_item) for k in range(args.steps)])
+    alg = float(np.mean([wl.algorithmic_bytes(k) for k in range(args.steps)]))
     peak, peak_kind = measured_peak()
     achieved = alg / (kernel_ms.mean() * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get("rowshard" if sharded else "c2"),
+                "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(workload),
                 "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
                 "kernel_us_mean": float(kernel_ms.mean() * 1e3),
                 "kernel_us_median": float(np.median(kernel_ms) * 1e3),
-                "algorithmic_bytes_per_launch": float(alg)}
+                "algorithmic_bytes_per_launch": alg}
 
+    verified = None if args.no_verify else verify(wl, workload, world, rank)
     e2e = None
-    cpu = None
     if not args.no_e2e:
-        e2e = run_e2e_sharded(args, batches, bag, rank, world, dev) if sharded else \
-            run_e2e(args, batches, table)
-    if rank == 0 and not sharded and not args.no_cpu_baseline:
-        tab = host_table(rows_local, dim)
-        rate, cores, reps, secs = cpu_embedding_bag_rate(tab, batches, budget_s=args.cpu_seconds)
-        cpu = {"value": rate, "unit": "lookups/s", "cores": cores, "kind": "port",
-               "sample": f"torch CPU EmbeddingBag (mean, fp16 table) on whole c2 batches: {reps} "
-                         f"calls, {secs:.1f} s"}
+        e2e = run_e2e_multi(args, wl, rank, world, dev) if multi else run_e2e(args, wl)
+    cpu = None
+    if rank == 0 and not multi and not args.no_cpu_baseline:
+        cpu = cpu_baseline(workload, world, args.cpu_seconds)
 
     if rank == 0:
         line = {
             "metric": "pooled_lookups_per_sec", "value": value, "unit": "lookups/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": workload_config(world), "roofline": roofline, "cpu_baseline": cpu,
-            "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+            "scaling": scaling_kind(workload), "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": describe(workload, world, args), "roofline": roofline,
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "verified_against_oracle": verified,
         }
         if exchange:
             line["exchange"] = exchange
         print(json.dumps(line), flush=True)
-    if sharded:
-        bag.close()
+    if multi:
+        wl.bag.close()
         dist.destroy_process_group()
 
 
-def run_e2e_sharded(args, batches, bag, rank, world, dev):
-    """N > 1: every step copies the whole batch from pinned host memory to this rank's GPU, runs
-    the sharded call and copies this rank's slice of the result back to pinned memory."""
-    import torch
-    import torch.distributed as dist
-    host = [(torch.from_numpy(b.indices).pin_memory(), torch.from_numpy(b.offsets).pin_memory())
-            for b in batches]
-    d_idx = [torch.empty_like(i, device=dev) for i, _ in host]
-    d_off = [torch.empty_like(o, device=dev) for _, o in host]
-    per = C2["bags"]
-    h_out = [torch.empty((per, C2["dim"]), dtype=torch.float32).pin_memory() for _ in range(NUM_BATCHES)]
-
-    def step(k):
-        j = k % NUM_BATCHES
-        d_idx[j].copy_(host[j][0], non_blocking=True)
-        d_off[j].copy_(host[j][1], non_blocking=True)
-        res = bag.forward(d_idx[j], d_off[j])
-        h_out[j][:res.shape[0]].copy_(res, non_blocking=True)
-
-    for k in range(max(args.warmup, 3)):
-        step(k)
-    dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for k in range(args.steps):
-        step(k)
-    torch.cuda.synchronize()
-    dt = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
-    dist.all_reduce(dt, op=dist.ReduceOp.MAX)
-    dt = float(dt.item())
-    lookups = sum(batches[k % NUM_BATCHES].num_indices for k in range(args.steps))
-    h2d = int(np.mean([b.num_indices * 4 + b.num_bags * 4 for b in batches]))
-    return {"value": lookups / dt, "unit": "lookups/s", "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": per * C2["dim"] * 4, "ms_per_step": dt / args.steps * 1e3,
-            "note": "bytes are per rank; every rank receives the whole batch",
-            "api": "forward_b200.dist.RowShardedBag.forward"}
-
-
-def run_e2e(args, batches, table):
-    """Same calls through the host-buffer session: pinned inputs in, result out, each step."""
+def verify(wl, workload, world, rank):
+    """One more step after the timed region, checked on every rank against the CPU oracle on a
+    sample of the bags that rank ends up with (all ranks must agree for `true`)."""
     import torch
 
-    from forward_b200 import capi
+    from oracle import eb_oracle as O
+    wl.step(0)
+    torch.cuda.synchronize()
+    got = wl.result().float().cpu().numpy()
+    b = wl.batches[0]
+    bags_n = b.num_bags
+    per = -(-bags_n // world)
+    lo = rank * per if world > 1 else 0
+    stride = max(1, per // 512)
+    take = np.arange(lo, min(lo + per, bags_n))[::stride]
+    ends = np.append(b.offsets, b.num_indices).astype(np.int64)
+    idx = np.concatenate([b.indices[ends[t]:ends[t + 1]] for t in take])
+    lens = np.array([ends[t + 1] - ends[t] for t in take])
+    offs = np.zeros(take.size, dtype=np.int32)
+    offs[1:] = np.cumsum(lens[:-1])
+    uniq, inv = np.unique(idx, return_inverse=True)
+    seed, scale = table_seed(workload, rank)
+    compact = O.table_rows(uniq, wl.dim, seed=seed, scale=scale, dtype=np.float16)
+    pad = -1
+    if wl.pad >= 0:
+        hit = int(np.searchsorted(uniq, wl.pad))
+        pad = hit if hit < uniq.size and uniq[hit] == wl.pad else -1
+    mode = {wl.capi.MODE_MEAN: O.MODE_MEAN, wl.capi.MODE_SUM: O.MODE_SUM,
+            wl.capi.MODE_MAX: O.MODE_MAX}[wl.mode]
+    exp = O.pool(compact, inv.astype(np.int32), offs, mode=mode, padding_idx=pad, out_dtype=np.float32)
+    if workload == "tablewise":
+        mine = got[take - lo, rank, :]        # column block of this rank's own table
+    else:
+        mine = got[take - lo]
+    ok = bool(np.allclose(mine, exp, rtol=2e-3, atol=2e-3))
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([1 if ok else 0], device=wl.dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        ok = bool(t.item())
+    return ok
+
+
+def run_e2e(args, wl):
+    """N = 1: the same calls through the host-buffer session: pinned inputs in, result out, each
+    step, `depth` calls in flight."""
+    import torch
+
     from forward_b200.session import Session
+    capi = wl.capi
     depth = 4
-    max_n = max(b.num_indices for b in batches)
-    s = Session(table_dtype=capi.F16, dim=C2["dim"], num_rows=C2["rows"], mode=capi.MODE_MEAN,
-                max_indices=max_n, max_bags=C2["bags"], depth=depth, external_table=True)
-    s.adopt_table(table.data_ptr())
+    max_n = max(b.num_indices for b in wl.batches)
+    bags_n = wl.batches[0].num_bags
+    s = Session(table_dtype=capi.F16, dim=wl.dim, num_rows=wl.table.shape[0], mode=wl.mode,
+                max_indices=max_n, max_bags=bags_n, depth=depth, external_table=True,
+                padding_idx=wl.pad)
+    s.adopt_table(wl.table.data_ptr())
     views = [s.slot(k) for k in range(depth)]
     sizes = []
     for k in range(depth):       # slot k carries batch k; its copy-in still happens every step
-        b = batches[k % NUM_BATCHES]
+        b = wl.batches[k % wl.nb]
         views[k][0][:b.num_indices] = b.indices
         views[k][1][:b.num_bags] = b.offsets
         sizes.append((b.num_indices, b.num_bags))
@@ -468,19 +655,65 @@ def run_e2e(args, batches, table):
             "calls_in_flight": depth, "api": "fwd_eb_session_submit / fwd_eb_session_wait"}
 
 
+def run_e2e_multi(args, wl, rank, world, dev):
+    """N > 1: every step copies this rank's batch from pinned host memory to its GPU, runs the
+    multi-GPU call and copies this rank's slice of the result back to pinned memory."""
+    import torch
+    import torch.distributed as dist
+    host = [(torch.from_numpy(b.indices).pin_memory(), torch.from_numpy(b.offsets).pin_memory())
+            for b in wl.batches]
+    d_idx = [torch.empty_like(i, device=dev) for i, _ in host]
+    d_off = [torch.empty_like(o, device=dev) for _, o in host]
+    wl.step(0)
+    torch.cuda.synchronize()
+    shape, dtype = tuple(wl.result().shape), wl.result().dtype
+    h_out = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(wl.nb)]
+    saved = wl.d_batches
+    wl.set_device_batches(list(zip(d_idx, d_off)))
+
+    def step(k):
+        j = k % wl.nb
+        d_idx[j].copy_(host[j][0], non_blocking=True)
+        d_off[j].copy_(host[j][1], non_blocking=True)
+        wl.step(k)
+        h_out[j].copy_(wl.result(), non_blocking=True)
+
+    for k in range(max(args.warmup, 3)):
+        step(k)
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for k in range(args.steps):
+        step(k)
+    torch.cuda.synchronize()
+    stats = torch.tensor([time.perf_counter() - t0], dtype=torch.float64, device=dev)
+    dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    dt = float(stats.item())
+    wl.set_device_batches(saved)
+    lookups = total_lookups(wl, args.steps, dev)
+    h2d = int(np.mean([b.num_indices * 4 + b.num_bags * 4 for b in wl.batches]))
+    d2h = int(np.prod(shape)) * h_out[0].element_size()
+    return {"value": lookups / dt, "unit": "lookups/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": dt / args.steps * 1e3,
+            "note": "bytes are per rank", "api": "forward_b200.dist forward()"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto",
+                    choices=["auto", "c2", "tablewise", "rowshard", "c5", "c3"])
+    ap.add_argument("--exchange", default="push", choices=["push", "a2a", "nccl"],
+                    help="N>1: how pooled rows / partial bags reach their owners")
+    ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
+                    help="row shards with --exchange push: element type of the partials on NVLink")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-verify", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--exchange", default="push", choices=["push", "a2a", "nccl"],
-                    help="N>1: how partial bags reach their owners")
-    ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
-                    help="N>1 with --exchange push: element type of the partials on NVLink")
     ap.add_argument("--preheat-ms", type=float, default=400.0,
                     help="untimed launches before the counted warm-up, to bring clocks up")
     args = ap.parse_args()
@@ -488,10 +721,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.gpus != world:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run "
-                             "(--nproc-per-node N)")
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run "
+                         "(--nproc-per-node N)")
     if args.impl == "reference":
         run_reference(args, world, rank)
         return

@@ -291,7 +291,8 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
   q.strategy = FWD_EB_STRATEGY_GROUP;
   q.out = x->peer_slots[x->rank];
   q.out_dtype = x->wire_dtype;
-  q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean torch would round
+  if (x->layout == FWD_EB_LAYOUT_ROW_SHARD)
+    q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean torch would round
   q.out_stride = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (int64_t)x->num_tables * p->dim : 0;
   PoolArgs a;
   int vec = 0, cpl = 0, tiles = 0;

@@ -353,15 +353,18 @@ class TableWiseBags:
             self.out_splits = [self.per * c for c in counts]
             self.by_src = [[t for t, r in enumerate(owner) if r == src] for src in range(self.world)]
 
-    def forward(self, inputs: dict):
+    def forward(self, inputs: dict, pool_events=None):
         """inputs[t] = (indices, offsets_or_None, weights_or_None) for every table this rank owns.
-        Returns [per, T, dim] (rows past the bags this rank owns are unspecified)."""
+        Returns [per, T, dim] (rows past the bags this rank owns are unspecified).  `pool_events`
+        = (start, end) CUDA events recorded around the pooling launches."""
         import torch
         import torch.distributed as dist
         stream = capi.current_stream_ptr()
         if self.exchange == "push":
             self.epoch += 1
             self.x.epoch = self.epoch
+            if pool_events:
+                pool_events[0].record()
             for k, t in enumerate(self.mine):
                 idx, off, w = inputs[t]
                 # `out` is ignored by the push entry point; any CUDA tensor satisfies the binding
@@ -370,6 +373,8 @@ class TableWiseBags:
                                      padding_idx=self.padding_idx)
                 self.x.table_index = t
                 capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
+            if pool_events:
+                pool_events[1].record()
             res = C.c_void_p()
             capi.check(_lib().fwd_eb_shard_wait(C.byref(self.x), self.dim, C.byref(res),
                                                 C.c_void_p(stream)))
@@ -377,6 +382,8 @@ class TableWiseBags:
             return torch.as_tensor(_DeviceView(res.value, (self.per, self.num_tables, self.dim), typestr),
                                    device="cuda")
         tl = len(self.mine)
+        if pool_events:
+            pool_events[0].record()
         for k, t in enumerate(self.mine):
             idx, off, w = inputs[t]
             out = self.send[:, k, :]
@@ -384,6 +391,8 @@ class TableWiseBags:
                                  fixed_len=self.fixed_len, per_sample_weights=w,
                                  padding_idx=self.padding_idx)
             capi.forward(p, stream)
+        if pool_events:
+            pool_events[1].record()
         send = self.send.view(self.per * self.world * max(1, tl), self.dim) if tl else \
             self.send.view(-1, self.dim)[:0]
         dist.all_to_all_single(self.recv, send, output_split_sizes=self.out_splits,
