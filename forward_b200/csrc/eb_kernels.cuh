@@ -133,9 +133,40 @@ __device__ __forceinline__ void add_pair(float& a0, float& a1, float x0, float x
 }
 
 // Fold one loaded chunk into the accumulators.
+// Max over fp16 rows is kept in fp16 while a bag is walked: the eight running values sit as
+// four packed pairs in acc[0..3] (bit patterns), a row replaces a value only where it is
+// strictly greater (one packed compare producing a lane mask, one bit select), and the first
+// row is taken whole.  Comparing halves orders exactly as comparing their float values, the
+// winner's bits are carried unchanged (so -0.0 / +0.0 and the first of equals survive), and a
+// NaN never wins over an earlier value.  unpack_half_max() turns the pairs into floats once
+// the bag is done.
+__device__ __forceinline__ void max_half2(float& acc_bits, unsigned x, bool first) {
+  const unsigned a = __float_as_uint(acc_bits);
+  unsigned gt;  // 0xffff in each half where x > a
+  asm("set.gt.u32.f16x2 %0, %1, %2;" : "=r"(gt) : "r"(x), "r"(a));
+  const unsigned m = first ? 0xffffffffu : gt;
+  acc_bits = __uint_as_float((x & m) | (a & ~m));
+}
+__device__ __forceinline__ void unpack_half_max(float (&acc)[8]) {
+  unsigned w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w[i] = __float_as_uint(acc[i]);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    acc[2 * i] = t.x;
+    acc[2 * i + 1] = t.y;
+  }
+}
+
 template <int OP>
 __device__ __forceinline__ void fold_chunk(float (&acc)[8], const uint4& v, float w, bool first) {
-  if (OP == kOpSum) {
+  if (OP == kOpMax) {
+    max_half2(acc[0], v.x, first);
+    max_half2(acc[1], v.y, first);
+    max_half2(acc[2], v.z, first);
+    max_half2(acc[3], v.w, first);
+  } else if (OP == kOpSum) {
     const unsigned wd[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -374,6 +405,10 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
       cur_counted[j] = nxt_counted[j];
     }
     base += block;
+  }
+  if (OP == kOpMax && VE == 8) {  // fp16 max ran on packed pairs: back to one float per column
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) unpack_half_max(reinterpret_cast<float(&)[8]>(s.v[c]));
   }
 }
 
