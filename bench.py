@@ -546,6 +546,7 @@ def run_ours(args, world: int, rank: int, local_rank: int):
     cpu = None
     if rank == 0 and not multi and not args.no_cpu_baseline:
         cpu = cpu_baseline(workload, world, args.cpu_seconds)
+    ref_kernel = reference_kernel_side_by_side(wl) if (workload == "c2" and not multi) else None
 
     if rank == 0:
         line = {
@@ -559,10 +560,55 @@ def run_ours(args, world: int, rank: int, local_rank: int):
         }
         if exchange:
             line["exchange"] = exchange
+        if ref_kernel:
+            line["reference_kernel"] = ref_kernel
         print(json.dumps(line), flush=True)
     if multi:
         wl.bag.close()
         dist.destroy_process_group()
+
+
+def reference_kernel_side_by_side(wl):
+    """The reference's own EmbeddingBagCuda, recompiled unmodified for sm_100a, on the c2 batches
+    with an fp32 copy of the table in sum mode (the only dtype it supports; its op codes for mean
+    and max are wrong), next to our kernel on exactly those inputs.  None where the reference
+    kernels were not built (the reference tree is not present on every machine)."""
+    import torch
+
+    from oracle import ref_kernels as R
+    if not R.available():
+        return None
+    capi = wl.capi
+    t32 = wl.table.float()
+    bags_n = wl.batches[0].num_bags
+    out_ref = torch.empty((bags_n, wl.dim), dtype=torch.float32, device=wl.dev)
+    out_ours = torch.empty_like(out_ref)
+    stream = torch.cuda.current_stream().cuda_stream
+    params = [capi.make_params(t32, i, o, out=out_ours, mode=capi.MODE_SUM) for i, o in wl.d_batches]
+
+    def timed(fn, n):
+        for k in range(5):
+            fn(k)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for k in range(n):
+            fn(k)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) * 1e3 / n
+
+    ref_us = timed(lambda k: R.bag(wl.d_batches[k % wl.nb][0], wl.d_batches[k % wl.nb][1], out_ref,
+                                   t32, 0, 0, stream), 50)
+    ours_us = timed(lambda k: capi.forward(params[k % wl.nb], stream), 200)
+    R.bag(wl.d_batches[0][0], wl.d_batches[0][1], out_ref, t32, 0, 0, stream)
+    capi.forward(params[0], stream)
+    torch.cuda.synchronize()
+    agree = bool(torch.allclose(out_ref, out_ours, rtol=1e-4, atol=1e-4))
+    n = float(np.mean([b.num_indices for b in wl.batches]))
+    return {"what": "reference EmbeddingBagCuda (embedding_bag_plugin.cu:66-118) recompiled for sm_100a, "
+                    "c2 batches, fp32 table, sum",
+            "reference_us": ref_us, "ours_same_inputs_us": ours_us, "speedup": ref_us / ours_us,
+            "reference_lookups_per_sec": n / (ref_us * 1e-6), "outputs_agree": agree}
 
 
 def verify(wl, workload, world, rank):
