@@ -113,11 +113,43 @@ def build_plugin(force: bool = False, verbose: bool = False) -> str | None:
     return target
 
 
+def build_torch(force: bool = False, verbose: bool = False) -> str | None:
+    """The torch parser slice (needs libtorch's C++ headers, which ship with the torch wheel)."""
+    tdir = os.path.join(CSRC, "torch_cvt")
+    pdir = os.path.join(CSRC, "plugin")
+    if not os.path.isdir(tdir):
+        return None
+    try:
+        import torch
+    except ImportError:
+        return None
+    troot = os.path.dirname(torch.__file__)
+    tinc = os.path.join(troot, "include")
+    if not os.path.exists(os.path.join(tinc, "torch", "script.h")):
+        return None
+    plugin = build_plugin(force, verbose)
+    target = os.path.join(LIBDIR, "libfwd_eb_torch.so")
+    srcs = _walk(tdir, (".cpp",))
+    deps = srcs + _walk(tdir, (".h",)) + _walk(pdir, (".h",)) + [plugin]
+    if force or _stale(target, deps):
+        gxx = shutil.which("g++") or "g++"
+        abi = int(torch.compiled_with_cxx11_abi())
+        cmd = [gxx, "-O2", "-std=c++17", "-fPIC", "-shared", f"-D_GLIBCXX_USE_CXX11_ABI={abi}",
+               "-I", tinc, "-I", os.path.join(tinc, "torch", "csrc", "api", "include"),
+               "-I", "/usr/local/cuda/include", "-I", tdir, "-I", pdir,
+               "-I", os.path.join(pdir, "trt_shim"), "-o", target] + srcs + [
+            "-L", LIBDIR, "-lfwd_eb_plugin", "-L", os.path.join(troot, "lib"), "-ltorch", "-ltorch_cpu",
+            "-lc10", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(troot, "lib")]
+        _run(cmd, verbose)
+    return target
+
+
 def build_all(force: bool = False, verbose: bool = False) -> list[str]:
     out = [build_core(force, verbose)]
-    p = build_plugin(force, verbose)
-    if p:
-        out.append(p)
+    for step in (build_plugin, build_torch):
+        p = step(force, verbose)
+        if p:
+            out.append(p)
     return out
 
 

@@ -80,6 +80,10 @@ void fwd_eb_host_free(fwd_eb_host* h) {
   delete h;
 }
 
+fwd_eb_host* fwd_eb_host_build_desc(const void* embedding_bag_desc, int idx_rank, const int* idx_dims,
+                                    int off_rank, const int* off_dims, int weights_rank,
+                                    const int* weights_dims);
+
 // Build: TrtEmbeddingBagDesc -> LayerCreatorManager -> CreateLayer -> network; then the engine's
 // own clone is configured and serialised.  `weights_rank` 0 = no per-sample-weights input.
 fwd_eb_host* fwd_eb_host_build(const void* table, int half_table, int count, int dim, int offset,
@@ -98,7 +102,17 @@ fwd_eb_host* fwd_eb_host_build(const void* table, int half_table, int count, int
   desc->data.SetType(half_table ? nvinfer1::DataType::kHALF : nvinfer1::DataType::kFLOAT);
   desc->data.SetCount((int64_t)dim * count);
   desc->data.SetData(static_cast<const char*>(table), (int64_t)dim * count * (half_table ? 2 : 4));
+  return fwd_eb_host_build_desc(desc.get(), idx_rank, idx_dims, off_rank, off_dims, weights_rank,
+                                weights_dims);
+}
 
+// The same from a description some parser produced (`embedding_bag_desc` is a
+// fwd::TrtEmbeddingBagDesc*; the torch parser slice enters here).
+fwd_eb_host* fwd_eb_host_build_desc(const void* embedding_bag_desc, int idx_rank, const int* idx_dims,
+                                    int off_rank, const int* off_dims, int weights_rank,
+                                    const int* weights_dims) {
+  const auto* desc = static_cast<const TrtEmbeddingBagDesc*>(embedding_bag_desc);
+  if (!desc) return nullptr;
   std::unique_ptr<fwd_eb_host> h(new fwd_eb_host());
   h->network.reset(new mini_trt::Network());
   fwd::trt_::ITensorVector inputs;
@@ -112,7 +126,7 @@ fwd_eb_host* fwd_eb_host_build(const void* table, int half_table, int count, int
   static fwd::trt_::LayerCreatorManager manager;
   fwd::trt_::ILayerCreator* creator = manager.FindCreator(desc->Name());  // "EmbeddingBag"
   if (!creator) return nullptr;
-  fwd::trt_::ITensorVector outputs = creator->CreateLayer(h->network.get(), desc.get(), inputs);
+  fwd::trt_::ITensorVector outputs = creator->CreateLayer(h->network.get(), desc, inputs);
   if (outputs.empty()) return nullptr;
   mini_trt::Layer* layer = h->network->LayerAt(h->network->getNbLayers() - 1);
   h->layer_name = layer->getName();
