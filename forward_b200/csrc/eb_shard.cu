@@ -97,37 +97,16 @@ __global__ void eb_shard_wait_kernel(const FlagSet f, int rank, int world, uint3
   }
 }
 
-// Wait (bounded) for every source rank's flag, then fold the slots in rank order.
-// Threads fold 16-byte packets (4 floats or 8 halves per slot) when the geometry allows.
+// Fold the G slots in rank order.  Threads fold 16-byte packets (4 floats or 8 halves per
+// slot) when the geometry allows.
 template <typename TP, typename TO, bool VEC>
 __global__ void __launch_bounds__(kCtaThreads)
-eb_shard_combine_kernel(const TP* slots, const FlagSet f, int rank, int world, uint32_t epoch,
-                        long long slot_stride, long long count, TO* out, int* status,
-                        long long max_spins) {
-  __shared__ int timed_out;
-  if (threadIdx.x == 0) {
-    timed_out = 0;
-    // The pooling grid that ran before this kernel on the stream has completed: publish.
-    if (blockIdx.x == 0) raise_flags(f.peer_flags, world, rank, epoch);
-  }
-  const uint32_t* flags = f.peer_flags[rank];
-  __syncthreads();
-  if (threadIdx.x < world) {
-    long long spins = 0;
-    // flags only grow; a peer may already be one call ahead
-    while ((int)(load_acquire_sys(flags + threadIdx.x) - epoch) < 0) {
-      if (++spins >= max_spins) {
-        atomicExch(&timed_out, 1);
-        break;
-      }
-      __nanosleep(64);
-    }
-  }
-  __syncthreads();
-  if (timed_out) {
-    if (threadIdx.x == 0) atomicExch(status, FWD_EB_SHARD_TIMEOUT);
-    return;
-  }
+eb_shard_combine_kernel(const TP* slots, int world, long long slot_stride, long long count, TO* out,
+                        const int* status) {
+  // The flag exchange ran in eb_shard_wait_kernel just before this grid (one warp, so no
+  // spinning CTA ever sits on an SM beside the next call's pooling); a wait that gave up has
+  // left its mark in the status word and the output is then left alone.
+  if (*static_cast<const volatile int*>(status) != 0) return;
   constexpr int PK = VEC ? 16 / (int)sizeof(TP) : 1;  // elements per packet
   const long long packets = count / PK;
   for (long long i = (long long)blockIdx.x * kCtaThreads + threadIdx.x; i < packets;
@@ -211,7 +190,7 @@ static size_t half_bytes(const fwd_eb_shard_exchange* x, int dim) {
 
 static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
   memset(out, 0, sizeof(*out));
-  const size_t half = half_bytes(x, dim) * (x->epoch & 1u);
+  const size_t half = half_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
   for (int r = 0; r < x->world; ++r) {
     out->peer_slots[r] = static_cast<char*>(x->peer_slots[r]) + half;
     out->peer_flags[r] = x->peer_flags[r];
@@ -274,7 +253,7 @@ extern "C" {
 size_t fwd_eb_shard_slots_bytes(int32_t world, int64_t bags_per_rank, int32_t dim,
                                 int32_t wire_dtype) {
   if (world < 1 || bags_per_rank < 1 || dim < 1) return 0;
-  return 2u * (size_t)world * (size_t)bags_per_rank * (size_t)dim * (wire_dtype == FWD_EB_F16 ? 2u : 4u);
+  return (size_t)FWD_EB_SHARD_BUFFERS * (size_t)world * (size_t)bags_per_rank * (size_t)dim * (wire_dtype == FWD_EB_F16 ? 2u : 4u);
 }
 
 int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream) {
@@ -313,7 +292,7 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
 size_t fwd_eb_shard_tablewise_bytes(int64_t bags_per_rank, int32_t num_tables, int32_t dim,
                                     int32_t wire_dtype) {
   if (num_tables < 1 || bags_per_rank < 1 || dim < 1) return 0;
-  return 2u * (size_t)num_tables * (size_t)bags_per_rank * (size_t)dim * (wire_dtype == FWD_EB_F16 ? 2u : 4u);
+  return (size_t)FWD_EB_SHARD_BUFFERS * (size_t)num_tables * (size_t)bags_per_rank * (size_t)dim * (wire_dtype == FWD_EB_F16 ? 2u : 4u);
 }
 
 int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_result, void* stream) {
@@ -327,7 +306,7 @@ int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_resu
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "wait kernel launch");
   if (d_result)
-    *d_result = static_cast<char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch & 1u);
+    *d_result = static_cast<char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
   return 0;
 }
 
@@ -352,7 +331,7 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
     return fail(FWD_EB_EINVAL, "unknown out_dtype %d", out_dtype);
   const long long count = (long long)num_bags * dim;
   const long long slot_stride = (long long)x->bags_per_rank * dim;
-  const char* slots = static_cast<const char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch & 1u);
+  const char* slots = static_cast<const char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
   const FlagSet flags = flag_set(x);
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
   const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
@@ -366,10 +345,13 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
   if (blocks < 1) blocks = 1;
   const unsigned g = (unsigned)blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define FWD_EB_COMBINE(TP, TO, V)                                                               \
-  eb_shard_combine_kernel<TP, TO, V><<<g, kCtaThreads, 0, st>>>(                                \
-      reinterpret_cast<const TP*>(slots), flags, x->rank, x->world, x->epoch, slot_stride, count, \
-      static_cast<TO*>(d_out), x->status, spins)
+  // flag exchange first, in a one-warp kernel of its own
+  eb_shard_wait_kernel<<<1, 32, 0, st>>>(flags, x->rank, x->world, x->epoch, x->status, spins);
+  count_launch();
+#define FWD_EB_COMBINE(TP, TO, V)                                                                \
+  eb_shard_combine_kernel<TP, TO, V><<<g, kCtaThreads, 0, st>>>(                                 \
+      reinterpret_cast<const TP*>(slots), x->world, slot_stride, count, static_cast<TO*>(d_out), \
+      x->status)
   if (vec) {
     if (!wire16 && !out16) FWD_EB_COMBINE(float, float, true);
     else if (!wire16 && out16) FWD_EB_COMBINE(float, __half, true);

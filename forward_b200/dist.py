@@ -207,7 +207,16 @@ class RowShardedBag:
         dev = table_local.device
         self.out = torch.empty((self.per, self.dim), dtype=self.out_dtype, device=dev)
         self.epoch = 0
+        self.side = None
+        self.ready = None
         if exchange == "push":
+            # The fold runs on a side stream so that the next call's pooling does not queue
+            # behind this call's flag wait; results alternate between two buffers.
+            self.side = torch.cuda.Stream(device=dev)
+            self.outs = [self.out, torch.empty_like(self.out), torch.empty_like(self.out)]
+            self._pushed = [torch.cuda.Event() for _ in range(3)]
+            self._done = [torch.cuda.Event() for _ in range(3)]
+            self._before = None   # completion of the fold two calls back
             nbytes = _lib().fwd_eb_shard_slots_bytes(self.world, self.per, self.dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -226,34 +235,52 @@ class RowShardedBag:
         return capi.make_params(self.table, indices, offsets, out=out, mode=self.mode,
                                 padding_idx=self.padding_idx, row_lo=self.row_lo)
 
-    def forward(self, indices, offsets, pool_events=None):
-        """Returns this rank's [bags_owned, dim] slice of the pooled output (a view reused by the
-        next call).  `pool_events` = (start, end) CUDA events recorded around the pooling launch."""
-        import torch
-        import torch.distributed as dist
+    def prepare(self, indices, offsets):
+        """Argument block for forward() on these tensors, built once for inputs that are reused
+        (the tensors must stay alive and in place)."""
         num_bags = offsets.numel()
         if num_bags > self.max_bags:
             raise ValueError("batch larger than max_bags")
-        stream = capi.current_stream_ptr()
         _, mine = owned_bags(self.per * self.world, self.world, self.rank)
         mine = max(0, min(mine, num_bags - self.rank * self.per))
+        out = self.out if self.exchange == "push" else self.partial
+        return (self.params(indices, offsets, out), mine, num_bags)
+
+    def forward(self, indices, offsets=None, pool_events=None):
+        """Returns this rank's [bags_owned, dim] slice of the pooled output (a buffer reused three
+        calls later).  `indices` may be a prepare()d argument block.  `pool_events` = (start, end)
+        CUDA events recorded around the pooling launch."""
+        import torch
+        import torch.distributed as dist
+        p, mine, num_bags = indices if isinstance(indices, tuple) else self.prepare(indices, offsets)
+        main = torch.cuda.current_stream()
+        stream = main.cuda_stream
         if self.exchange == "push":
             self.epoch += 1
             self.x.epoch = self.epoch
-            p = self.params(indices, offsets, self.out)
+            if self._before is not None:
+                # Our fold of call e-2 saw every peer's flag e-2, so the peers are done with the
+                # buffer part this call writes (note at FWD_EB_SHARD_BUFFERS).  The fold of call
+                # e-1 may still be running: it overlaps this call's pooling.
+                main.wait_event(self._before)
+            self._before = self.ready
             if pool_events:
                 pool_events[0].record()
             capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
             if pool_events:
                 pool_events[1].record()
-            capi.check(_lib().fwd_eb_shard_combine(C.byref(self.x), self.dim, mine,
-                                                   self.out.data_ptr(),
-                                                   capi._torch_dtype_code(self.out),
-                                                   C.c_void_p(stream)))
-            return self.out[:mine]
+            pushed = self._pushed[self.epoch % 3]
+            pushed.record(main)
+            self.side.wait_event(pushed)
+            out = self.outs[self.epoch % 3]
+            capi.check(_lib().fwd_eb_shard_combine(C.byref(self.x), self.dim, mine, out.data_ptr(),
+                                                   capi._torch_dtype_code(out),
+                                                   C.c_void_p(self.side.cuda_stream)))
+            self.ready = self._done[self.epoch % 3]
+            self.ready.record(self.side)
+            return out[:mine]
         if num_bags < self.per * self.world:
             self.partial[num_bags:].zero_()
-        p = self.params(indices, offsets, self.partial)
         if pool_events:
             pool_events[0].record()
         capi.forward(p, stream)
@@ -268,12 +295,24 @@ class RowShardedBag:
             self.out.copy_(self.out32)
         return self.out[:mine]
 
+    def sync_result(self):
+        """Make the current stream wait until the result of the last forward() is complete.
+        (With exchange="push" the fold runs on `self.side`; work queued on that stream needs no
+        call.)  The result buffer is reused three calls later; consume a result before the next forward()."""
+        if self.ready is not None:
+            import torch
+            torch.cuda.current_stream().wait_event(self.ready)
+
     def check_status(self) -> int:
         """Non-zero when a bounded wait gave up (reads one device word; synchronises)."""
-        return int(self.status.item()) if self.exchange == "push" else 0
+        if self.exchange != "push":
+            return 0
+        self.side.synchronize()
+        return int(self.status.item())
 
     def close(self):
         if self.exchange == "push":
+            self.side.synchronize()
             self.buffers.close()
 
 
@@ -337,7 +376,14 @@ class TableWiseBags:
         self.wire_dtype = wire_dtype
         dev = torch.device("cuda", torch.cuda.current_device())
         self.epoch = 0
+        self.side = None
+        self.ready = None
+        self._views = [None, None, None]
         if exchange == "push":
+            self.side = torch.cuda.Stream(device=dev)   # the flag wait runs beside the next pooling
+            self._pushed = [torch.cuda.Event() for _ in range(3)]
+            self._done = [torch.cuda.Event() for _ in range(3)]
+            self._before = None
             nbytes = _lib().fwd_eb_shard_tablewise_bytes(self.per, self.num_tables, dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -353,43 +399,60 @@ class TableWiseBags:
             self.out_splits = [self.per * c for c in counts]
             self.by_src = [[t for t, r in enumerate(owner) if r == src] for src in range(self.world)]
 
-    def forward(self, inputs: dict, pool_events=None):
-        """inputs[t] = (indices, offsets_or_None, weights_or_None) for every table this rank owns.
-        Returns [per, T, dim] (rows past the bags this rank owns are unspecified).  `pool_events`
-        = (start, end) CUDA events recorded around the pooling launches."""
+    def prepare(self, inputs: dict):
+        """Argument blocks for forward() on these tensors, built once for inputs that are reused
+        (the tensors must stay alive and in place)."""
+        blocks = []
+        for k, t in enumerate(self.mine):
+            idx, off, w = inputs[t]
+            # with "push" `out` is ignored by the entry point; any CUDA tensor satisfies the binding
+            out = self.tables[t][:1] if self.exchange == "push" else self.send[:, k, :]
+            blocks.append((t, capi.make_params(self.tables[t], idx, off, out=out, mode=self.mode,
+                                               fixed_len=self.fixed_len, per_sample_weights=w,
+                                               padding_idx=self.padding_idx)))
+        return blocks
+
+    def forward(self, inputs, pool_events=None):
+        """inputs[t] = (indices, offsets_or_None, weights_or_None) for every table this rank owns,
+        or a prepare()d list.  Returns [per, T, dim] (rows past the bags this rank owns are
+        unspecified).  `pool_events` = (start, end) CUDA events recorded around the pooling
+        launches."""
         import torch
         import torch.distributed as dist
+        blocks = inputs if isinstance(inputs, list) else self.prepare(inputs)
         stream = capi.current_stream_ptr()
         if self.exchange == "push":
             self.epoch += 1
             self.x.epoch = self.epoch
+            main = torch.cuda.current_stream()
+            if self._before is not None:
+                main.wait_event(self._before)   # flag exchange of call e-2 (see RowShardedBag)
+            self._before = self.ready
             if pool_events:
                 pool_events[0].record()
-            for k, t in enumerate(self.mine):
-                idx, off, w = inputs[t]
-                # `out` is ignored by the push entry point; any CUDA tensor satisfies the binding
-                p = capi.make_params(self.tables[t], idx, off, out=self.tables[t][:1], mode=self.mode,
-                                     fixed_len=self.fixed_len, per_sample_weights=w,
-                                     padding_idx=self.padding_idx)
+            for t, p in blocks:
                 self.x.table_index = t
                 capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
             if pool_events:
                 pool_events[1].record()
+            pushed = self._pushed[self.epoch % 3]
+            pushed.record(main)
+            self.side.wait_event(pushed)
             res = C.c_void_p()
             capi.check(_lib().fwd_eb_shard_wait(C.byref(self.x), self.dim, C.byref(res),
-                                                C.c_void_p(stream)))
-            typestr = "<f2" if self.wire_dtype == capi.F16 else "<f4"
-            return torch.as_tensor(_DeviceView(res.value, (self.per, self.num_tables, self.dim), typestr),
-                                   device="cuda")
+                                                C.c_void_p(self.side.cuda_stream)))
+            self.ready = self._done[self.epoch % 3]
+            self.ready.record(self.side)
+            half = self.epoch % 3
+            if self._views[half] is None or self._views[half].data_ptr() != res.value:
+                typestr = "<f2" if self.wire_dtype == capi.F16 else "<f4"
+                self._views[half] = torch.as_tensor(
+                    _DeviceView(res.value, (self.per, self.num_tables, self.dim), typestr), device="cuda")
+            return self._views[half]
         tl = len(self.mine)
         if pool_events:
             pool_events[0].record()
-        for k, t in enumerate(self.mine):
-            idx, off, w = inputs[t]
-            out = self.send[:, k, :]
-            p = capi.make_params(self.tables[t], idx, off, out=out, mode=self.mode,
-                                 fixed_len=self.fixed_len, per_sample_weights=w,
-                                 padding_idx=self.padding_idx)
+        for t, p in blocks:
             capi.forward(p, stream)
         if pool_events:
             pool_events[1].record()
@@ -408,9 +471,20 @@ class TableWiseBags:
             pos += self.per * len(ts)
         return self.result
 
+    def sync_result(self):
+        """Make the current stream wait until the result of the last forward() is complete (the
+        flag wait runs on `self.side`).  The result buffer is reused three calls later; consume a result before the next forward()."""
+        if self.ready is not None:
+            import torch
+            torch.cuda.current_stream().wait_event(self.ready)
+
     def check_status(self) -> int:
-        return int(self.status.item()) if self.exchange == "push" else 0
+        if self.exchange != "push":
+            return 0
+        self.side.synchronize()
+        return int(self.status.item())
 
     def close(self):
         if self.exchange == "push":
+            self.side.synchronize()
             self.buffers.close()

@@ -12,10 +12,10 @@
  *
  * Exchange layout.  Bags are owned in contiguous runs of `bags_per_rank`: rank o
  * owns bags [o*bags_per_rank, (o+1)*bags_per_rank).  Each rank exposes a receive
- * buffer of 2 x G x bags_per_rank x dim elements (two halves used alternately by
- * call parity, one slot per source rank) and G flag words, all mapped into every
+ * buffer of 3 x G x bags_per_rank x dim elements (three parts used in turn, call
+ * number modulo 3, one slot per source rank) and G flag words, all mapped into every
  * peer (CUDA IPC below, or any other peer mapping).  fwd_eb_shard_push pools, and
- * writes bag b's partial row straight into slot [parity][rank] of b's owner with
+ * writes bag b's partial row straight into slot [part][rank] of b's owner with
  * plain peer stores.  fwd_eb_shard_combine, queued behind it on the same stream,
  * first publishes `epoch` in every peer's flag word (the pooling grid has
  * completed by then, so its peer stores have been performed), then waits
@@ -36,18 +36,23 @@ extern "C" {
 #endif
 
 #define FWD_EB_MAX_PEERS 16
+/* Parts of a receive buffer.  A rank raises flag f only after it has consumed the result of
+ * call f-1, and a rank starts call e only after it has seen every peer's flag e-2; with three
+ * parts the part call e writes (last used by call e-3) is therefore free, and the pooling of
+ * call e never has to wait for the flag exchange of call e-1, which can run beside it. */
+#define FWD_EB_SHARD_BUFFERS 3
 #define FWD_EB_SHARD_TIMEOUT 1
 #define FWD_EB_IPC_HANDLE_BYTES 64
 
 /* Receive-buffer layouts (fwd_eb_shard_exchange.layout). */
 enum {
-  /* Row shards of one table: [2 halves][G source ranks][bags_per_rank][dim];
+  /* Row shards of one table: [3 parts][G source ranks][bags_per_rank][dim];
    * the owner folds the G slots with fwd_eb_shard_combine. */
   FWD_EB_LAYOUT_ROW_SHARD = 0,
-  /* Whole tables placed on different ranks: [2 halves][bags_per_rank][num_tables][dim];
+  /* Whole tables placed on different ranks: [3 parts][bags_per_rank][num_tables][dim];
    * the rank holding table t pools the whole batch and writes column block
    * `table_index` of every owner's buffer.  Nothing is folded: after
-   * fwd_eb_shard_wait the buffer half IS the result (the all-to-all of pooled
+   * fwd_eb_shard_wait that part of the buffer IS the result (the all-to-all of pooled
    * outputs, done by the pooling kernels' own stores). */
   FWD_EB_LAYOUT_TABLE_WISE = 1
 };
@@ -57,7 +62,7 @@ typedef struct fwd_eb_shard_exchange {
   int32_t rank;
   int64_t bags_per_rank;      /* owner of bag b is b / bags_per_rank */
   int32_t wire_dtype;         /* FWD_EB_F32, or FWD_EB_F16 to halve the NVLink bytes */
-  uint32_t epoch;             /* call number, starting at 1; parity picks the buffer half */
+  uint32_t epoch;             /* call number, starting at 1; epoch % 3 picks the buffer part */
   void* peer_slots[FWD_EB_MAX_PEERS];      /* rank r's receive buffer as mapped here */
   uint32_t* peer_flags[FWD_EB_MAX_PEERS];  /* rank r's G flag words as mapped here */
   int32_t* status;            /* one device word of this rank; 0 = fine */
@@ -88,7 +93,7 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
 
 /* TABLE_WISE: after the last fwd_eb_shard_push of this call on the same stream: raise
  * this rank's flag, wait (bounded) until every rank has raised `epoch`; on success
- * *d_result (if not NULL) receives the address of this call's buffer half, laid out
+ * *d_result (if not NULL) receives the address of this call's buffer part, laid out
  * [num_bags owned][num_tables][dim]. */
 int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_result, void* stream);
 

@@ -40,6 +40,7 @@ def _worker(rank, world, port, tmp):
                 bags.indices[::11] = 3
                 got = bag.forward(torch.from_numpy(bags.indices).to(dev),
                                   torch.from_numpy(bags.offsets).to(dev))
+                bag.sync_result()
                 torch.cuda.synchronize()
                 parts = np.stack([O.pool(table[a:a + c], bags.indices, bags.offsets, mode=mode,
                                          padding_idx=3, row_lo=a, out_dtype=np.float32)
@@ -73,6 +74,7 @@ def _worker(rank, world, port, tmp):
             inputs = {t: (torch.from_numpy(idx[t]).to(dev), None, torch.from_numpy(w[t]).to(dev))
                       for t in mine_t}
             res = tw.forward(inputs)
+            tw.sync_result()
             torch.cuda.synchronize()
             expect = np.stack([O.pool(tables[t], idx[t], fixed_len=L, per_sample_weights=w[t])
                                for t in range(ntab)], axis=1)
