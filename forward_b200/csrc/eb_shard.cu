@@ -10,6 +10,7 @@
 // with a bound, for the peers' flags.
 #include <climits>
 #include <cstring>
+#include <new>
 
 #include "eb_internal.h"
 #include "eb_kernels.cuh"
@@ -368,6 +369,132 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "combine kernel launch");
   clear_error();
+  return 0;
+}
+
+// ---- pipeline: a step's stream / event choreography ------------------------------------------------
+
+}  // extern "C"
+
+struct fwd_eb_pipeline {
+  cudaStream_t side = nullptr;
+  cudaEvent_t pushed[FWD_EB_SHARD_BUFFERS] = {};
+  cudaEvent_t done[FWD_EB_SHARD_BUFFERS] = {};
+  uint32_t epoch = 0;
+};
+
+static int pipeline_begin(fwd_eb_pipeline* pl, fwd_eb_shard_exchange* x, cudaStream_t main) {
+  pl->epoch += 1;
+  x->epoch = pl->epoch;
+  if (pl->epoch > 2) {
+    // exchange of step e-2 done => every peer has finished with the part step e writes
+    cudaError_t e = cudaStreamWaitEvent(main, pl->done[(pl->epoch - 2) % FWD_EB_SHARD_BUFFERS], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent (main)");
+  }
+  return 0;
+}
+
+static int pipeline_handover(fwd_eb_pipeline* pl, cudaStream_t main) {
+  const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
+  cudaError_t e = cudaEventRecord(pl->pushed[k], main);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(pl->side, pl->pushed[k], 0);
+  if (e != cudaSuccess) return cuda_fail(e, "handing a step to the side stream");
+  return 0;
+}
+
+extern "C" {
+
+int fwd_eb_pipeline_create(fwd_eb_pipeline** out) {
+  if (!out) return fail(FWD_EB_EINVAL, "out pointer is null");
+  *out = nullptr;
+  fwd_eb_pipeline* pl = new (std::nothrow) fwd_eb_pipeline();
+  if (!pl) return fail(FWD_EB_EINVAL, "out of host memory");
+  int lo = 0, hi = 0;
+  cudaError_t e = cudaDeviceGetStreamPriorityRange(&lo, &hi);  // hi = numerically lowest = most urgent
+  if (e == cudaSuccess) e = cudaStreamCreateWithPriority(&pl->side, cudaStreamNonBlocking, hi);
+  for (int k = 0; k < FWD_EB_SHARD_BUFFERS && e == cudaSuccess; ++k) {
+    e = cudaEventCreateWithFlags(&pl->pushed[k], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pl->done[k], cudaEventDisableTiming);
+  }
+  if (e != cudaSuccess) {
+    int rc = cuda_fail(e, "creating the pipeline's stream and events");
+    fwd_eb_pipeline_destroy(pl);
+    return rc;
+  }
+  *out = pl;
+  return 0;
+}
+
+void fwd_eb_pipeline_destroy(fwd_eb_pipeline* pl) {
+  if (!pl) return;
+  if (pl->side) cudaStreamSynchronize(pl->side);
+  for (int k = 0; k < FWD_EB_SHARD_BUFFERS; ++k) {
+    if (pl->pushed[k]) cudaEventDestroy(pl->pushed[k]);
+    if (pl->done[k]) cudaEventDestroy(pl->done[k]);
+  }
+  if (pl->side) cudaStreamDestroy(pl->side);
+  delete pl;
+}
+
+void* fwd_eb_pipeline_side_stream(fwd_eb_pipeline* pl) { return pl ? pl->side : nullptr; }
+
+int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
+                                  fwd_eb_shard_exchange* x, int64_t num_bags_owned,
+                                  void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
+                                  void* main_stream, int32_t* which) {
+  if (!pl || !p || !x || !d_out) return fail(FWD_EB_EINVAL, "null argument");
+  cudaStream_t main = static_cast<cudaStream_t>(main_stream);
+  int rc = pipeline_begin(pl, x, main);
+  if (rc) return rc;
+  rc = fwd_eb_shard_push(p, x, main);
+  if (rc) return rc;
+  rc = pipeline_handover(pl, main);
+  if (rc) return rc;
+  const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
+  rc = fwd_eb_shard_combine(x, p->dim, num_bags_owned, d_out[k], out_dtype, pl->side);
+  if (rc) return rc;
+  cudaError_t e = cudaEventRecord(pl->done[k], pl->side);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord (side)");
+  if (which) *which = k;
+  return 0;
+}
+
+int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
+                                   const int32_t* table_index, int32_t count,
+                                   fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
+                                   void** d_result) {
+  if (!pl || !x || count < 0 || (count > 0 && (!params || !table_index)))
+    return fail(FWD_EB_EINVAL, "null argument");
+  cudaStream_t main = static_cast<cudaStream_t>(main_stream);
+  int rc = pipeline_begin(pl, x, main);
+  if (rc) return rc;
+  for (int i = 0; i < count; ++i) {
+    x->table_index = table_index[i];
+    rc = fwd_eb_shard_push(params[i], x, main);
+    if (rc) return rc;
+  }
+  rc = pipeline_handover(pl, main);
+  if (rc) return rc;
+  rc = fwd_eb_shard_wait(x, dim, d_result, pl->side);
+  if (rc) return rc;
+  cudaError_t e = cudaEventRecord(pl->done[pl->epoch % FWD_EB_SHARD_BUFFERS], pl->side);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord (side)");
+  return 0;
+}
+
+int fwd_eb_pipeline_sync_result(fwd_eb_pipeline* pl, void* stream) {
+  if (!pl) return fail(FWD_EB_EINVAL, "null pipeline");
+  if (pl->epoch == 0) return 0;
+  cudaError_t e = cudaStreamWaitEvent(static_cast<cudaStream_t>(stream),
+                                      pl->done[pl->epoch % FWD_EB_SHARD_BUFFERS], 0);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent (result)");
+  return 0;
+}
+
+int fwd_eb_pipeline_drain(fwd_eb_pipeline* pl) {
+  if (!pl) return fail(FWD_EB_EINVAL, "null pipeline");
+  cudaError_t e = cudaStreamSynchronize(pl->side);
+  if (e != cudaSuccess) return cuda_fail(e, "draining the side stream");
   return 0;
 }
 

@@ -87,6 +87,18 @@ SIGNATURES = {
     "fwd_eb_shard_wait": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.POINTER(C.c_void_p),
                                     C.c_void_p]),
     "fwd_eb_shard_signal": (C.c_int, [C.POINTER(ShardExchange), C.c_void_p]),
+    "fwd_eb_pipeline_create": (C.c_int, [C.POINTER(C.c_void_p)]),
+    "fwd_eb_pipeline_destroy": (None, [C.c_void_p]),
+    "fwd_eb_pipeline_side_stream": (C.c_void_p, [C.c_void_p]),
+    "fwd_eb_pipeline_step_rowshard": (C.c_int, [C.c_void_p, C.POINTER(capi.Params), C.POINTER(ShardExchange),
+                                                C.c_int64, C.POINTER(C.c_void_p), C.c_int32, C.c_void_p,
+                                                C.POINTER(C.c_int32)]),
+    "fwd_eb_pipeline_step_tablewise": (C.c_int, [C.c_void_p, C.POINTER(C.POINTER(capi.Params)),
+                                                 C.POINTER(C.c_int32), C.c_int32,
+                                                 C.POINTER(ShardExchange), C.c_int32, C.c_void_p,
+                                                 C.POINTER(C.c_void_p)]),
+    "fwd_eb_pipeline_sync_result": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "fwd_eb_pipeline_drain": (C.c_int, [C.c_void_p]),
     "fwd_eb_ipc_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
     "fwd_eb_ipc_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "fwd_eb_ipc_close": (C.c_int, [C.c_void_p]),
@@ -210,13 +222,14 @@ class RowShardedBag:
         self.side = None
         self.ready = None
         if exchange == "push":
-            # The fold runs on a side stream so that the next call's pooling does not queue
-            # behind this call's flag wait; results alternate between two buffers.
-            self.side = torch.cuda.Stream(device=dev)
+            # The fold runs on the pipeline's side stream so that the next call's pooling does
+            # not queue behind this call's flag exchange; results rotate through three buffers.
             self.outs = [self.out, torch.empty_like(self.out), torch.empty_like(self.out)]
-            self._pushed = [torch.cuda.Event() for _ in range(3)]
-            self._done = [torch.cuda.Event() for _ in range(3)]
-            self._before = None   # completion of the fold two calls back
+            self._out_ptrs = (C.c_void_p * 3)(*[o.data_ptr() for o in self.outs])
+            self._pl = C.c_void_p()
+            capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
+            self.side = torch.cuda.ExternalStream(_lib().fwd_eb_pipeline_side_stream(self._pl), device=dev)
+            self._which = C.c_int32(0)
             nbytes = _lib().fwd_eb_shard_slots_bytes(self.world, self.per, self.dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -256,29 +269,15 @@ class RowShardedBag:
         main = torch.cuda.current_stream()
         stream = main.cuda_stream
         if self.exchange == "push":
-            self.epoch += 1
-            self.x.epoch = self.epoch
-            if self._before is not None:
-                # Our fold of call e-2 saw every peer's flag e-2, so the peers are done with the
-                # buffer part this call writes (note at FWD_EB_SHARD_BUFFERS).  The fold of call
-                # e-1 may still be running: it overlaps this call's pooling.
-                main.wait_event(self._before)
-            self._before = self.ready
             if pool_events:
                 pool_events[0].record()
-            capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
+            capi.check(_lib().fwd_eb_pipeline_step_rowshard(
+                self._pl, C.byref(p), C.byref(self.x), mine, self._out_ptrs,
+                capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))
             if pool_events:
-                pool_events[1].record()
-            pushed = self._pushed[self.epoch % 3]
-            pushed.record(main)
-            self.side.wait_event(pushed)
-            out = self.outs[self.epoch % 3]
-            capi.check(_lib().fwd_eb_shard_combine(C.byref(self.x), self.dim, mine, out.data_ptr(),
-                                                   capi._torch_dtype_code(out),
-                                                   C.c_void_p(self.side.cuda_stream)))
-            self.ready = self._done[self.epoch % 3]
-            self.ready.record(self.side)
-            return out[:mine]
+                pool_events[1].record()   # after the push launch (the fold went to the side stream)
+            self.ready = True
+            return self.outs[self._which.value][:mine]
         if num_bags < self.per * self.world:
             self.partial[num_bags:].zero_()
         if pool_events:
@@ -298,21 +297,21 @@ class RowShardedBag:
     def sync_result(self):
         """Make the current stream wait until the result of the last forward() is complete.
         (With exchange="push" the fold runs on `self.side`; work queued on that stream needs no
-        call.)  The result buffer is reused three calls later; consume a result before the next forward()."""
-        if self.ready is not None:
-            import torch
-            torch.cuda.current_stream().wait_event(self.ready)
+        call.)  Consume a result before the next forward()."""
+        if self.exchange == "push" and self.ready:
+            capi.check(_lib().fwd_eb_pipeline_sync_result(self._pl, C.c_void_p(capi.current_stream_ptr())))
 
     def check_status(self) -> int:
         """Non-zero when a bounded wait gave up (reads one device word; synchronises)."""
         if self.exchange != "push":
             return 0
-        self.side.synchronize()
+        capi.check(_lib().fwd_eb_pipeline_drain(self._pl))
         return int(self.status.item())
 
     def close(self):
         if self.exchange == "push":
-            self.side.synchronize()
+            _lib().fwd_eb_pipeline_destroy(self._pl)
+            self._pl = C.c_void_p()
             self.buffers.close()
 
 
@@ -378,12 +377,12 @@ class TableWiseBags:
         self.epoch = 0
         self.side = None
         self.ready = None
-        self._views = [None, None, None]
+        self._views = {}
         if exchange == "push":
-            self.side = torch.cuda.Stream(device=dev)   # the flag wait runs beside the next pooling
-            self._pushed = [torch.cuda.Event() for _ in range(3)]
-            self._done = [torch.cuda.Event() for _ in range(3)]
-            self._before = None
+            self._pl = C.c_void_p()
+            capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
+            # the flag exchange runs on the pipeline's side stream, beside the next pooling
+            self.side = torch.cuda.ExternalStream(_lib().fwd_eb_pipeline_side_stream(self._pl), device=dev)
             nbytes = _lib().fwd_eb_shard_tablewise_bytes(self.per, self.num_tables, dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -410,7 +409,10 @@ class TableWiseBags:
             blocks.append((t, capi.make_params(self.tables[t], idx, off, out=out, mode=self.mode,
                                                fixed_len=self.fixed_len, per_sample_weights=w,
                                                padding_idx=self.padding_idx)))
-        return blocks
+        n = len(blocks)
+        ptrs = (C.POINTER(capi.Params) * max(n, 1))(*[C.pointer(p) for _, p in blocks])
+        tabs = (C.c_int32 * max(n, 1))(*[t for t, _ in blocks])
+        return [blocks, ptrs, tabs, n]
 
     def forward(self, inputs, pool_events=None):
         """inputs[t] = (indices, offsets_or_None, weights_or_None) for every table this rank owns,
@@ -419,36 +421,25 @@ class TableWiseBags:
         launches."""
         import torch
         import torch.distributed as dist
-        blocks = inputs if isinstance(inputs, list) else self.prepare(inputs)
+        prepared = inputs if isinstance(inputs, list) else self.prepare(inputs)
+        blocks, ptrs, tabs, n = prepared
         stream = capi.current_stream_ptr()
         if self.exchange == "push":
-            self.epoch += 1
-            self.x.epoch = self.epoch
-            main = torch.cuda.current_stream()
-            if self._before is not None:
-                main.wait_event(self._before)   # flag exchange of call e-2 (see RowShardedBag)
-            self._before = self.ready
             if pool_events:
                 pool_events[0].record()
-            for t, p in blocks:
-                self.x.table_index = t
-                capi.check(_lib().fwd_eb_shard_push(C.byref(p), C.byref(self.x), C.c_void_p(stream)))
-            if pool_events:
-                pool_events[1].record()
-            pushed = self._pushed[self.epoch % 3]
-            pushed.record(main)
-            self.side.wait_event(pushed)
             res = C.c_void_p()
-            capi.check(_lib().fwd_eb_shard_wait(C.byref(self.x), self.dim, C.byref(res),
-                                                C.c_void_p(self.side.cuda_stream)))
-            self.ready = self._done[self.epoch % 3]
-            self.ready.record(self.side)
-            half = self.epoch % 3
-            if self._views[half] is None or self._views[half].data_ptr() != res.value:
+            capi.check(_lib().fwd_eb_pipeline_step_tablewise(self._pl, ptrs, tabs, n, C.byref(self.x),
+                                                             self.dim, C.c_void_p(stream), C.byref(res)))
+            if pool_events:
+                pool_events[1].record()   # after the push launches (the flag exchange is on the side stream)
+            self.ready = True
+            view = self._views.get(res.value)
+            if view is None:
                 typestr = "<f2" if self.wire_dtype == capi.F16 else "<f4"
-                self._views[half] = torch.as_tensor(
-                    _DeviceView(res.value, (self.per, self.num_tables, self.dim), typestr), device="cuda")
-            return self._views[half]
+                view = torch.as_tensor(_DeviceView(res.value, (self.per, self.num_tables, self.dim), typestr),
+                                       device="cuda")
+                self._views[res.value] = view
+            return view
         tl = len(self.mine)
         if pool_events:
             pool_events[0].record()
@@ -473,18 +464,18 @@ class TableWiseBags:
 
     def sync_result(self):
         """Make the current stream wait until the result of the last forward() is complete (the
-        flag wait runs on `self.side`).  The result buffer is reused three calls later; consume a result before the next forward()."""
-        if self.ready is not None:
-            import torch
-            torch.cuda.current_stream().wait_event(self.ready)
+        flag exchange runs on `self.side`).  Consume a result before the next forward()."""
+        if self.exchange == "push" and self.ready:
+            capi.check(_lib().fwd_eb_pipeline_sync_result(self._pl, C.c_void_p(capi.current_stream_ptr())))
 
     def check_status(self) -> int:
         if self.exchange != "push":
             return 0
-        self.side.synchronize()
+        capi.check(_lib().fwd_eb_pipeline_drain(self._pl))
         return int(self.status.item())
 
     def close(self):
         if self.exchange == "push":
-            self.side.synchronize()
+            _lib().fwd_eb_pipeline_destroy(self._pl)
+            self._pl = C.c_void_p()
             self.buffers.close()

@@ -101,6 +101,42 @@ int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_resu
  * call early). */
 int fwd_eb_shard_signal(const fwd_eb_shard_exchange* x, void* stream);
 
+/* ---- one call = one step: the stream / event choreography in native code ---------
+ *
+ * A pipeline owns a high-priority side stream and the events that order a step:
+ *   main stream   [wait: exchange of step e-2 done]  pooling + push of step e
+ *   side stream   [wait: push of step e issued]      flag exchange (+ fold) of step e
+ * so the pooling of step e overlaps the flag exchange and fold of step e-1 (three buffer
+ * parts make that safe, see FWD_EB_SHARD_BUFFERS), and a step costs the host one call.
+ * It keeps the call number itself (x->epoch is overwritten).  Results complete on the side
+ * stream: queue consumers there (fwd_eb_pipeline_side_stream) or call
+ * fwd_eb_pipeline_sync_result on the stream that will read them; consume a result before
+ * the next step is issued. */
+typedef struct fwd_eb_pipeline fwd_eb_pipeline;
+
+int fwd_eb_pipeline_create(fwd_eb_pipeline** out);
+void fwd_eb_pipeline_destroy(fwd_eb_pipeline* pl);
+void* fwd_eb_pipeline_side_stream(fwd_eb_pipeline* pl);
+
+/* Row shards: push `p` on `main_stream`, fold on the side stream into d_out[epoch % 3]
+ * (three caller buffers of [bags_per_rank, dim]); *which receives epoch % 3. */
+int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
+                                  fwd_eb_shard_exchange* x, int64_t num_bags_owned,
+                                  void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
+                                  void* main_stream, int32_t* which);
+
+/* Table-wise: push the `count` local tables (x->table_index is set from table_index[i]),
+ * then the flag exchange on the side stream; *d_result receives this step's buffer part. */
+int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
+                                   const int32_t* table_index, int32_t count,
+                                   fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
+                                   void** d_result);
+
+/* Make `stream` wait for the last step's result. */
+int fwd_eb_pipeline_sync_result(fwd_eb_pipeline* pl, void* stream);
+/* Block the host until everything the pipeline queued has run. */
+int fwd_eb_pipeline_drain(fwd_eb_pipeline* pl);
+
 /* ---- peer mapping through CUDA IPC (one process per GPU on one node) ---------- */
 
 /* cudaMalloc + zero-fill `bytes` and produce the 64-byte handle peers open. */
