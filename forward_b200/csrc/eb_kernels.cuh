@@ -32,10 +32,13 @@
 namespace fwd_eb {
 
 constexpr unsigned kFull = 0xffffffffu;
-constexpr int kCtaThreads = 256;
+#ifndef FWD_EB_CTA_THREADS
+#define FWD_EB_CTA_THREADS 128
+#endif
+constexpr int kCtaThreads = FWD_EB_CTA_THREADS;
 // Resident CTAs per SM the pooling kernels are compiled for (caps registers per thread).
 #ifndef FWD_EB_MIN_CTAS
-#define FWD_EB_MIN_CTAS 4
+#define FWD_EB_MIN_CTAS 8
 #endif
 #ifndef FWD_EB_U1
 #define FWD_EB_U1 4
@@ -558,10 +561,11 @@ eb_pool_cta_kernel(const PoolArgs a) {
   long long bstart, bend;
   bag_bounds(a, bag, bstart, bend);
   const long long blen = bend - bstart;
-  // slice of this split, then of this group, both in whole index blocks
+  // slice of this split, then of this group: whole multiples of U indices (a pass), so short
+  // bags still spread over several groups
   const long long total_slices = (long long)a.splits * groups;
   long long per = (blen + total_slices - 1) / total_slices;
-  per = ((per + lanes - 1) >> lanes_log2) << lanes_log2;
+  per = (per + U - 1) / U * U;
   const long long slot = (long long)split * groups + g;
   long long start = bstart + slot * per;
   long long end = start + per;
