@@ -47,7 +47,7 @@ if ROOT not in sys.path:
 NUM_BATCHES = 8
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the pooling kernel, from the ncu
 # captures summarised under profiles/ (None where no capture of that workload exists yet).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 35.9e6, "tablewise": None, "rowshard": None, "c5": None, "c3": None}
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 35.9e6, "tablewise": None, "rowshard": None, "c5": None, "c3": 129.9e6}
 C2 = dict(rows=1_000_000, dim=128, bags=16384)
 C5 = dict(rows=1_000_000_000, dim=64, bags=131072)
 C3 = dict(rows=4_000_000, dim=256, bags=8192)
