@@ -196,6 +196,13 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
   a.mean_raw_len = (p->flags & FWD_EB_FLAG_MEAN_RAW_LENGTH) != 0;
   a.mean_double_round = (p->flags & FWD_EB_FLAG_MEAN_SINGLE_ROUNDING) == 0;
   a.splits = 1;
+  // 32-bit filter constants for int32 indices
+  a.lo32 = (unsigned)p->row_lo;
+  // (idx - row_lo) in wrap-around 32-bit arithmetic is exact whenever row_lo itself fits an int;
+  // a window starting beyond the int range cannot contain an int32 index at all
+  a.nrows32 = (p->row_lo >= INT_MIN && p->row_lo <= INT_MAX) ? (unsigned)p->num_rows : 0u;
+  a.pad32_on = p->padding_idx >= 0 && p->padding_idx <= INT_MAX;
+  a.pad32 = a.pad32_on ? (int)p->padding_idx : 0;
 
   switch (p->mode) {
     case FWD_EB_MODE_MAX:

@@ -73,6 +73,11 @@ struct PoolArgs {
   int mean_raw_len;         // ... by the raw bag length instead of the non-padding count
   int mean_double_round;    // fp16 mean the way torch CPU rounds it
   int splits;               // split strategy: CTAs per bag
+  // 32-bit form of the filter for int32 indices (set by the host; see fetch in pool_range)
+  unsigned lo32;            // row_lo
+  unsigned nrows32;         // num_rows, or 0 when the window lies beyond the int32 range
+  int pad32;                // padding_idx, or INT_MIN-like sentinel that matches nothing counted
+  int pad32_on;             // padding_idx is set and fits an int
 };
 
 template <typename TW, int VE>
@@ -268,6 +273,20 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
     w = 1.0f;
     counted = false;
     if (pos < end) {
+      if (!a.idx64) {
+        // int32 indices: the whole filter in 32-bit arithmetic.  (unsigned)(idx - lo) < rows
+        // is the window test; a negative or too-small index wraps to a value >= 2^31.
+        const int idx = __ldg(reinterpret_cast<const int*>(a.indices) + pos);
+        if (!a.pad32_on || idx != a.pad32) {
+          counted = true;
+          const unsigned r = (unsigned)idx - a.lo32;
+          if (r < a.nrows32) {
+            row = (int)r;
+            if (OP == kOpWeighted) w = __ldg(a.psw + pos);
+          }
+        }
+        return;
+      }
       long long idx = load_index(a.indices, a.idx64, pos);
       if (a.padding_idx < 0 || idx != a.padding_idx) {
         counted = true;

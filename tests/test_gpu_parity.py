@@ -369,3 +369,26 @@ def test_config4_one_table_weighted_sum():
     exp = O.pool(compact, inv.astype(np.int32), mode=O.MODE_SUM, fixed_len=20,
                  per_sample_weights=bags.per_sample_weights)
     assert_close(got.cpu().numpy(), exp, np.float32, exact=True)
+
+
+def test_int32_filter_edges_negative_indices_and_window_origin():
+    """int32 indices take a 32-bit filter: negative indices, indices below the window origin and
+    a negative origin (the reference's data_offset is a signed int) must behave as in the oracle."""
+    rng = np.random.default_rng(77)
+    table = rng.standard_normal((100, 16)).astype(np.float32)
+    idx = rng.integers(-50, 300, 4000).astype(np.int32)
+    idx[::50] = np.iinfo(np.int32).min
+    idx[1::50] = np.iinfo(np.int32).max
+    lengths = rng.integers(0, 40, 200)
+    lengths[-1] += 4000 - lengths.sum() if lengths.sum() < 4000 else 0
+    off = workloads.offsets_from_lengths(lengths).astype(np.int32)
+    n = int(lengths.sum())
+    idx = idx[:n] if n <= idx.size else np.resize(idx, n)
+    for row_lo in (0, 120, -30):
+        for mode in (capi.MODE_SUM, capi.MODE_MEAN, capi.MODE_MAX):
+            got = gpu_pool(table, idx, off, mode=mode, row_lo=row_lo, padding_idx=7)
+            exp = O.pool(table, idx, off, mode=mode, row_lo=row_lo, padding_idx=7)
+            assert_close(got, exp, np.float32, exact=True)
+            got64 = gpu_pool(table, idx.astype(np.int64), off.astype(np.int64), mode=mode,
+                             row_lo=row_lo, padding_idx=7)
+            assert_close(got64, exp, np.float32, exact=True)
