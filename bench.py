@@ -426,7 +426,7 @@ class GpuWorkload:
         return self._last
 
     def lookups(self, k: int) -> int:
-        """Lookups of step k on the table(s) this rank's batches address."""
+        """Lookups of step k on the table this rank's batches address."""
         return self.batches[k % self.nb].num_indices
 
     def algorithmic_bytes(self, k: int) -> float:

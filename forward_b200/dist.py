@@ -8,8 +8,9 @@ Row shards (one huge table): rank r holds rows [r*rows/G, (r+1)*rows/G); every r
 batch, pools what it owns into partial bags, and bag b ends up, summed, on rank b // bags_per_rank.
   exchange="nccl"  partial [B, D] fp32 in local memory, then ncclReduceScatter
   exchange="a2a"   all-to-all of the partial slices, then a fixed-order fold (deterministic)
-  exchange="push"  fwd_eb_shard_push / fwd_eb_shard_combine: partial rows go straight into the
-                   owner's slots over NVLink from inside the pooling kernel
+  exchange="push"  fwd_eb_pipeline_step_rowshard: partial rows go straight into the owner's slots
+                   over NVLink from inside the pooling kernel; the flag exchange and the fold run on
+                   a side stream beside the next call's pooling
 
 Table-wise (many tables): whole tables are assigned to ranks; each rank pools the full batch for
 its tables and the pooled outputs are exchanged so that rank g ends with [B/G, T, D].
@@ -17,8 +18,6 @@ its tables and the pooled outputs are exchanged so that rank g ends with [B/G, T
 from __future__ import annotations
 
 import ctypes as C
-
-import numpy as np
 
 from . import capi
 
@@ -218,7 +217,6 @@ class RowShardedBag:
         self.out_dtype = out_dtype or torch.float32
         dev = table_local.device
         self.out = torch.empty((self.per, self.dim), dtype=self.out_dtype, device=dev)
-        self.epoch = 0
         self.side = None
         self.ready = None
         if exchange == "push":
@@ -374,7 +372,6 @@ class TableWiseBags:
         self.exchange = exchange
         self.wire_dtype = wire_dtype
         dev = torch.device("cuda", torch.cuda.current_device())
-        self.epoch = 0
         self.side = None
         self.ready = None
         self._views = {}
