@@ -672,7 +672,7 @@ def run_e2e(args, wl):
 
     from forward_b200.session import Session
     capi = wl.capi
-    depth = 4
+    depth = args.e2e_depth
     max_n = max(b.num_indices for b in wl.batches)
     bags_n = wl.batches[0].num_bags
     s = Session(table_dtype=capi.F16, dim=wl.dim, num_rows=wl.table.shape[0], mode=wl.mode,
@@ -774,6 +774,7 @@ def main():
     ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
                     help="row shards with --exchange push: element type of the partials on NVLink")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--e2e-depth", type=int, default=4, help="N=1 e2e: calls in flight (1..16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-verify", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)

@@ -131,7 +131,7 @@ EmbeddingBagPlugin::EmbeddingBagPlugin(const float* data, int dim, int count, in
 
 EmbeddingBagPlugin::EmbeddingBagPlugin(const void* data, int dim, int count, int offset,
                                        ReduceOperation op, const EmbeddingBagOptions& options)
-    : dim_(dim), count_(count), data_offset_(offset), op_(op), opt_(options) {
+    : opt_(options), op_(op), dim_(dim), count_(count), data_offset_(offset) {
   valid_ = dim > 0 && count >= 0 && (data != nullptr || count == 0);
   if (valid_) {
     table_ = std::make_shared<EmbeddingTable>(data, TableBytes(dim, count, opt_.half_table),
@@ -176,8 +176,8 @@ EmbeddingBagPlugin::EmbeddingBagPlugin(void const* serialData, size_t serialLeng
 }
 
 EmbeddingBagPlugin::EmbeddingBagPlugin(const EmbeddingBagPlugin& o)
-    : dim_(o.dim_), count_(o.count_), data_offset_(o.data_offset_), op_(o.op_), opt_(o.opt_),
-      table_(o.table_), d_data_(nullptr), valid_(o.valid_), namespace_(o.namespace_) {}
+    : table_(o.table_), d_data_(nullptr), opt_(o.opt_), op_(o.op_), dim_(o.dim_), count_(o.count_),
+      data_offset_(o.data_offset_), valid_(o.valid_), namespace_(o.namespace_) {}
 
 EmbeddingBagPlugin::~EmbeddingBagPlugin() noexcept { terminate(); }
 

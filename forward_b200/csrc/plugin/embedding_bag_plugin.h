@@ -87,43 +87,49 @@ struct EmbeddingBagOptions {
 
 class EmbeddingBagPlugin final : public nvinfer1::IPluginV2DynamicExt {
  public:
-  // reference constructor (fp32 table, reference semantics)
+  // ---- construction -------------------------------------------------------------------------
+  EmbeddingBagPlugin() = delete;
+  // reference constructor: fp32 table, reference semantics
   EmbeddingBagPlugin(const float* data, int dim, int count, int offset, ReduceOperation op);
   // extended constructor: `data` holds dim*count elements of the table's element type
   EmbeddingBagPlugin(const void* data, int dim, int count, int offset, ReduceOperation op,
                      const EmbeddingBagOptions& options);
-  EmbeddingBagPlugin(void const* serialData, size_t serialLength);
-  EmbeddingBagPlugin() = delete;
+  // from an engine blob
+  EmbeddingBagPlugin(void const* blob, size_t blob_bytes);
   ~EmbeddingBagPlugin() noexcept override;
 
-  int getNbOutputs() const noexcept override;
-  nvinfer1::DimsExprs getOutputDimensions(int outputIndex, const nvinfer1::DimsExprs* inputs,
-                                          int nbInputs,
-                                          nvinfer1::IExprBuilder& exprBuilder) noexcept override;
-  bool supportsFormatCombination(int pos, const nvinfer1::PluginTensorDesc* inOut, int nbInputs,
-                                 int nbOutputs) noexcept override;
-  void configurePlugin(const nvinfer1::DynamicPluginTensorDesc* in, int nbInputs,
-                       const nvinfer1::DynamicPluginTensorDesc* out, int nbOutputs) noexcept override;
-  size_t getWorkspaceSize(const nvinfer1::PluginTensorDesc* inputs, int nbInputs,
-                          const nvinfer1::PluginTensorDesc* outputs,
-                          int nbOutputs) const noexcept override;
-  int initialize() noexcept override;
-  void terminate() noexcept override;
-  int enqueue(const nvinfer1::PluginTensorDesc* inputDesc,
-              const nvinfer1::PluginTensorDesc* outputDesc, const void* const* inputs,
-              void* const* outputs, void* workspace, cudaStream_t stream) noexcept override;
-  size_t getSerializationSize() const noexcept override;
-  void serialize(void* buffer) const noexcept override;
+  // ---- identity, copies, blob ------------------------------------------------------------------
   const char* getPluginType() const noexcept override;
   const char* getPluginVersion() const noexcept override;
-  void destroy() noexcept override;
-  nvinfer1::IPluginV2DynamicExt* clone() const noexcept override;
-  void setPluginNamespace(const char* pluginNamespace) noexcept override;
   const char* getPluginNamespace() const noexcept override;
-  nvinfer1::DataType getOutputDataType(int index, const nvinfer1::DataType* inputTypes,
-                                       int nbInputs) const noexcept override;
+  void setPluginNamespace(const char* ns) noexcept override;
+  nvinfer1::IPluginV2DynamicExt* clone() const noexcept override;
+  void destroy() noexcept override;
+  size_t getSerializationSize() const noexcept override;
+  void serialize(void* dst) const noexcept override;
 
-  // for tests: did construction / deserialisation succeed, and how the table is shared
+  // ---- shape and format negotiation ------------------------------------------------------------
+  int getNbOutputs() const noexcept override;
+  nvinfer1::DataType getOutputDataType(int index, const nvinfer1::DataType* in_types,
+                                       int nb_inputs) const noexcept override;
+  nvinfer1::DimsExprs getOutputDimensions(int out_index, const nvinfer1::DimsExprs* in_dims,
+                                          int nb_inputs,
+                                          nvinfer1::IExprBuilder& exprs) noexcept override;
+  bool supportsFormatCombination(int pos, const nvinfer1::PluginTensorDesc* in_out, int nb_inputs,
+                                 int nb_outputs) noexcept override;
+  size_t getWorkspaceSize(const nvinfer1::PluginTensorDesc* in, int nb_inputs,
+                          const nvinfer1::PluginTensorDesc* out, int nb_outputs) const noexcept override;
+
+  // ---- life cycle and execution ----------------------------------------------------------------
+  void configurePlugin(const nvinfer1::DynamicPluginTensorDesc* in, int nb_inputs,
+                       const nvinfer1::DynamicPluginTensorDesc* out, int nb_outputs) noexcept override;
+  int initialize() noexcept override;
+  void terminate() noexcept override;
+  int enqueue(const nvinfer1::PluginTensorDesc* in_desc, const nvinfer1::PluginTensorDesc* out_desc,
+              const void* const* inputs, void* const* outputs, void* workspace,
+              cudaStream_t stream) noexcept override;
+
+  // ---- for tests: did construction / deserialisation succeed, and how the table is shared -------
   bool Valid() const { return valid_; }
   const std::shared_ptr<EmbeddingTable>& Table() const { return table_; }
   const EmbeddingBagOptions& Options() const { return opt_; }
@@ -131,13 +137,13 @@ class EmbeddingBagPlugin final : public nvinfer1::IPluginV2DynamicExt {
  private:
   EmbeddingBagPlugin(const EmbeddingBagPlugin& other);  // clone: shares the table
 
+  std::shared_ptr<EmbeddingTable> table_;
+  const void* d_data_{nullptr};  // cached Device() of the GPU configured on
+  EmbeddingBagOptions opt_;
+  ReduceOperation op_{ReduceOperation::SUM};
   int dim_{0};
   int count_{0};
   int data_offset_{0};
-  ReduceOperation op_{ReduceOperation::SUM};
-  EmbeddingBagOptions opt_;
-  std::shared_ptr<EmbeddingTable> table_;
-  const void* d_data_{nullptr};  // cached Device() of the GPU configured on
   bool valid_{true};
   std::string namespace_;
 };

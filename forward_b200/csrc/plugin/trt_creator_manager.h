@@ -8,7 +8,7 @@
 #include <memory>
 #include <string>
 
-#include "i_trt_layer_creator.h"
+#include "layer_creator_iface.h"
 
 FWD_TRT_NAMESPACE_BEGIN
 

@@ -13,7 +13,7 @@
 #include <vector>
 
 #include "embedding_bag_plugin.h"
-#include "i_trt_layer_creator.h"
+#include "layer_creator_iface.h"
 
 FWD_TRT_NAMESPACE_BEGIN
 
