@@ -717,10 +717,13 @@ def run_e2e_multi(args, wl, rank, world, dev):
     multi-GPU call and copies this rank's slice of the result back to pinned memory."""
     import torch
     import torch.distributed as dist
-    host = [(torch.from_numpy(b.indices).pin_memory(), torch.from_numpy(b.offsets).pin_memory())
+    # offsets and indices of a batch share one pinned block and go up as ONE copy (a second,
+    # small copy per step costs far more copy-engine time than its bytes)
+    host = [torch.cat([torch.from_numpy(b.offsets), torch.from_numpy(b.indices)]).pin_memory()
             for b in wl.batches]
-    d_idx = [torch.empty_like(i, device=dev) for i, _ in host]
-    d_off = [torch.empty_like(o, device=dev) for _, o in host]
+    d_in = [torch.empty_like(h, device=dev) for h in host]
+    d_off = [d[:b.offsets.size] for d, b in zip(d_in, wl.batches)]
+    d_idx = [d[b.offsets.size:] for d, b in zip(d_in, wl.batches)]
     wl.step(0)
     wl.bag.sync_result()
     torch.cuda.synchronize()
@@ -731,8 +734,7 @@ def run_e2e_multi(args, wl, rank, world, dev):
 
     def step(k):
         j = k % wl.nb
-        d_idx[j].copy_(host[j][0], non_blocking=True)
-        d_off[j].copy_(host[j][1], non_blocking=True)
+        d_in[j].copy_(host[j], non_blocking=True)
         wl.step(k)
         side = wl.bag.side                      # with "push" the result completes on a side stream
         if side is not None:

@@ -20,21 +20,26 @@ namespace {
 struct Slot {
   cudaStream_t stream = nullptr;
   cudaEvent_t done = nullptr;
-  // pinned host staging
-  void* h_idx = nullptr;
-  void* h_off = nullptr;
-  float* h_w = nullptr;
-  void* h_out = nullptr;
-  // device buffers
-  void* d_idx = nullptr;
-  void* d_off = nullptr;
-  float* d_w = nullptr;
+  // One pinned input block and its device twin, laid out [offsets | indices | weights]
+  // (each area 256-byte aligned), so that a call's inputs go up in ONE copy: on a B200 a second,
+  // small host-to-device copy per call costs about 30 us of copy-engine time when copies in both
+  // directions are in flight, far more than its bytes.
+  char* h_in = nullptr;
+  char* d_in = nullptr;
+  void* h_out = nullptr;  // pinned
   void* d_out = nullptr;
   void* d_ws = nullptr;
   size_t ws_bytes = 0;
   bool busy = false;
   int64_t out_rows = 0;
 };
+
+struct Span {
+  size_t begin, end;
+};
+
+// Areas closer than this are sent as one copy, unused bytes between them included.
+constexpr size_t kMergeGapBytes = 1u << 20;
 
 struct DeviceGuard {
   int prev = -1;
@@ -59,6 +64,39 @@ struct fwd_eb_session {
   bool owns_table = false;
   size_t isize = 4, tsize = 4, osize = 4;
   std::vector<Slot> slots;
+  size_t off_at = 0, idx_at = 0, w_at = 0, in_bytes = 0;  // areas of a slot's input block
+
+  void* h_idx(const Slot& sl) const { return sl.h_in + idx_at; }
+  void* h_off(const Slot& sl) const { return sl.h_in + off_at; }
+  float* h_w(const Slot& sl) const {
+    return cfg.weighted ? reinterpret_cast<float*>(sl.h_in + w_at) : nullptr;
+  }
+  void* d_idx(const Slot& sl) const { return sl.d_in + idx_at; }
+  void* d_off(const Slot& sl) const { return sl.d_in + off_at; }
+  float* d_w(const Slot& sl) const {
+    return cfg.weighted ? reinterpret_cast<float*>(sl.d_in + w_at) : nullptr;
+  }
+
+  // The host-to-device copies of one call: the used part of each area, neighbours merged
+  // across small gaps.  Returns the number of spans written to `out` (at most 3).
+  int input_spans(int64_t num_indices, int64_t num_bags, Span* out) const {
+    Span used[3];
+    int n = 0;
+    const int64_t n_off = offsets_per_call(num_bags);
+    if (n_off > 0) used[n++] = {off_at, off_at + (size_t)n_off * isize};
+    if (num_indices > 0) {
+      used[n++] = {idx_at, idx_at + (size_t)num_indices * isize};
+      if (cfg.weighted) used[n++] = {w_at, w_at + (size_t)num_indices * 4};
+    }
+    int m = 0;
+    for (int i = 0; i < n; ++i) {
+      if (m > 0 && used[i].begin - out[m - 1].end <= kMergeGapBytes)
+        out[m - 1].end = used[i].end;
+      else
+        out[m++] = used[i];
+    }
+    return m;
+  }
 
   int64_t offsets_per_call(int64_t bags) const {
     if (cfg.fixed_len > 0 || cfg.mode == FWD_EB_MODE_GATHER) return 0;
@@ -74,13 +112,9 @@ static void release(fwd_eb_session* s) {
   DeviceGuard g(s->device);
   for (Slot& sl : s->slots) {
     if (sl.stream) cudaStreamSynchronize(sl.stream);
-    if (sl.h_idx) cudaFreeHost(sl.h_idx);
-    if (sl.h_off) cudaFreeHost(sl.h_off);
-    if (sl.h_w) cudaFreeHost(sl.h_w);
+    if (sl.h_in) cudaFreeHost(sl.h_in);
     if (sl.h_out) cudaFreeHost(sl.h_out);
-    if (sl.d_idx) cudaFree(sl.d_idx);
-    if (sl.d_off) cudaFree(sl.d_off);
-    if (sl.d_w) cudaFree(sl.d_w);
+    if (sl.d_in) cudaFree(sl.d_in);
     if (sl.d_out) cudaFree(sl.d_out);
     if (sl.d_ws) cudaFree(sl.d_ws);
     if (sl.done) cudaEventDestroy(sl.done);
@@ -145,22 +179,19 @@ int fwd_eb_session_create(const fwd_eb_session_config* cfg, fwd_eb_session** out
   const size_t n_out =
       (size_t)(s->out_rows(cfg->max_indices, cfg->max_bags) > 0 ? s->out_rows(cfg->max_indices, cfg->max_bags) : 1) *
       cfg->dim;
+  auto up256 = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  s->off_at = 0;
+  s->idx_at = up256(n_off * s->isize);
+  s->w_at = s->idx_at + up256(n_idx * s->isize);
+  s->in_bytes = s->w_at + (cfg->weighted ? up256(n_idx * sizeof(float)) : 0);
   s->slots.resize(cfg->depth);
   for (Slot& sl : s->slots) {
     SESSION_CUDA(cudaStreamCreateWithFlags(&sl.stream, cudaStreamNonBlocking), "stream");
     SESSION_CUDA(cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming), "event");
-    SESSION_CUDA(cudaMallocHost(&sl.h_idx, n_idx * s->isize), "pinned indices");
-    SESSION_CUDA(cudaMallocHost(&sl.h_off, n_off * s->isize), "pinned offsets");
+    SESSION_CUDA(cudaMallocHost(reinterpret_cast<void**>(&sl.h_in), s->in_bytes), "pinned inputs");
     SESSION_CUDA(cudaMallocHost(&sl.h_out, n_out * s->osize), "pinned output");
-    SESSION_CUDA(cudaMalloc(&sl.d_idx, n_idx * s->isize), "device indices");
-    SESSION_CUDA(cudaMalloc(&sl.d_off, n_off * s->isize), "device offsets");
+    SESSION_CUDA(cudaMalloc(reinterpret_cast<void**>(&sl.d_in), s->in_bytes), "device inputs");
     SESSION_CUDA(cudaMalloc(&sl.d_out, n_out * s->osize), "device output");
-    if (cfg->weighted) {
-      SESSION_CUDA(cudaMallocHost(reinterpret_cast<void**>(&sl.h_w), n_idx * sizeof(float)),
-                   "pinned weights");
-      SESSION_CUDA(cudaMalloc(reinterpret_cast<void**>(&sl.d_w), n_idx * sizeof(float)),
-                   "device weights");
-    }
   }
   *out = s;
   fwd_eb::clear_error();
@@ -198,9 +229,9 @@ int fwd_eb_session_slot(fwd_eb_session* s, int32_t slot, void** h_indices, void*
   if (!s || slot < 0 || slot >= (int32_t)s->slots.size())
     return fail(FWD_EB_EINVAL, "bad session or slot");
   Slot& sl = s->slots[slot];
-  if (h_indices) *h_indices = sl.h_idx;
-  if (h_offsets) *h_offsets = sl.h_off;
-  if (h_weights) *h_weights = sl.h_w;
+  if (h_indices) *h_indices = s->h_idx(sl);
+  if (h_offsets) *h_offsets = s->h_off(sl);
+  if (h_weights) *h_weights = s->h_w(sl);
   if (h_out) *h_out = sl.h_out;
   return 0;
 }
@@ -208,9 +239,12 @@ int fwd_eb_session_slot(fwd_eb_session* s, int32_t slot, void** h_indices, void*
 int fwd_eb_session_copy_bytes(fwd_eb_session* s, int64_t num_indices, int64_t num_bags,
                               int64_t* h2d, int64_t* d2h) {
   if (!s) return fail(FWD_EB_EINVAL, "null session");
-  if (h2d)
-    *h2d = num_indices * (int64_t)s->isize + s->offsets_per_call(num_bags) * (int64_t)s->isize +
-           (s->cfg.weighted ? num_indices * 4 : 0);
+  if (h2d) {  // what submit really sends, bytes between merged areas included
+    Span spans[3];
+    const int n = s->input_spans(num_indices, num_bags, spans);
+    *h2d = 0;
+    for (int i = 0; i < n; ++i) *h2d += (int64_t)(spans[i].end - spans[i].begin);
+  }
   if (d2h) *d2h = s->out_rows(num_indices, num_bags) * s->cfg.dim * (int64_t)s->osize;
   return 0;
 }
@@ -227,21 +261,14 @@ int fwd_eb_session_submit(fwd_eb_session* s, int32_t slot, int64_t num_indices, 
   if (sl.busy) return fail(FWD_EB_EINVAL, "slot %d is still in flight: wait for it first", slot);
   DeviceGuard g(s->device);
   cudaError_t e;
-  if (num_indices > 0) {
-    e = cudaMemcpyAsync(sl.d_idx, sl.h_idx, (size_t)num_indices * s->isize, cudaMemcpyHostToDevice,
-                        sl.stream);
-    if (e != cudaSuccess) return cuda_fail(e, "indices H2D");
-    if (s->cfg.weighted) {
-      e = cudaMemcpyAsync(sl.d_w, sl.h_w, (size_t)num_indices * 4, cudaMemcpyHostToDevice, sl.stream);
-      if (e != cudaSuccess) return cuda_fail(e, "weights H2D");
-    }
+  Span spans[3];
+  const int n_spans = s->input_spans(num_indices, num_bags, spans);
+  for (int i = 0; i < n_spans; ++i) {
+    e = cudaMemcpyAsync(sl.d_in + spans[i].begin, sl.h_in + spans[i].begin,
+                        spans[i].end - spans[i].begin, cudaMemcpyHostToDevice, sl.stream);
+    if (e != cudaSuccess) return cuda_fail(e, "inputs H2D");
   }
   const int64_t n_off = s->offsets_per_call(num_bags);
-  if (n_off > 0) {
-    e = cudaMemcpyAsync(sl.d_off, sl.h_off, (size_t)n_off * s->isize, cudaMemcpyHostToDevice,
-                        sl.stream);
-    if (e != cudaSuccess) return cuda_fail(e, "offsets H2D");
-  }
 
   fwd_eb_params p;
   memset(&p, 0, sizeof(p));
@@ -250,13 +277,13 @@ int fwd_eb_session_submit(fwd_eb_session* s, int32_t slot, int64_t num_indices, 
   p.dim = s->cfg.dim;
   p.num_rows = s->cfg.num_rows;
   p.row_lo = s->cfg.row_lo;
-  p.indices = sl.d_idx;
-  p.offsets = n_off > 0 ? sl.d_off : nullptr;
+  p.indices = s->d_idx(sl);
+  p.offsets = n_off > 0 ? s->d_off(sl) : nullptr;
   p.index_dtype = s->cfg.index_dtype;
   p.fixed_len = s->cfg.fixed_len;
   p.num_indices = num_indices;
   p.num_bags = s->cfg.mode == FWD_EB_MODE_GATHER ? 0 : num_bags;
-  p.per_sample_weights = s->cfg.weighted ? sl.d_w : nullptr;
+  p.per_sample_weights = s->d_w(sl);
   p.mode = s->cfg.mode;
   p.include_last_offset = s->cfg.include_last_offset;
   p.padding_idx = s->cfg.padding_idx;
@@ -317,15 +344,15 @@ int fwd_eb_session_run(fwd_eb_session* s, const void* h_indices, int64_t num_ind
   const int64_t n_off = s->offsets_per_call(num_bags);
   if (num_indices > 0) {
     if (!h_indices) return fail(FWD_EB_EINVAL, "indices is null");
-    memcpy(sl.h_idx, h_indices, (size_t)num_indices * s->isize);
+    memcpy(s->h_idx(sl), h_indices, (size_t)num_indices * s->isize);
     if (s->cfg.weighted) {
       if (!h_weights) return fail(FWD_EB_EINVAL, "weights are null");
-      memcpy(sl.h_w, h_weights, (size_t)num_indices * 4);
+      memcpy(s->h_w(sl), h_weights, (size_t)num_indices * 4);
     }
   }
   if (n_off > 0) {
     if (!h_offsets) return fail(FWD_EB_EINVAL, "offsets is null");
-    memcpy(sl.h_off, h_offsets, (size_t)n_off * s->isize);
+    memcpy(s->h_off(sl), h_offsets, (size_t)n_off * s->isize);
   }
   rc = fwd_eb_session_submit(s, 0, num_indices, num_bags);
   if (rc) return rc;

@@ -72,8 +72,11 @@ int fwd_eb_session_adopt_table(fwd_eb_session* s, void* d_table);
 int fwd_eb_session_slot(fwd_eb_session* s, int32_t slot, void** h_indices, void** h_offsets,
                         float** h_weights, void** h_out);
 
-/* Queue one call on slot `slot`: host-to-device copies of its inputs, the
- * pooling kernel, device-to-host copy of the result.  Returns at once. */
+/* Queue one call on slot `slot`: host-to-device copy of its inputs, the
+ * pooling kernel, device-to-host copy of the result.  Returns at once.
+ * A slot's offsets, indices and weights live in one pinned block so that they
+ * normally go up as a single copy (areas less than 1 MiB apart are merged,
+ * the unused bytes between them included). */
 int fwd_eb_session_submit(fwd_eb_session* s, int32_t slot, int64_t num_indices, int64_t num_bags);
 
 /* Block until slot `slot`'s result is in its h_out. */
@@ -84,7 +87,8 @@ int fwd_eb_session_run(fwd_eb_session* s, const void* h_indices, int64_t num_ind
                        const void* h_offsets, int64_t num_bags, const float* h_weights,
                        void* h_out);
 
-/* Bytes moved per submit for the sizes given: host-to-device and device-to-host. */
+/* Bytes moved per submit for the sizes given: host-to-device (bytes between
+ * merged areas included) and device-to-host. */
 int fwd_eb_session_copy_bytes(fwd_eb_session* s, int64_t num_indices, int64_t num_bags,
                               int64_t* h2d, int64_t* d2h);
 
