@@ -2,7 +2,7 @@
 """Throughput of the EmbeddingBag gather-and-pool path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload auto|c2|tablewise|rowshard|c5|c3] [--exchange push|a2a|nccl]
+                    [--workload auto|c2|tablewise|rowshard|c5|c3|c4] [--exchange push|a2a|nccl]
                     [--wire f32|f16]
 
 One "step" is one pooled call over one synthetic batch.  Rank 0 prints ONE JSON line.
@@ -21,6 +21,11 @@ Workloads (all synthetic: shapes and distributions only, rotating index batches 
              bags of 1..100 uniform indices, sum.  Strong scaling.
   c3         N = 1.  Table 4,000,000 x 256 fp16, 8192 bags of 0..64 uniform indices, 5 % of the
              indices are padding_idx 0, max pooling.
+  c4         N >= 1.  26 tables of 1e3..3e7 rows x 128 fp32 (42 GB in all), 65536 bags of exactly
+             20 Zipf(1.1) indices per table with per-sample weights, sum.  Tables are placed
+             whole on ranks (greedy by lookups, then bytes); every rank pools the whole batch
+             for its tables and the pooled rows go to [65536/N, 26, 128] fp32 on the rank owning
+             the bag.  Strong scaling; N = 1 holds all 26 tables.
   auto       c2 at N = 1, tablewise at N > 1.
 
 `value` times K steps on data resident in HBM (CUDA events, barrier + synchronize on both sides,
@@ -47,10 +52,12 @@ if ROOT not in sys.path:
 NUM_BATCHES = 8
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the pooling kernel, from the ncu
 # captures summarised under profiles/ (None where no capture of that workload exists yet).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 35.9e6, "tablewise": None, "rowshard": None, "c5": None, "c3": 129.9e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 35.9e6, "tablewise": None, "rowshard": None, "c5": None, "c3": 129.9e6,
+                             "c4": None}
 C2 = dict(rows=1_000_000, dim=128, bags=16384)
 C5 = dict(rows=1_000_000_000, dim=64, bags=131072)
 C3 = dict(rows=4_000_000, dim=256, bags=8192)
+C4 = dict(tables=26, dim=128, bags=65536, pooling=20, cpu_row_cap=1 << 19)
 
 
 # ---- clocks --------------------------------------------------------------------------
@@ -192,6 +199,14 @@ def describe(workload: str, world: int, args):
                     bags_per_step=C5["bags"], table_rows=C5["rows"], dim=C5["dim"],
                     parallelism=f"rowshard{world}" if world > 1 else "single",
                     exchange=args.exchange if world > 1 else None, wire=args.wire)
+    elif workload == "c4":
+        base.update(workload="c4: 26 tables of 1e3..3e7 rows x 128 fp32 (42 GB), 65536 bags x 20 Zipf(1.1) "
+                             "indices per table, per-sample weights, sum; tables placed whole on ranks, "
+                             f"pooled rows exchanged to [65536/{world}, 26, 128] fp32 per rank",
+                    bags_per_step=C4["bags"], tables=C4["tables"], dim=C4["dim"],
+                    parallelism=f"tablewise{world}" if world > 1 else "single",
+                    exchange=args.exchange if world > 1 else None,
+                    l2_policy="no flush: one step reads 18 GB of rows from 42 GB of tables")
     elif workload == "c3":
         base.update(workload="c3: EmbeddingBag max, table 4000000x256 fp16, 8192 bags/step of 0..64 "
                              "uniform indices, 5% padding_idx=0",
@@ -200,7 +215,7 @@ def describe(workload: str, world: int, args):
 
 
 def scaling_kind(workload: str) -> str:
-    return "strong" if workload == "c5" else "weak"
+    return "strong" if workload in ("c5", "c4") else "weak"
 
 
 # ---- CPU arms ----------------------------------------------------------------------------
@@ -251,16 +266,33 @@ class CpuWorkload:
             self.tables = [torch.from_numpy(host_table(C3["rows"], C3["dim"], 0, 2, 0.1))]
             self.batches = [make_batches(workload, world)]
             self.mode, self.pad = "max", 0
+        elif workload == "c4":
+            from forward_b200 import workloads
+            cap = C4["cpu_row_cap"]
+            self.mode = "sum"
+            self.tables, self.batches, self.prepared = [], [], []
+            for t, rows in enumerate(workloads.config4_rows()):
+                held = int(min(rows, cap))
+                # values do not affect timing: a plain normal draw instead of the counter generator
+                self.tables.append(torch.empty((held, C4["dim"]), dtype=torch.float32).normal_(0, 0.1))
+                b = workloads.config4_bags(t, int(rows))
+                self.batches.append([b])
+                i = torch.from_numpy((b.indices % held).astype(np.int64)).view(-1, C4["pooling"])
+                w = torch.from_numpy(b.per_sample_weights).view(-1, C4["pooling"])
+                self.prepared.append([(i, None, w)])
+            self.note = f" (tables above {cap} rows cut to {cap} rows, indices folded: same lookups)"
+            return
         self.prepared = [[(torch.from_numpy(b.indices.astype(np.int64)),
-                           torch.from_numpy(b.offsets.astype(np.int64))) for b in bs]
+                           torch.from_numpy(b.offsets.astype(np.int64)), None) for b in bs]
                          for bs in self.batches]
 
     def step(self, k: int) -> int:
         done = 0
         for t, table in enumerate(self.tables):
             nb = len(self.prepared[t])
-            i, o = self.prepared[t][k % nb]
-            self.F.embedding_bag(i, table, o, mode=self.mode, padding_idx=self.pad)
+            i, o, w = self.prepared[t][k % nb]
+            self.F.embedding_bag(i, table, o, mode=self.mode, padding_idx=self.pad,
+                                 per_sample_weights=w)
             done += self.batches[t][k % nb].num_indices
         return done
 
@@ -285,6 +317,8 @@ def run_reference(args, world: int, rank: int):
     if rank != 0:
         return
     workload = resolve_workload(args.workload, world)
+    if workload == "c4":       # a step is 34 M lookups (a quarter of a second of CPU time)
+        args.steps, args.warmup = min(args.steps, 40), min(args.warmup, 3)
     cw = CpuWorkload(workload, world)
     for k in range(args.warmup):
         cw.step(k)
@@ -298,7 +332,8 @@ def run_reference(args, world: int, rank: int):
         "impl": "reference", "metric": "pooled_lookups_per_sec", "value": value,
         "unit": "lookups/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": scaling_kind(workload), "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "scaling": scaling_kind(workload), "vs_baseline": None,
+        "dtype": "f32" if workload == "c4" else "f16", "data": "synthetic",
         "config": describe(workload, world, args),
         "cpu_baseline": {"value": value, "unit": "lookups/s", "cores": cw.cores, "kind": "port",
                          "sample": f"torch CPU EmbeddingBag on whole {workload} steps{cw.note}, "
@@ -438,10 +473,212 @@ class GpuWorkload:
             num_bags=b.num_bags, out_itemsize=self.out_itemsize)
 
 
+class C4Workload:
+    """Config 4 on this rank: the tables placed here, their fixed-length weighted batches, and
+    the step that pools every local table for the whole batch (N > 1: with the pooled rows
+    pushed to the bags' owner ranks).  Same surface as GpuWorkload where run_ours() uses it."""
+
+    workload = "c4"
+
+    def __init__(self, world: int, rank: int, dev, args):
+        import torch
+
+        from forward_b200 import capi, workloads
+        from forward_b200 import dist as fd
+        self.world, self.rank, self.dev, self.args = world, rank, dev, args
+        self.capi, self.torch = capi, torch
+        self.dim, self.mode, self.pad = C4["dim"], capi.MODE_SUM, -1
+        self.out_itemsize = 4
+        self.L = C4["pooling"]
+        self.rows = [int(r) for r in workloads.config4_rows()]
+        self.T = len(self.rows)
+        n_per_table = C4["bags"] * self.L
+        self.owner = fd.place_tables([r * self.dim * 4 for r in self.rows], world,
+                                     [n_per_table] * self.T)
+        self.mine = [t for t in range(self.T) if self.owner[t] == rank]
+        self.tables, self.bags, self.h_in, self.d_in, self.d_idx, self.d_w = {}, {}, {}, {}, {}, {}
+        for t in self.mine:
+            tab = torch.empty((self.rows[t], self.dim), dtype=torch.float32, device=dev)
+            capi.fill_table(tab, 0, seed=300 + t, scale=0.1)
+            self.tables[t] = tab
+            b = workloads.config4_bags(t, self.rows[t])
+            self.bags[t] = b
+            # indices and weights of a table share one pinned block: one copy per table per step
+            blk = np.concatenate([b.indices, b.per_sample_weights.view(np.int32)])
+            self.h_in[t] = torch.from_numpy(blk).pin_memory()
+            self.d_in[t] = self.h_in[t].to(dev)
+            self.d_idx[t] = self.d_in[t][:n_per_table]
+            self.d_w[t] = self.d_in[t][n_per_table:].view(torch.float32)
+        self.batches = [workloads.Bags(np.empty(n_per_table, dtype=np.int32), None, fixed_len=self.L)]
+        self.bag = None
+        self.pool_only = None
+        self._last = None
+        stream = torch.cuda.current_stream()
+        self.launches_per_step = len(self.mine)
+        if world == 1:
+            out = torch.empty((C4["bags"], self.T, self.dim), dtype=torch.float32, device=dev)
+            params = [capi.make_params(self.tables[t], self.d_idx[t], None, out=out[:, t, :],
+                                       mode=self.mode, fixed_len=self.L,
+                                       per_sample_weights=self.d_w[t]) for t in self.mine]
+
+            def step(k, events=None):
+                if events:
+                    events[0].record()
+                for p in params:
+                    capi.forward(p, stream.cuda_stream)
+                if events:
+                    events[1].record()
+                self._last = out
+            self.step = step
+            return
+        self.bag = fd.TableWiseBags(self.tables, self.owner, dim=self.dim, max_bags=C4["bags"],
+                                    exchange=args.exchange, wire_dtype=capi.F32, mode=self.mode,
+                                    fixed_len=self.L)
+        prepared = self.bag.prepare({t: (self.d_idx[t], None, self.d_w[t]) for t in self.mine})
+
+        def step(k, events=None):
+            self._last = self.bag.forward(prepared, pool_events=events)
+        self.step = step
+        local = torch.empty((C4["bags"], max(1, len(self.mine)), self.dim), dtype=torch.float32,
+                            device=dev)
+        lp = [capi.make_params(self.tables[t], self.d_idx[t], None, out=local[:, j, :], mode=self.mode,
+                               fixed_len=self.L, per_sample_weights=self.d_w[t])
+              for j, t in enumerate(self.mine)]
+
+        def pool_only(k):
+            for p in lp:
+                capi.forward(p, stream.cuda_stream)
+        self.pool_only = pool_only
+
+    def result(self):
+        return self._last
+
+    def lookups(self, k: int) -> int:
+        return len(self.mine) * C4["bags"] * self.L
+
+    def algorithmic_bytes(self, k: int) -> float:
+        from forward_b200 import workloads
+        n = C4["bags"] * self.L
+        return float(len(self.mine) * workloads.algorithmic_bytes(
+            gathered_rows=n, dim=self.dim, table_itemsize=4, num_indices=n, num_offsets=0,
+            index_itemsize=4, num_bags=C4["bags"], out_itemsize=4, weighted=True))
+
+    def egress_bytes(self) -> int:
+        """Pooled bytes this rank sends to other ranks per step."""
+        return len(self.mine) * C4["bags"] * (self.world - 1) // self.world * self.dim * 4
+
+    def verify(self) -> bool:
+        """A sample of the bags of EVERY rank, gathered to every rank; each rank checks the column
+        blocks of its own tables against the CPU oracle (so every peer store path is covered)."""
+        import torch
+
+        from oracle import eb_oracle as O
+        self.step(0)
+        if self.bag is not None:
+            self.bag.sync_result()
+        torch.cuda.synchronize()
+        per = -(-C4["bags"] // self.world)
+        local_rows = np.arange(0, per, max(1, per // 256))
+        sample = self._last[torch.from_numpy(local_rows).to(self.dev)].contiguous()
+        if self.world > 1:
+            import torch.distributed as dist
+            parts = [torch.empty_like(sample) for _ in range(self.world)]
+            dist.all_gather(parts, sample)
+        else:
+            parts = [sample]
+        ok = True
+        for r, part in enumerate(parts):
+            got = part.cpu().numpy()
+            take = local_rows + r * per
+            keep = take < C4["bags"]
+            take = take[keep]
+            for t in self.mine:
+                b = self.bags[t]
+                idx = b.indices.reshape(-1, self.L)[take].reshape(-1)
+                w = b.per_sample_weights.reshape(-1, self.L)[take].reshape(-1)
+                uniq, inv = np.unique(idx, return_inverse=True)
+                compact = O.table_rows(uniq, self.dim, seed=300 + t, scale=0.1, dtype=np.float32)
+                exp = O.pool(compact, inv.astype(np.int32), None, mode=O.MODE_SUM, fixed_len=self.L,
+                             per_sample_weights=w, out_dtype=np.float32)
+                ok = ok and bool(np.allclose(got[keep][:, t, :], exp, rtol=1e-5, atol=1e-6))
+        if self.world > 1:
+            flag = torch.tensor([1 if ok else 0], device=self.dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok = bool(flag.item())
+        return ok
+
+    def run_e2e(self, args):
+        """Every step: one host-to-device copy per local table (indices + weights from pinned
+        memory), the step, and this rank's result copied back to pinned memory.  N = 1: results
+        alternate between two device buffers and go back on a second stream, so a step's
+        copy-out overlaps the next step's copy-in and pooling."""
+        import torch
+        capi = self.capi
+        self.step(0)
+        if self.bag is not None:
+            self.bag.sync_result()
+        torch.cuda.synchronize()
+        res = self.result()
+        h_out = [torch.empty(tuple(res.shape), dtype=res.dtype).pin_memory() for _ in range(2)]
+        steps = max(3, min(args.steps, 50))
+        main = torch.cuda.current_stream()
+        if self.world == 1:
+            outs = [res, torch.empty_like(res)]
+            params = [[capi.make_params(self.tables[t], self.d_idx[t], None, out=o[:, t, :],
+                                        mode=self.mode, fixed_len=self.L,
+                                        per_sample_weights=self.d_w[t]) for t in self.mine]
+                      for o in outs]
+            back = torch.cuda.Stream()
+            pooled = [torch.cuda.Event() for _ in range(2)]
+            copied = [torch.cuda.Event() for _ in range(2)]
+
+            def step(k):
+                j = k % 2
+                for t in self.mine:
+                    self.d_in[t].copy_(self.h_in[t], non_blocking=True)
+                main.wait_event(copied[j])          # outs[j] was last read by the copy-out of step k-2
+                for p in params[j]:
+                    capi.forward(p, main.cuda_stream)
+                pooled[j].record(main)
+                with torch.cuda.stream(back):
+                    back.wait_event(pooled[j])
+                    h_out[j].copy_(outs[j], non_blocking=True)
+                    copied[j].record(back)
+        else:
+            def step(k):
+                for t in self.mine:
+                    self.d_in[t].copy_(self.h_in[t], non_blocking=True)
+                self.step(k)
+                self.bag.sync_result()
+                h_out[k % 2].copy_(self.result(), non_blocking=True)
+
+        for k in range(3):
+            step(k)
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for k in range(steps):
+            step(k)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        if self.world > 1:
+            tt = torch.tensor([dt], dtype=torch.float64, device=self.dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt = float(tt.item())
+        h2d = sum(self.h_in[t].numel() * 4 for t in self.mine)
+        d2h = h_out[0].numel() * h_out[0].element_size()
+        return {"value": self.T * C4["bags"] * self.L * steps / dt, "unit": "lookups/s",
+                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                "ms_per_step": dt / steps * 1e3, "steps": steps, "note": "bytes are per rank",
+                "api": "fwd_eb_forward per table" if self.world == 1 else "forward_b200.dist TableWiseBags.forward"}
+
+
 def total_lookups(wl, steps: int, dev) -> float:
     """Whole-job lookups over `steps` steps: table-wise ranks each look up their own table."""
     n = float(sum(wl.lookups(k) for k in range(steps)))
-    if wl.world > 1 and wl.workload == "tablewise":
+    if wl.world > 1 and wl.workload in ("tablewise", "c4"):
         import torch
         import torch.distributed as dist
         t = torch.tensor([n], dtype=torch.float64, device=dev)
@@ -464,7 +701,8 @@ def run_ours(args, world: int, rank: int, local_rank: int):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     workload = resolve_workload(args.workload, world)
-    wl = GpuWorkload(workload, world, rank, dev, args)
+    wl = C4Workload(world, rank, dev, args) if workload == "c4" else \
+        GpuWorkload(workload, world, rank, dev, args)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps)]
 
     def barrier():
@@ -474,7 +712,7 @@ def run_ours(args, world: int, rank: int, local_rank: int):
 
     # bring clocks up before the counted warm-up; a fixed count when ranks must stay in step
     if multi:
-        for k in range(int(args.preheat_ms * 4)):
+        for k in range(200 if workload == "c4" else int(args.preheat_ms * 4)):
             wl.step(k)
             if k % 64 == 63:
                 torch.cuda.synchronize()
@@ -530,7 +768,8 @@ def run_ours(args, world: int, rank: int, local_rank: int):
         total_ms, pool_only_us = float(tt[0].item()), float(tt[1].item())
         step_us = total_ms * 1e3 / args.steps
         bags_n = wl.batches[0].num_bags
-        egress = bags_n * (world - 1) // world * wl.dim * wl.out_itemsize
+        egress = wl.egress_bytes() if hasattr(wl, "egress_bytes") else \
+            bags_n * (world - 1) // world * wl.dim * wl.out_itemsize
         exchange = {"method": args.exchange, "wire": "f16" if wl.out_itemsize == 2 else "f32",
                     "pool_only_us": pool_only_us, "step_us": step_us,
                     "overhead_frac": (step_us - pool_only_us) / pool_only_us,
@@ -548,10 +787,16 @@ def run_ours(args, world: int, rank: int, local_rank: int):
                 "kernel_us_median": float(np.median(kernel_ms) * 1e3),
                 "algorithmic_bytes_per_launch": alg}
 
-    verified = None if args.no_verify else verify(wl, workload, world, rank)
-    e2e = None
-    if not args.no_e2e:
-        e2e = run_e2e_multi(args, wl, rank, world, dev) if multi else run_e2e(args, wl)
+    if workload == "c4":
+        roofline["launches_per_step"] = wl.launches_per_step
+        roofline["note"] = "kernel_us_* and the bytes cover one step = all of this rank's tables"
+        verified = None if args.no_verify else wl.verify()
+        e2e = None if args.no_e2e else wl.run_e2e(args)
+    else:
+        verified = None if args.no_verify else verify(wl, workload, world, rank)
+        e2e = None
+        if not args.no_e2e:
+            e2e = run_e2e_multi(args, wl, rank, world, dev) if multi else run_e2e(args, wl)
     cpu = None
     if rank == 0 and not multi and not args.no_cpu_baseline:
         cpu = cpu_baseline(workload, world, args.cpu_seconds)
@@ -562,7 +807,8 @@ def run_ours(args, world: int, rank: int, local_rank: int):
             "metric": "pooled_lookups_per_sec", "value": value, "unit": "lookups/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": scaling_kind(workload), "vs_baseline": None, "dtype": "f16",
+            "scaling": scaling_kind(workload), "vs_baseline": None,
+            "dtype": "f32" if workload == "c4" else "f16",
             "data": "synthetic", "config": describe(workload, world, args), "roofline": roofline,
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "verified_against_oracle": verified,
@@ -770,7 +1016,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto",
-                    choices=["auto", "c2", "tablewise", "rowshard", "c5", "c3"])
+                    choices=["auto", "c2", "tablewise", "rowshard", "c5", "c3", "c4"])
     ap.add_argument("--exchange", default="push", choices=["push", "a2a", "nccl"],
                     help="N>1: how pooled rows / partial bags reach their owners")
     ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
