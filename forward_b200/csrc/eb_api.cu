@@ -261,11 +261,12 @@ static cudaError_t launch_pool(const Plan& pl, cudaStream_t st) {
   const PoolArgs& a = pl.a;
   if (pl.strategy == FWD_EB_STRATEGY_GROUP) {
     const long long threads = a.num_bags << a.lanes_log2;
-    const long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+    const int cta = group_cta_threads(a.lanes_log2);
+    const long long blocks = (threads + cta - 1) / cta;
     if (blocks == 0) return cudaSuccess;
     if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
     dim3 grid((unsigned)blocks, (unsigned)pl.tiles);
-    eb_pool_group_kernel<TW, VE, CPL, OP, U, IPL><<<grid, kCtaThreads, 0, st>>>(a);
+    eb_pool_group_kernel<TW, VE, CPL, OP, U, IPL><<<grid, cta, 0, st>>>(a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return cudaGetLastError();
   }

@@ -54,7 +54,7 @@ template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 __global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
   const int lanes_log2 = a.lanes_log2;
-  const long long bag = ((long long)blockIdx.x * kCtaThreads + threadIdx.x) >> lanes_log2;
+  const long long bag = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> lanes_log2;
   const int chunk0 = blockIdx.y * (CPL << lanes_log2);
   const bool live = bag < a.num_bags;
   long long start = 0, end = 0;
@@ -220,14 +220,15 @@ template <typename TW, int VE, int CPL, int U, int IPL>
 static cudaError_t launch_push(const PoolArgs& a, const PushArgs& x, int tiles, bool weighted,
                                cudaStream_t st) {
   const long long threads = a.num_bags << a.lanes_log2;
-  const long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+  const int cta = group_cta_threads(a.lanes_log2);
+  const long long blocks = (threads + cta - 1) / cta;
   if (blocks == 0) return cudaSuccess;
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)blocks, (unsigned)tiles);
   if (weighted) {
-    eb_pool_push_kernel<TW, VE, CPL, kOpWeighted, U, IPL><<<grid, kCtaThreads, 0, st>>>(a, x);
+    eb_pool_push_kernel<TW, VE, CPL, kOpWeighted, U, IPL><<<grid, cta, 0, st>>>(a, x);
   } else {
-    eb_pool_push_kernel<TW, VE, CPL, kOpSum, U, IPL><<<grid, kCtaThreads, 0, st>>>(a, x);
+    eb_pool_push_kernel<TW, VE, CPL, kOpSum, U, IPL><<<grid, cta, 0, st>>>(a, x);
   }
   count_launch();
   return cudaGetLastError();
