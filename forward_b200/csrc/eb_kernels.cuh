@@ -547,6 +547,12 @@ eb_pool_group_kernel(const PoolArgs a) {
       ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> lanes_log2;
   const int chunk0 = blockIdx.y * (CPL << lanes_log2);
   const bool live = bag < a.num_bags;
+  // Programmatic dependent launch: let the next grid on the stream (if it was launched with
+  // programmatic stream serialization) place its CTAs while this grid's last ones drain, and
+  // touch no memory before every grid ahead of this one has completed.  Both are no-ops for
+  // an ordinary launch.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   long long start = 0, end = 0;
   if (live) bag_bounds(a, bag, start, end);
 

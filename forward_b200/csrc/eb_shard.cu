@@ -24,8 +24,10 @@ struct PushArgs {
   long long bags_per_rank;
   long long row_base;    // destination row of this rank's first bag inside the owner's buffer
   long long col_offset;  // destination column of this call's first column
+  long long first_bag;   // bag the grid starts with; later bags follow, wrapping at num_bags
   int world;
   int rank;
+  int small;             // bag numbers and bags_per_rank fit 32 bits
   uint32_t epoch;
 };
 
@@ -54,9 +56,16 @@ template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 __global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
   const int lanes_log2 = a.lanes_log2;
-  const long long bag = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> lanes_log2;
+  const long long seq = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> lanes_log2;
   const int chunk0 = blockIdx.y * (CPL << lanes_log2);
-  const bool live = bag < a.num_bags;
+  const bool live = seq < a.num_bags;
+  // The grid starts with the bags of the next rank and ends with this rank's own, so the
+  // stores that cross NVLink are issued first and the grid's tail stores locally.
+  long long bag = seq + x.first_bag;
+  if (bag >= a.num_bags) bag -= a.num_bags;
+  // programmatic dependent launch, as in eb_pool_group_kernel
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   long long start = 0, end = 0;
   if (live) bag_bounds(a, bag, start, end);
 
@@ -69,7 +78,10 @@ eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
   for (int c = 0; c < CPL; ++c)
 #pragma unroll
     for (int e = 0; e < VE; ++e) s.v[c][e] = finish(a, s.v[c][e], s.counted, end - start, tf16);
-  long long owner = live ? bag / x.bags_per_rank : 0;
+  // bag / bags_per_rank: 32-bit when it fits (a 64-bit division is some hundred instructions)
+  long long owner = 0;
+  if (live)
+    owner = x.small ? (long long)((unsigned)bag / (unsigned)x.bags_per_rank) : bag / x.bags_per_rank;
   if (owner >= x.world) owner = x.world - 1;
   const long long local_bag = bag - owner * x.bags_per_rank;
   // this rank's slot (row shards) or this table's column block (table-wise) at the owner
@@ -225,13 +237,20 @@ static cudaError_t launch_push(const PoolArgs& a, const PushArgs& x, int tiles, 
   if (blocks == 0) return cudaSuccess;
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   dim3 grid((unsigned)blocks, (unsigned)tiles);
-  if (weighted) {
-    eb_pool_push_kernel<TW, VE, CPL, kOpWeighted, U, IPL><<<grid, cta, 0, st>>>(a, x);
-  } else {
-    eb_pool_push_kernel<TW, VE, CPL, kOpSum, U, IPL><<<grid, cta, 0, st>>>(a, x);
-  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3((unsigned)cta);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];  // see launch_pool in eb_api.cu
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = weighted
+      ? cudaLaunchKernelEx(&cfg, eb_pool_push_kernel<TW, VE, CPL, kOpWeighted, U, IPL>, a, x)
+      : cudaLaunchKernelEx(&cfg, eb_pool_push_kernel<TW, VE, CPL, kOpSum, U, IPL>, a, x);
   count_launch();
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 template <typename TW>
@@ -281,6 +300,9 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
   if (rc) return rc;
   PushArgs px;
   fill_push(x, p->dim, &px);
+  px.first_bag = (long long)((x->rank + 1) % x->world) * x->bags_per_rank;
+  if (px.first_bag >= p->num_bags) px.first_bag = 0;
+  px.small = p->num_bags <= 0x7fffffffLL && x->bags_per_rank <= 0x7fffffffLL;
   const bool weighted = p->per_sample_weights != nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e = p->table_dtype == FWD_EB_F16
