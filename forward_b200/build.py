@@ -144,9 +144,28 @@ def build_torch(force: bool = False, verbose: bool = False) -> str | None:
     return target
 
 
+def build_tf(force: bool = False, verbose: bool = False) -> str | None:
+    """The TensorFlow parser slice (own GraphDef reader: no TensorFlow needed)."""
+    tdir = os.path.join(CSRC, "tf_cvt")
+    pdir = os.path.join(CSRC, "plugin")
+    if not os.path.isdir(tdir):
+        return None
+    plugin = build_plugin(force, verbose)
+    target = os.path.join(LIBDIR, "libfwd_eb_tf.so")
+    srcs = _walk(tdir, (".cpp",))
+    deps = srcs + _walk(tdir, (".h",)) + _walk(pdir, (".h",)) + [plugin]
+    if force or _stale(target, deps):
+        gxx = shutil.which("g++") or "g++"
+        cmd = [gxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-I", "/usr/local/cuda/include",
+               "-I", tdir, "-I", pdir, "-I", os.path.join(pdir, "trt_shim"), "-o", target] + srcs + [
+            "-L", LIBDIR, "-lfwd_eb_plugin", "-Wl,-rpath,$ORIGIN"]
+        _run(cmd, verbose)
+    return target
+
+
 def build_all(force: bool = False, verbose: bool = False) -> list[str]:
     out = [build_core(force, verbose)]
-    for step in (build_plugin, build_torch):
+    for step in (build_plugin, build_tf, build_torch):
         p = step(force, verbose)
         if p:
             out.append(p)

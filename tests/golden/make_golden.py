@@ -12,6 +12,13 @@ embedding_bag_pth.npz   weights of the reference's own fixture
                         and of its trace call (unit_test_model_factory.py:301), and the
                         outputs the loaded TorchScript module gives for both on CPU —
                         the ground truth the reference test compares its engine with.
+embedding_bag_pb.npz    the table of the reference's TensorFlow fixture
+                        data/tf_unit_tests/embedding_bag.pb (read with the protobuf
+                        reader in tests/tf_graphdef.py; TensorFlow is not needed), seeded
+                        indices of the shape its unit test draws
+                        (source/unit_test/test_tf_nodes.h:199-211: int32 [10, 5] in
+                        [0, 50)), and what the graph computes for them in numpy: the
+                        two pooled terms and its output "sub" = Sum^2 - Sum_1.
 torch_cpu_cases.npz     torch CPU EmbeddingBag outputs for small seeded cases that
                         the reference never tests (mean, max, fp16, padding_idx,
                         per_sample_weights, include_last_offset, empty bags).
@@ -46,6 +53,29 @@ def reference_fixture(ref_root: str) -> None:
         out[f"{name}_offsets"] = o.numpy()
         out[f"{name}_expected"] = y.numpy()
     np.savez(os.path.join(HERE, "embedding_bag_pth.npz"), **out)
+
+
+def tf_reference_fixture(ref_root: str) -> None:
+    sys.path.insert(0, os.path.dirname(HERE))
+    import tf_graphdef as G
+    path = os.path.join(ref_root, "data", "tf_unit_tests", "embedding_bag.pb")
+    nodes = G.read_nodes(open(path, "rb").read())
+    gather = nodes["embedding_lookup"]
+    assert gather["op"] == "GatherV2" and nodes["Sum"]["op"] == "Sum" and nodes["sub"]["op"] == "Sub"
+    table_node = nodes[gather["inputs"][0]]
+    while table_node["op"] == "Identity":
+        table_node = nodes[table_node["inputs"][0]]
+    weight = G.const_value(table_node["attrs"]["value"])
+    rng = np.random.default_rng(199)
+    indices = rng.integers(0, weight.shape[0], (10, 5)).astype(np.int32)
+    e = weight[indices].astype(np.float32)             # mask = sequence_mask(5, 5): all ones
+    s = np.zeros((10, weight.shape[1]), dtype=np.float32)
+    q = np.zeros_like(s)
+    for l in range(indices.shape[1]):                  # in bag order, fp32, like the kernels
+        s = s + e[:, l, :]
+        q = q + e[:, l, :] * e[:, l, :]
+    np.savez(os.path.join(HERE, "embedding_bag_pb.npz"), weight=weight, indices=indices,
+             sum=s, square_sum=q, sub=s * s - q)
 
 
 def torch_cases() -> None:
@@ -104,5 +134,6 @@ def torch_cases() -> None:
 if __name__ == "__main__":
     root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     reference_fixture(root)
+    tf_reference_fixture(root)
     torch_cases()
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
