@@ -2,7 +2,7 @@
 """Throughput of the EmbeddingBag gather-and-pool path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload auto|c2|tablewise|rowshard|c5|c3|c4] [--exchange push|a2a|nccl]
+                    [--workload auto|c2|tablewise|rowshard|c5|c3|c4] [--exchange push|stage|a2a|nccl]
                     [--wire f32|f16]
 
 One "step" is one pooled call over one synthetic batch.  Rank 0 prints ONE JSON line.
@@ -429,7 +429,7 @@ class GpuWorkload:
             wire = capi.F16 if args.wire == "f16" else capi.F32
             self.bag = fd.RowShardedBag(self.table, self.row_lo, mode=self.mode, max_bags=bags_n,
                                         exchange=args.exchange, wire_dtype=wire)
-            self.out_itemsize = 2 if (args.exchange == "push" and args.wire == "f16") else 4
+            self.out_itemsize = 2 if (args.exchange in ("push", "stage") and args.wire == "f16") else 4
 
             self._prepared = [self.bag.prepare(i, o) for i, o in self.d_batches]
 
@@ -1030,8 +1030,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto",
                     choices=["auto", "c2", "tablewise", "rowshard", "c5", "c3", "c4"])
-    ap.add_argument("--exchange", default="push", choices=["push", "a2a", "nccl"],
-                    help="N>1: how pooled rows / partial bags reach their owners")
+    ap.add_argument("--exchange", default="push", choices=["push", "stage", "a2a", "nccl"],
+                    help="N>1: how pooled rows / partial bags reach their owners (stage: row shards "
+                         "only, copy engines instead of the pooling kernel's own peer stores)")
     ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
                     help="row shards with --exchange push: element type of the partials on NVLink")
     ap.add_argument("--no-e2e", action="store_true")

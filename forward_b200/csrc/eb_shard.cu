@@ -482,6 +482,61 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
   return 0;
 }
 
+int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_params* p,
+                                         fwd_eb_shard_exchange* x, int64_t num_bags_owned,
+                                         void* const d_stage[FWD_EB_SHARD_BUFFERS],
+                                         void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
+                                         void* main_stream, int32_t* which) {
+  if (!pl || !p || !x || !d_out || !d_stage) return fail(FWD_EB_EINVAL, "null argument");
+  int rc = 0;
+  if (x->layout != FWD_EB_LAYOUT_ROW_SHARD)
+    return fail(FWD_EB_EINVAL, "the staged exchange is for the row-shard layout");
+  if (p->mode != FWD_EB_MODE_SUM && p->mode != FWD_EB_MODE_MEAN)
+    return fail(FWD_EB_EUNSUPPORTED, "sharded pooling supports SUM and MEAN (got mode %d)", p->mode);
+  if (p->num_bags > x->bags_per_rank * x->world)
+    return fail(FWD_EB_EINVAL, "%lld bags do not fit %d ranks x %lld bags", (long long)p->num_bags,
+                x->world, (long long)x->bags_per_rank);
+  cudaStream_t main = static_cast<cudaStream_t>(main_stream);
+  rc = pipeline_begin(pl, x, main);
+  if (rc) return rc;
+  rc = check_exchange(x);
+  if (rc) return rc;
+  const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
+  if (!d_stage[k] || !d_out[k]) return fail(FWD_EB_EINVAL, "null staging or output buffer");
+  // 1. pool every bag's partial into local staging (the plain lane-group kernel)
+  fwd_eb_params q = *p;
+  q.strategy = FWD_EB_STRATEGY_GROUP;
+  q.out = d_stage[k];
+  q.out_dtype = x->wire_dtype;
+  q.out_stride = 0;
+  q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean
+  rc = fwd_eb_forward(&q, main);
+  if (rc) return rc;
+  rc = pipeline_handover(pl, main);
+  if (rc) return rc;
+  // 2. one copy-engine transfer per owner: its block of partial bags -> slot [rank] over there
+  const size_t esize = x->wire_dtype == FWD_EB_F16 ? 2 : 4;
+  const size_t row_bytes = (size_t)p->dim * esize;
+  const size_t part = half_bytes(x, p->dim) * (size_t)k;
+  for (int i = 0; i < x->world; ++i) {
+    const int r = (x->rank + 1 + i) % x->world;  // peers first, own block last
+    long long rows = p->num_bags - (long long)r * x->bags_per_rank;
+    if (rows > x->bags_per_rank) rows = x->bags_per_rank;
+    if (rows <= 0) continue;
+    const char* src = static_cast<const char*>(d_stage[k]) + (size_t)r * x->bags_per_rank * row_bytes;
+    char* dst = static_cast<char*>(x->peer_slots[r]) + part + (size_t)x->rank * x->bags_per_rank * row_bytes;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)rows * row_bytes, cudaMemcpyDefault, pl->side);
+    if (e != cudaSuccess) return cuda_fail(e, "copying a block of partial bags to its owner");
+  }
+  // 3. flags (raised by the kernel that follows the copies on the stream), bounded wait, fold
+  rc = fwd_eb_shard_combine(x, p->dim, num_bags_owned, d_out[k], out_dtype, pl->side);
+  if (rc) return rc;
+  cudaError_t e = cudaEventRecord(pl->done[k], pl->side);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord (side)");
+  if (which) *which = k;
+  return 0;
+}
+
 int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
                                    const int32_t* table_index, int32_t count,
                                    fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,

@@ -11,6 +11,9 @@ batch, pools what it owns into partial bags, and bag b ends up, summed, on rank 
   exchange="push"  fwd_eb_pipeline_step_rowshard: partial rows go straight into the owner's slots
                    over NVLink from inside the pooling kernel; the flag exchange and the fold run on
                    a side stream beside the next call's pooling
+  exchange="stage" fwd_eb_pipeline_step_rowshard_staged: the plain pooling kernel writes the partial
+                   bags locally and the copy engines carry each owner's block over NVLink (side
+                   stream, beside the next call's pooling); same flags and fold as "push"
 
 Table-wise (many tables): whole tables are assigned to ranks; each rank pools the full batch for
 its tables and the pooled outputs are exchanged so that rank g ends with [B/G, T, D].
@@ -92,6 +95,10 @@ SIGNATURES = {
     "fwd_eb_pipeline_step_rowshard": (C.c_int, [C.c_void_p, C.POINTER(capi.Params), C.POINTER(ShardExchange),
                                                 C.c_int64, C.POINTER(C.c_void_p), C.c_int32, C.c_void_p,
                                                 C.POINTER(C.c_int32)]),
+    "fwd_eb_pipeline_step_rowshard_staged": (C.c_int, [C.c_void_p, C.POINTER(capi.Params),
+                                                       C.POINTER(ShardExchange), C.c_int64,
+                                                       C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                                       C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]),
     "fwd_eb_pipeline_step_tablewise": (C.c_int, [C.c_void_p, C.POINTER(C.POINTER(capi.Params)),
                                                  C.POINTER(C.c_int32), C.c_int32,
                                                  C.POINTER(ShardExchange), C.c_int32, C.c_void_p,
@@ -219,7 +226,8 @@ class RowShardedBag:
         self.out = torch.empty((self.per, self.dim), dtype=self.out_dtype, device=dev)
         self.side = None
         self.ready = None
-        if exchange == "push":
+        self.piped = exchange in ("push", "stage")
+        if self.piped:
             # The fold runs on the pipeline's side stream so that the next call's pooling does
             # not queue behind this call's flag exchange; results rotate through three buffers.
             self.outs = [self.out, torch.empty_like(self.out), torch.empty_like(self.out)]
@@ -232,6 +240,13 @@ class RowShardedBag:
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
             self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status)
+            if exchange == "stage":
+                # "stage": the plain pooling kernel writes all partial bags here and the copy
+                # engines carry each owner's block over NVLink beside the next call's pooling
+                wire = torch.float16 if wire_dtype == capi.F16 else torch.float32
+                self.stages = [torch.empty((self.per * self.world, self.dim), dtype=wire, device=dev)
+                               for _ in range(3)]
+                self._stage_ptrs = (C.c_void_p * 3)(*[t.data_ptr() for t in self.stages])
         elif exchange in ("nccl", "a2a"):
             self.partial = torch.empty((self.per * self.world, self.dim), dtype=torch.float32,
                                        device=dev)
@@ -254,7 +269,7 @@ class RowShardedBag:
             raise ValueError("batch larger than max_bags")
         _, mine = owned_bags(self.per * self.world, self.world, self.rank)
         mine = max(0, min(mine, num_bags - self.rank * self.per))
-        out = self.out if self.exchange == "push" else self.partial
+        out = self.out if self.piped else self.partial
         return (self.params(indices, offsets, out), mine, num_bags)
 
     def forward(self, indices, offsets=None, pool_events=None):
@@ -266,12 +281,17 @@ class RowShardedBag:
         p, mine, num_bags = indices if isinstance(indices, tuple) else self.prepare(indices, offsets)
         main = torch.cuda.current_stream()
         stream = main.cuda_stream
-        if self.exchange == "push":
+        if self.piped:
             if pool_events:
                 pool_events[0].record()
-            capi.check(_lib().fwd_eb_pipeline_step_rowshard(
-                self._pl, C.byref(p), C.byref(self.x), mine, self._out_ptrs,
-                capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))
+            if self.exchange == "stage":
+                capi.check(_lib().fwd_eb_pipeline_step_rowshard_staged(
+                    self._pl, C.byref(p), C.byref(self.x), mine, self._stage_ptrs, self._out_ptrs,
+                    capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))
+            else:
+                capi.check(_lib().fwd_eb_pipeline_step_rowshard(
+                    self._pl, C.byref(p), C.byref(self.x), mine, self._out_ptrs,
+                    capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))
             if pool_events:
                 pool_events[1].record()   # after the push launch (the fold went to the side stream)
             self.ready = True
@@ -296,18 +316,18 @@ class RowShardedBag:
         """Make the current stream wait until the result of the last forward() is complete.
         (With exchange="push" the fold runs on `self.side`; work queued on that stream needs no
         call.)  Consume a result before the next forward()."""
-        if self.exchange == "push" and self.ready:
+        if self.piped and self.ready:
             capi.check(_lib().fwd_eb_pipeline_sync_result(self._pl, C.c_void_p(capi.current_stream_ptr())))
 
     def check_status(self) -> int:
         """Non-zero when a bounded wait gave up (reads one device word; synchronises)."""
-        if self.exchange != "push":
+        if not self.piped:
             return 0
         capi.check(_lib().fwd_eb_pipeline_drain(self._pl))
         return int(self.status.item())
 
     def close(self):
-        if self.exchange == "push":
+        if self.piped:
             _lib().fwd_eb_pipeline_destroy(self._pl)
             self._pl = C.c_void_p()
             self.buffers.close()

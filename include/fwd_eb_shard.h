@@ -125,6 +125,18 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
                                   void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
                                   void* main_stream, int32_t* which);
 
+/* Row shards, exchange by the copy engines instead of by the pooling kernel's own stores: the
+ * plain pooling kernel writes every bag's partial into d_stage[epoch % 3] (three local buffers of
+ * [world * bags_per_rank, dim] in the wire dtype) on `main_stream`; the side stream then sends
+ * each owner its block with one cudaMemcpyAsync over NVLink, raises the flags, waits (bounded)
+ * and folds as above.  All of the exchange runs beside the next step's pooling and takes no SM
+ * time from it; a result is complete one pooling step later than with the fused push. */
+int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_params* p,
+                                         fwd_eb_shard_exchange* x, int64_t num_bags_owned,
+                                         void* const d_stage[FWD_EB_SHARD_BUFFERS],
+                                         void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
+                                         void* main_stream, int32_t* which);
+
 /* Table-wise: push the `count` local tables (x->table_index is set from table_index[i]),
  * then the flag exchange on the side stream; *d_result receives this step's buffer part. */
 int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,

@@ -30,7 +30,8 @@ def _worker(rank, world, port, tmp):
     lo, n = fd.shard_rows(rows, world, rank)
     local = torch.from_numpy(table[lo:lo + n]).to(dev)
     shards = [fd.shard_rows(rows, world, r) for r in range(world)]
-    for exchange, wire in (("push", capi.F32), ("push", capi.F16), ("a2a", capi.F32), ("nccl", capi.F32)):
+    for exchange, wire in (("push", capi.F32), ("push", capi.F16), ("stage", capi.F32),
+                           ("stage", capi.F16), ("a2a", capi.F32), ("nccl", capi.F32)):
         for mode in (capi.MODE_SUM, capi.MODE_MEAN):
             bag = fd.RowShardedBag(local, lo, mode=mode, max_bags=nb, exchange=exchange,
                                    wire_dtype=wire, padding_idx=3)
