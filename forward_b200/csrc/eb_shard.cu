@@ -482,6 +482,31 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
   return 0;
 }
 
+int fwd_eb_shard_send_staged(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                             const void* d_stage, void* stream) {
+  int rc = check_exchange(x);
+  if (rc) return rc;
+  if (x->layout != FWD_EB_LAYOUT_ROW_SHARD)
+    return fail(FWD_EB_EINVAL, "the staged exchange is for the row-shard layout");
+  if (dim <= 0 || num_bags < 0 || num_bags > x->bags_per_rank * x->world || !d_stage)
+    return fail(FWD_EB_EINVAL, "bad send_staged arguments");
+  const size_t esize = x->wire_dtype == FWD_EB_F16 ? 2 : 4;
+  const size_t row_bytes = (size_t)dim * esize;
+  const size_t part = half_bytes(x, dim) * (size_t)(x->epoch % FWD_EB_SHARD_BUFFERS);
+  for (int i = 0; i < x->world; ++i) {
+    const int r = (x->rank + 1 + i) % x->world;  // peers first, own block last
+    long long rows = num_bags - (long long)r * x->bags_per_rank;
+    if (rows > x->bags_per_rank) rows = x->bags_per_rank;
+    if (rows <= 0) continue;
+    const char* src = static_cast<const char*>(d_stage) + (size_t)r * x->bags_per_rank * row_bytes;
+    char* dst = static_cast<char*>(x->peer_slots[r]) + part + (size_t)x->rank * x->bags_per_rank * row_bytes;
+    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)rows * row_bytes, cudaMemcpyDefault,
+                                    static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(e, "copying a block of partial bags to its owner");
+  }
+  return 0;
+}
+
 int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_params* p,
                                          fwd_eb_shard_exchange* x, int64_t num_bags_owned,
                                          void* const d_stage[FWD_EB_SHARD_BUFFERS],
@@ -515,19 +540,8 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
   rc = pipeline_handover(pl, main);
   if (rc) return rc;
   // 2. one copy-engine transfer per owner: its block of partial bags -> slot [rank] over there
-  const size_t esize = x->wire_dtype == FWD_EB_F16 ? 2 : 4;
-  const size_t row_bytes = (size_t)p->dim * esize;
-  const size_t part = half_bytes(x, p->dim) * (size_t)k;
-  for (int i = 0; i < x->world; ++i) {
-    const int r = (x->rank + 1 + i) % x->world;  // peers first, own block last
-    long long rows = p->num_bags - (long long)r * x->bags_per_rank;
-    if (rows > x->bags_per_rank) rows = x->bags_per_rank;
-    if (rows <= 0) continue;
-    const char* src = static_cast<const char*>(d_stage[k]) + (size_t)r * x->bags_per_rank * row_bytes;
-    char* dst = static_cast<char*>(x->peer_slots[r]) + part + (size_t)x->rank * x->bags_per_rank * row_bytes;
-    cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)rows * row_bytes, cudaMemcpyDefault, pl->side);
-    if (e != cudaSuccess) return cuda_fail(e, "copying a block of partial bags to its owner");
-  }
+  rc = fwd_eb_shard_send_staged(x, p->dim, p->num_bags, d_stage[k], pl->side);
+  if (rc) return rc;
   // 3. flags (raised by the kernel that follows the copies on the stream), bounded wait, fold
   rc = fwd_eb_shard_combine(x, p->dim, num_bags_owned, d_out[k], out_dtype, pl->side);
   if (rc) return rc;

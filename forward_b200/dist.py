@@ -89,6 +89,8 @@ SIGNATURES = {
     "fwd_eb_shard_wait": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.POINTER(C.c_void_p),
                                     C.c_void_p]),
     "fwd_eb_shard_signal": (C.c_int, [C.POINTER(ShardExchange), C.c_void_p]),
+    "fwd_eb_shard_send_staged": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.c_int64, C.c_void_p,
+                                           C.c_void_p]),
     "fwd_eb_pipeline_create": (C.c_int, [C.POINTER(C.c_void_p)]),
     "fwd_eb_pipeline_destroy": (None, [C.c_void_p]),
     "fwd_eb_pipeline_side_stream": (C.c_void_p, [C.c_void_p]),

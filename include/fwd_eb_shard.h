@@ -91,6 +91,15 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
 int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
                          void* d_out, int32_t out_dtype, void* stream);
 
+/* ROW_SHARD, the copy-engine alternative to fwd_eb_shard_push: `d_stage` holds the partial
+ * bags of ALL `num_bags` bags, [num_bags, dim] in the wire dtype, as fwd_eb_forward with this
+ * rank's row window (and FWD_EB_FLAG_MEAN_SINGLE_ROUNDING for MEAN) wrote them; each owner's
+ * block of rows is sent to slot [part][rank] of that owner with one cudaMemcpyAsync on
+ * `stream` (peers first, this rank's own block last).  fwd_eb_shard_combine then follows on
+ * the same stream exactly as after a push. */
+int fwd_eb_shard_send_staged(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                             const void* d_stage, void* stream);
+
 /* TABLE_WISE: after the last fwd_eb_shard_push of this call on the same stream: raise
  * this rank's flag, wait (bounded) until every rank has raised `epoch`; on success
  * *d_result (if not NULL) receives the address of this call's buffer part, laid out

@@ -77,6 +77,46 @@ def test_row_shard_push_and_combine_four_ranks(wire, mode):
     np.testing.assert_allclose(expect, whole, rtol=1e-3, atol=2e-2 if wire == capi.F16 else 1e-4)
 
 
+@pytest.mark.parametrize("wire", [capi.F32, capi.F16])
+def test_row_shard_staged_send_equals_push(wire):
+    """The copy-engine exchange: plain pooling into a staging buffer, one copy per owner, then the
+    same flags and fold; bit-identical to the CPU fold of the ranks' partials."""
+    rng = np.random.default_rng(18)
+    world, rows, dim, nb = 4, 6000, 64, 1000
+    table = rng.standard_normal((rows, dim)).astype(np.float16)
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, wire)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    shards = [fd.shard_rows(rows, world, r) for r in range(world)]
+    tabs = [_cuda(table[lo:lo + n]) for lo, n in shards]
+    wdt = torch.float16 if wire == capi.F16 else torch.float32
+    for epoch, mode in ((1, capi.MODE_SUM), (2, capi.MODE_MEAN)):
+        bags = workloads.ragged_bags(rows, rng.integers(0, 60, nb), rng)
+        i, o = _cuda(bags.indices), _cuda(bags.offsets)
+        for r in range(world):
+            xs[r].epoch = epoch
+            stage = torch.empty((nb, dim), dtype=wdt, device=DEV)
+            p = capi.make_params(tabs[r], i, o, out=stage, mode=mode, row_lo=shards[r][0],
+                                 flags=capi.FLAG_MEAN_SINGLE_ROUNDING)
+            capi.forward(p)
+            capi.check(lib.fwd_eb_shard_send_staged(C.byref(xs[r]), dim, nb, stage.data_ptr(), stream))
+        for r in range(world):
+            capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
+        parts = np.stack([O.pool(table[lo:lo + n], bags.indices, bags.offsets, mode=mode, row_lo=lo,
+                                 out_dtype=np.float32) for lo, n in shards])
+        if wire == capi.F16:
+            parts = parts.astype(np.float16)
+        expect = O.combine_partials(parts, np.float32)
+        for r in range(world):
+            lo, mine = fd.owned_bags(nb, world, r)
+            out = torch.empty((per, dim), device=DEV)
+            capi.check(lib.fwd_eb_shard_combine(C.byref(xs[r]), dim, mine, out.data_ptr(), capi.F32,
+                                                stream))
+            torch.cuda.synchronize()
+            assert np.array_equal(out[:mine].cpu().numpy(), expect[lo:lo + mine])
+    assert all(int(k.item()) == 0 for k in keep)
+
+
 def test_table_wise_push_lands_in_result_layout():
     rng = np.random.default_rng(9)
     world, ntab, dim, nb, L = 2, 5, 32, 96, 4
