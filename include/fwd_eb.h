@@ -212,9 +212,11 @@ int fwd_eb_bag_f32(const int* d_input, const int* d_offsets, float* d_output, in
 
 /*
  * Fill rows [row_lo, row_lo+num_rows) of a logical table in place on the
- * device with the counter-based generator  value(seed,row,col) =
- * scale * N(0,1), Box-Muller over a 64-bit mix of (seed,row,col).  A host twin
- * (same bits) lives in the test oracle so a CPU check can regenerate only the
+ * device with the counter-based generator  value(seed,row,col) = scale * z,
+ * z = the centred sum of eight 16-bit uniforms drawn from a 64-bit mix of
+ * (seed,row,col), scaled to unit variance (an Irwin-Hall bell: integer
+ * arithmetic and one multiplication, so host and device give the same bits).
+ * A host twin lives in the test oracle so a CPU check can regenerate only the
  * rows a sampled bag touches.
  */
 int fwd_eb_fill_table(void* d_table, int32_t table_dtype, int64_t num_rows, int32_t dim,
