@@ -15,6 +15,8 @@ LIB_PATH = os.path.join(_HERE, "lib", "libfwd_eb.so")
 
 MODE_SUM, MODE_MEAN, MODE_MAX, MODE_SQUARE_SUM, MODE_GATHER = 0, 1, 2, 3, 999
 F32, F16 = 0, 1
+F32_POS = 2          # MODE_MAX only: {fp32 value, int32 position} per column
+NO_POS = 0x7FFFFFFF
 I32, I64 = 0, 1
 STRATEGY_AUTO, STRATEGY_GROUP, STRATEGY_CTA, STRATEGY_SPLIT = 0, 1, 2, 3
 FLAG_MEAN_RAW_LENGTH, FLAG_GATHER_KEEP_SKIPPED, FLAG_MEAN_SINGLE_ROUNDING = 1, 2, 4

@@ -89,8 +89,16 @@ static int validate(const fwd_eb_params* p) {
                 (long long)p->num_rows);
   if (p->table_dtype != FWD_EB_F32 && p->table_dtype != FWD_EB_F16)
     return fail(FWD_EB_EINVAL, "unknown table_dtype %d", p->table_dtype);
-  if (p->out_dtype != FWD_EB_F32 && p->out_dtype != FWD_EB_F16)
+  if (p->out_dtype == FWD_EB_F32_POS) {
+    if (p->mode != FWD_EB_MODE_MAX)
+      return fail(FWD_EB_EINVAL, "out_dtype FWD_EB_F32_POS is defined for MODE_MAX only");
+    if (p->strategy != FWD_EB_STRATEGY_AUTO && p->strategy != FWD_EB_STRATEGY_GROUP)
+      return fail(FWD_EB_EUNSUPPORTED, "max with positions runs with the GROUP strategy only");
+    if (reinterpret_cast<uintptr_t>(p->out) & 7u)
+      return fail(FWD_EB_EALIGN, "FWD_EB_F32_POS output must be 8-byte aligned");
+  } else if (p->out_dtype != FWD_EB_F32 && p->out_dtype != FWD_EB_F16) {
     return fail(FWD_EB_EINVAL, "unknown out_dtype %d", p->out_dtype);
+  }
   if (p->index_dtype != FWD_EB_I32 && p->index_dtype != FWD_EB_I64)
     return fail(FWD_EB_EINVAL, "unknown index_dtype %d", p->index_dtype);
   switch (p->mode) {
@@ -219,6 +227,10 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
     pl->strategy = FWD_EB_STRATEGY_GROUP;
     return 0;
   }
+  if (p->out_dtype == FWD_EB_F32_POS) {
+    pl->strategy = FWD_EB_STRATEGY_GROUP;
+    return 0;
+  }
   pl->strategy = pick_strategy(p);
   if (pl->strategy == FWD_EB_STRATEGY_SPLIT) {
     int splits = choose_splits(p);
@@ -335,6 +347,24 @@ static cudaError_t launch_shape(const Plan& pl, cudaStream_t st) {
 }
 
 template <typename TW>
+static cudaError_t launch_maxpos(const Plan& pl, cudaStream_t st) {
+  const PoolArgs& a = pl.a;
+  const long long threads = a.num_bags << a.lanes_log2;
+  const long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+  if (blocks == 0) return cudaSuccess;
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  const int lanes = 1 << a.lanes_log2;
+  dim3 grid((unsigned)blocks, (unsigned)((a.nchunks + lanes - 1) / lanes));
+  if (pl.vec) {
+    eb_pool_maxpos_kernel<TW, 16 / (int)sizeof(TW)><<<grid, kCtaThreads, 0, st>>>(a);
+  } else {
+    eb_pool_maxpos_kernel<TW, 1><<<grid, kCtaThreads, 0, st>>>(a);
+  }
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError();
+}
+
+template <typename TW>
 static cudaError_t launch_gather(const Plan& pl, bool keep, cudaStream_t st) {
   const PoolArgs& a = pl.a;
   const long long threads = a.num_indices << a.lanes_log2;
@@ -399,6 +429,8 @@ int fwd_eb_forward(const fwd_eb_params* p, void* stream) {
   if (p->mode == FWD_EB_MODE_GATHER) {
     const bool keep = (p->flags & FWD_EB_FLAG_GATHER_KEEP_SKIPPED) != 0;
     e = pl.table_f16 ? launch_gather<__half>(pl, keep, st) : launch_gather<float>(pl, keep, st);
+  } else if (p->out_dtype == FWD_EB_F32_POS) {
+    e = pl.table_f16 ? launch_maxpos<__half>(pl, st) : launch_maxpos<float>(pl, st);
   } else {
     e = pl.table_f16 ? launch_shape<__half>(pl, st) : launch_shape<float>(pl, st);
   }

@@ -568,6 +568,98 @@ eb_pool_group_kernel(const PoolArgs a) {
   store_row<VE, CPL, true>(a, a.out, bag, chunk0, s.v, live);
 }
 
+// ---- max with the winner's position (output type FWD_EB_F32_POS) ---------------
+// out[bag][col] = {value as fp32, position inside the bag of the index that supplied it}, 8
+// bytes per column; {0, kNoPos} where no row of the bag lies inside the table window.  This is
+// what a row shard sends to a bag's owner: the owner keeps the greater value and, among equal
+// ones (+0.0 / -0.0), the earlier position, which is torch's first-of-equals rule across shards.
+// NaN follows the sequential rule "the bag's first non-padding entry is taken as is, later
+// entries only when strictly greater": a NaN is taken only when its entry is that first one
+// (every shard scans every index, so each knows where the bag's first non-padding entry is).
+// One lane group per bag, the survivor mask of a block of `lanes` indices walked four rows at
+// a time; rows wider than the group are covered by further column tiles (blockIdx.y).
+constexpr int kNoPos = 0x7fffffff;
+
+template <typename TW, int VE>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_pool_maxpos_kernel(const PoolArgs a) {
+  using V = typename Chunk<TW, VE>::type;
+  const int lanes_log2 = a.lanes_log2;
+  const int lanes = 1 << lanes_log2;
+  const unsigned lane = threadIdx.x & 31u;
+  const int lig = lane & (lanes - 1);
+  const int gbase = lane & ~(lanes - 1);
+  const unsigned gmask = lanes == 32 ? kFull : ((1u << lanes) - 1u);
+  const long long bag = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> lanes_log2;
+  const bool live = bag < a.num_bags;
+  const int chunk = blockIdx.y * lanes + lig;
+  const bool chunk_ok = chunk < a.nchunks;
+  long long start = 0, end = 0;
+  if (live) bag_bounds(a, bag, start, end);
+
+  float acc[VE];
+  int pos[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    acc[e] = 0.0f;
+    pos[e] = kNoPos;
+  }
+  bool seen = false;  // a non-padding entry lies before the current block (same in a group)
+  const unsigned stride32 = (unsigned)a.row_bytes_stride;
+  for (long long base = start; __any_sync(kFull, base < end); base += lanes) {
+    const long long at = base + lig;
+    int row = -1;
+    bool counted = false;
+    if (at < end) {
+      const long long idx = load_index(a.indices, a.idx64, at);
+      if (a.padding_idx < 0 || idx != a.padding_idx) {
+        counted = true;
+        const long long r = idx - a.row_lo;
+        if (r >= 0 && r < a.num_rows) row = (int)r;
+      }
+    }
+    unsigned m = (__ballot_sync(kFull, row >= 0) >> gbase) & gmask;
+    const unsigned cm = (__ballot_sync(kFull, counted) >> gbase) & gmask;
+    while (__any_sync(kFull, m != 0u)) {
+      int r4[4], e4[4];
+      bool ok[4];
+      V val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        ok[u] = m != 0u;
+        e4[u] = ok[u] ? (__ffs(m) - 1) : 0;
+        m &= (m - 1u);
+        r4[u] = __shfl_sync(kFull, row, gbase + e4[u]);
+        if (ok[u] && chunk_ok)
+          val[u] = load_chunk<V>(a.table + (unsigned long long)(unsigned)r4[u] * stride32 +
+                                 (size_t)chunk * (VE * sizeof(TW)));
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (ok[u] && chunk_ok) {
+          float f[VE];
+          unpack(val[u], f);
+          // is this entry the bag's first non-padding one?
+          const bool first_entry = !seen && (cm & ((1u << e4[u]) - 1u)) == 0u;
+          const int p = (int)(base - start) + e4[u];
+#pragma unroll
+          for (int e = 0; e < VE; ++e) {
+            const bool take = pos[e] == kNoPos ? (f[e] == f[e] || first_entry) : f[e] > acc[e];
+            acc[e] = take ? f[e] : acc[e];
+            pos[e] = take ? p : pos[e];
+          }
+        }
+      }
+    }
+    seen = seen || cm != 0u;
+  }
+  if (live && chunk_ok) {
+    int2* dst = reinterpret_cast<int2*>(a.out) + bag * a.out_stride + (long long)chunk * VE;
+#pragma unroll
+    for (int e = 0; e < VE; ++e) dst[e] = make_int2(__float_as_int(acc[e]), pos[e]);
+  }
+}
+
 // ---- strategies 2 and 3: a CTA (or `splits` CTAs) per bag --------------------
 // Lane groups take consecutive slices of the bag (of the split's part of it),
 // stage their fp32 partials in shared memory and thread t folds column t over

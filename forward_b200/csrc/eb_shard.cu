@@ -89,6 +89,40 @@ eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
   store_row<VE, CPL, true>(a, base, x.row_base + local_bag, chunk0, s.v, live);
 }
 
+// Fold of a sharded MAX: slot r holds, per column of each bag, {value, position of the index
+// that supplied it} or {0, kNoPos} when rank r had no row of the bag.  The greater value wins;
+// among equal values (+0.0 / -0.0) the earlier position; a NaN partial exists only when the
+// NaN was the bag's first non-padding entry, and then it is the result (the sequential rule of
+// eb_pool_maxpos_kernel).  A bag without any row gives 0.
+template <typename TO>
+__global__ void __launch_bounds__(kCtaThreads)
+eb_shard_combine_max_kernel(const int2* slots, int world, long long slot_stride, long long count,
+                            TO* out, const int* status) {
+  if (*static_cast<const volatile int*>(status) != 0) return;
+  for (long long i = (long long)blockIdx.x * kCtaThreads + threadIdx.x; i < count;
+       i += (long long)gridDim.x * kCtaThreads) {
+    float best = 0.0f;
+    int best_pos = kNoPos;
+    for (int r = 0; r < world; ++r) {
+      const int2 pr = slots[r * slot_stride + i];
+      const float v = __int_as_float(pr.x);
+      const int pos = pr.y;
+      if (pos == kNoPos) continue;
+      bool take;
+      if (best_pos == kNoPos) take = true;
+      else if (best != best) take = false;          // a NaN that was the bag's first entry stays
+      else if (v != v) take = true;
+      else take = v > best || (v == best && pos < best_pos);
+      if (take) {
+        best = v;
+        best_pos = pos;
+      }
+    }
+    if (sizeof(TO) == 2) out[i] = (TO)__float2half_rn(best);
+    else out[i] = (TO)best;
+  }
+}
+
 __global__ void eb_shard_signal_kernel(const FlagSet f, int world, int rank, uint32_t epoch) {
   if (threadIdx.x == 0 && blockIdx.x == 0) raise_flags(f.peer_flags, world, rank, epoch);
 }
@@ -174,14 +208,20 @@ eb_shard_combine_kernel(const TP* slots, int world, long long slot_stride, long 
   }
 }
 
+static size_t wire_bytes(int wire_dtype) {
+  return wire_dtype == FWD_EB_F16 ? 2u : (wire_dtype == FWD_EB_F32_POS ? 8u : 4u);
+}
+
 static int check_exchange(const fwd_eb_shard_exchange* x) {
   if (!x) return fail(FWD_EB_EINVAL, "exchange description is null");
   if (x->world < 1 || x->world > FWD_EB_MAX_PEERS)
     return fail(FWD_EB_EINVAL, "world must be 1..%d (got %d)", FWD_EB_MAX_PEERS, x->world);
   if (x->rank < 0 || x->rank >= x->world) return fail(FWD_EB_EINVAL, "rank %d outside the world", x->rank);
   if (x->bags_per_rank <= 0) return fail(FWD_EB_EINVAL, "bags_per_rank must be positive");
-  if (x->wire_dtype != FWD_EB_F32 && x->wire_dtype != FWD_EB_F16)
+  if (x->wire_dtype != FWD_EB_F32 && x->wire_dtype != FWD_EB_F16 && x->wire_dtype != FWD_EB_F32_POS)
     return fail(FWD_EB_EINVAL, "unknown wire_dtype %d", x->wire_dtype);
+  if (x->wire_dtype == FWD_EB_F32_POS && x->layout != FWD_EB_LAYOUT_ROW_SHARD)
+    return fail(FWD_EB_EINVAL, "the value + position wire type is for row shards");
   if (x->epoch == 0) return fail(FWD_EB_EINVAL, "epoch starts at 1");
   if (!x->status) return fail(FWD_EB_EINVAL, "status word is null");
   for (int r = 0; r < x->world; ++r) {
@@ -198,7 +238,7 @@ static int check_exchange(const fwd_eb_shard_exchange* x) {
 
 static size_t half_bytes(const fwd_eb_shard_exchange* x, int dim) {
   const size_t blocks = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (size_t)x->num_tables : (size_t)x->world;
-  return blocks * (size_t)x->bags_per_rank * (size_t)dim * (x->wire_dtype == FWD_EB_F16 ? 2u : 4u);
+  return blocks * (size_t)x->bags_per_rank * (size_t)dim * wire_bytes(x->wire_dtype);
 }
 
 static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
@@ -274,7 +314,7 @@ extern "C" {
 size_t fwd_eb_shard_slots_bytes(int32_t world, int64_t bags_per_rank, int32_t dim,
                                 int32_t wire_dtype) {
   if (world < 1 || bags_per_rank < 1 || dim < 1) return 0;
-  return (size_t)FWD_EB_SHARD_BUFFERS * (size_t)world * (size_t)bags_per_rank * (size_t)dim * (wire_dtype == FWD_EB_F16 ? 2u : 4u);
+  return (size_t)FWD_EB_SHARD_BUFFERS * (size_t)world * (size_t)bags_per_rank * (size_t)dim * wire_bytes(wire_dtype);
 }
 
 int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream) {
@@ -282,7 +322,10 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
   if (rc) return rc;
   if (!p) return fail(FWD_EB_EINVAL, "params is null");
   if (p->mode != FWD_EB_MODE_SUM && p->mode != FWD_EB_MODE_MEAN)
-    return fail(FWD_EB_EUNSUPPORTED, "pushed pooling supports SUM and MEAN (got mode %d)", p->mode);
+    return fail(FWD_EB_EUNSUPPORTED, "pushed pooling supports SUM and MEAN (got mode %d); a sharded "
+                "MAX goes through the staged exchange", p->mode);
+  if (x->wire_dtype == FWD_EB_F32_POS)
+    return fail(FWD_EB_EINVAL, "the value + position wire type belongs to MAX (staged exchange)");
   if (p->num_bags > x->bags_per_rank * x->world)
     return fail(FWD_EB_EINVAL, "%lld bags do not fit %d ranks x %lld bags", (long long)p->num_bags,
                 x->world, (long long)x->bags_per_rank);
@@ -359,6 +402,28 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
   const FlagSet flags = flag_set(x);
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
   const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
+  if (x->wire_dtype == FWD_EB_F32_POS) {
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks < 1) blocks = 1;
+    eb_shard_wait_kernel<<<1, 32, 0, st>>>(flags, x->rank, x->world, x->epoch, x->status, spins);
+    count_launch();
+    if (out16) {
+      eb_shard_combine_max_kernel<__half><<<(unsigned)blocks, kCtaThreads, 0, st>>>(
+          reinterpret_cast<const int2*>(slots), x->world, slot_stride, count,
+          static_cast<__half*>(d_out), x->status);
+    } else {
+      eb_shard_combine_max_kernel<float><<<(unsigned)blocks, kCtaThreads, 0, st>>>(
+          reinterpret_cast<const int2*>(slots), x->world, slot_stride, count,
+          static_cast<float*>(d_out), x->status);
+    }
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "max fold kernel launch");
+    clear_error();
+    return 0;
+  }
   const int pk = wire16 ? 8 : 4;
   const bool vec = count % pk == 0 && slot_stride % pk == 0 &&
                    (reinterpret_cast<uintptr_t>(slots) & 15u) == 0 &&
@@ -490,8 +555,7 @@ int fwd_eb_shard_send_staged(const fwd_eb_shard_exchange* x, int32_t dim, int64_
     return fail(FWD_EB_EINVAL, "the staged exchange is for the row-shard layout");
   if (dim <= 0 || num_bags < 0 || num_bags > x->bags_per_rank * x->world || !d_stage)
     return fail(FWD_EB_EINVAL, "bad send_staged arguments");
-  const size_t esize = x->wire_dtype == FWD_EB_F16 ? 2 : 4;
-  const size_t row_bytes = (size_t)dim * esize;
+  const size_t row_bytes = (size_t)dim * wire_bytes(x->wire_dtype);
   const size_t part = half_bytes(x, dim) * (size_t)(x->epoch % FWD_EB_SHARD_BUFFERS);
   for (int i = 0; i < x->world; ++i) {
     const int r = (x->rank + 1 + i) % x->world;  // peers first, own block last
@@ -516,8 +580,11 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
   int rc = 0;
   if (x->layout != FWD_EB_LAYOUT_ROW_SHARD)
     return fail(FWD_EB_EINVAL, "the staged exchange is for the row-shard layout");
-  if (p->mode != FWD_EB_MODE_SUM && p->mode != FWD_EB_MODE_MEAN)
-    return fail(FWD_EB_EUNSUPPORTED, "sharded pooling supports SUM and MEAN (got mode %d)", p->mode);
+  const bool is_max = p->mode == FWD_EB_MODE_MAX;
+  if (p->mode != FWD_EB_MODE_SUM && p->mode != FWD_EB_MODE_MEAN && !is_max)
+    return fail(FWD_EB_EUNSUPPORTED, "sharded pooling supports SUM, MEAN and MAX (got mode %d)", p->mode);
+  if (is_max != (x->wire_dtype == FWD_EB_F32_POS))
+    return fail(FWD_EB_EINVAL, "MAX needs wire_dtype FWD_EB_F32_POS, and only MAX does");
   if (p->num_bags > x->bags_per_rank * x->world)
     return fail(FWD_EB_EINVAL, "%lld bags do not fit %d ranks x %lld bags", (long long)p->num_bags,
                 x->world, (long long)x->bags_per_rank);
@@ -532,7 +599,7 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
   fwd_eb_params q = *p;
   q.strategy = FWD_EB_STRATEGY_GROUP;
   q.out = d_stage[k];
-  q.out_dtype = x->wire_dtype;
+  q.out_dtype = x->wire_dtype;  // fp32 / fp16 partial sums, or {value, position} pairs for MAX
   q.out_stride = 0;
   q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean
   rc = fwd_eb_forward(&q, main);

@@ -213,8 +213,15 @@ class RowShardedBag:
                  out_dtype=None):
         import torch
         import torch.distributed as dist
-        if mode not in (capi.MODE_SUM, capi.MODE_MEAN):
-            raise ValueError("row-sharded pooling supports sum and mean")
+        if mode == capi.MODE_MAX:
+            # a shard's partial is {value, position}: only the staged exchange carries it
+            if exchange != "stage":
+                raise ValueError("row-sharded max needs exchange='stage'")
+            wire_dtype = capi.F32_POS
+        elif mode not in (capi.MODE_SUM, capi.MODE_MEAN):
+            raise ValueError("row-sharded pooling supports sum, mean and max")
+        elif wire_dtype == capi.F32_POS:
+            raise ValueError("the value + position wire type belongs to max")
         self.table, self.row_lo, self.mode, self.padding_idx = table_local, row_lo, mode, padding_idx
         self.group = group
         self.world = dist.get_world_size(group)
@@ -246,7 +253,8 @@ class RowShardedBag:
                 # "stage": the plain pooling kernel writes all partial bags here and the copy
                 # engines carry each owner's block over NVLink beside the next call's pooling
                 wire = torch.float16 if wire_dtype == capi.F16 else torch.float32
-                self.stages = [torch.empty((self.per * self.world, self.dim), dtype=wire, device=dev)
+                cols = self.dim * (2 if wire_dtype == capi.F32_POS else 1)   # pairs: 8 bytes a column
+                self.stages = [torch.empty((self.per * self.world, cols), dtype=wire, device=dev)
                                for _ in range(3)]
                 self._stage_ptrs = (C.c_void_p * 3)(*[t.data_ptr() for t in self.stages])
         elif exchange in ("nccl", "a2a"):

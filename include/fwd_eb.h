@@ -45,6 +45,12 @@ enum {
 };
 
 enum { FWD_EB_F32 = 0, FWD_EB_F16 = 1 };  /* table / output element type   */
+/* Output type for MODE_MAX only (and wire type of a sharded max): per column the pair
+ * {fp32 value, int32 position inside the bag of the index that supplied it}, 8 bytes;
+ * {0, FWD_EB_NO_POS} where no row of the bag lies inside the table window.  What a row shard
+ * must send for the owner to apply torch's first-of-equals rule across shards. */
+enum { FWD_EB_F32_POS = 2 };
+#define FWD_EB_NO_POS 0x7fffffff
 enum { FWD_EB_I32 = 0, FWD_EB_I64 = 1 };  /* indices / offsets element type */
 
 /* Pooling strategies (fwd_eb_params.strategy). AUTO picks by shape. */
@@ -116,7 +122,7 @@ typedef struct fwd_eb_params {
   int64_t padding_idx;      /* logical index to skip; < 0 = none */
 
   void* out;                /* device, [num_bags, dim] (GATHER: [num_indices, dim]) */
-  int32_t out_dtype;        /* FWD_EB_F32 / FWD_EB_F16 */
+  int32_t out_dtype;        /* FWD_EB_F32 / FWD_EB_F16 (MODE_MAX also FWD_EB_F32_POS) */
   int32_t strategy;         /* FWD_EB_STRATEGY_* */
   int64_t out_stride;       /* elements between output rows; 0 = dim */
 

@@ -61,7 +61,8 @@ typedef struct fwd_eb_shard_exchange {
   int32_t world;              /* G, 1..FWD_EB_MAX_PEERS */
   int32_t rank;
   int64_t bags_per_rank;      /* owner of bag b is b / bags_per_rank */
-  int32_t wire_dtype;         /* FWD_EB_F32, or FWD_EB_F16 to halve the NVLink bytes */
+  int32_t wire_dtype;         /* FWD_EB_F32, or FWD_EB_F16 to halve the NVLink bytes; a sharded
+                                 MAX uses FWD_EB_F32_POS ({value, position}, 8 bytes a column) */
   uint32_t epoch;             /* call number, starting at 1; epoch % 3 picks the buffer part */
   void* peer_slots[FWD_EB_MAX_PEERS];      /* rank r's receive buffer as mapped here */
   uint32_t* peer_flags[FWD_EB_MAX_PEERS];  /* rank r's G flag words as mapped here */
@@ -139,7 +140,11 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
  * [world * bags_per_rank, dim] in the wire dtype) on `main_stream`; the side stream then sends
  * each owner its block with one cudaMemcpyAsync over NVLink, raises the flags, waits (bounded)
  * and folds as above.  All of the exchange runs beside the next step's pooling and takes no SM
- * time from it; a result is complete one pooling step later than with the fused push. */
+ * time from it; a result is complete a copy later than with the fused push.
+ * This is also how MODE_MAX is sharded (x->wire_dtype = FWD_EB_F32_POS): each rank's partial is
+ * the {value, position} pair of fwd_eb_forward's FWD_EB_F32_POS output, and the fold keeps the
+ * greater value, the earlier position among equal values, and a NaN only where it was the
+ * bag's first entry — bit for bit what torch's max gives on the unsharded table. */
 int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_params* p,
                                          fwd_eb_shard_exchange* x, int64_t num_bags_owned,
                                          void* const d_stage[FWD_EB_SHARD_BUFFERS],

@@ -59,6 +59,23 @@ def _worker(rank, world, port, tmp):
                     failures.append(f"rowshard {exchange} wire{wire} mode{mode} step{step}")
             dist.barrier()
             bag.close()
+    # sharded max (staged exchange, {value, position} partials): the whole-table max, bit for bit
+    bag = fd.RowShardedBag(local, lo, mode=capi.MODE_MAX, max_bags=nb, exchange="stage", padding_idx=3,
+                           out_dtype=torch.float16)
+    for step in range(2):
+        brng = np.random.default_rng(200 + step)
+        bags = workloads.ragged_bags(rows, brng.integers(0, 40, nb), brng)
+        bags.indices[::11] = 3
+        got = bag.forward(torch.from_numpy(bags.indices).to(dev), torch.from_numpy(bags.offsets).to(dev))
+        bag.sync_result()
+        torch.cuda.synchronize()
+        expect = O.pool(table, bags.indices, bags.offsets, mode=O.MODE_MAX, padding_idx=3)
+        blo, mine = fd.owned_bags(nb, world, rank)
+        if not np.array_equal(got.cpu().numpy().view(np.uint16), expect[blo:blo + mine].view(np.uint16)) \
+                or bag.check_status() != 0:
+            failures.append(f"rowshard max step{step}")
+    dist.barrier()
+    bag.close()
     # table-wise: 5 tables over the ranks, fixed pooling factor, weights
     ntab, L, dim2, nb2 = 5, 8, 64, 1024
     owner = fd.place_tables([1] * ntab, world)

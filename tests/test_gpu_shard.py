@@ -117,6 +117,107 @@ def test_row_shard_staged_send_equals_push(wire):
     assert all(int(k.item()) == 0 for k in keep)
 
 
+def _maxpos_reference(table, indices, offsets, row_lo, num_rows, padding_idx):
+    """Sequential restatement of the {value, position} partial of one row window (numpy, small
+    cases): the bag's first non-padding entry is taken as is, later entries only when strictly
+    greater, a NaN only when its entry is that first one; entries outside the window are skipped."""
+    nb, dim = offsets.size, table.shape[1]
+    ends = np.append(offsets, indices.size)
+    val = np.zeros((nb, dim), dtype=np.float32)
+    pos = np.full((nb, dim), capi.NO_POS, dtype=np.int32)
+    for b in range(nb):
+        seen = False
+        for p, j in enumerate(range(ends[b], ends[b + 1])):
+            idx = int(indices[j])
+            if idx == padding_idx:
+                continue
+            first = not seen
+            seen = True
+            r = idx - row_lo
+            if r < 0 or r >= num_rows:
+                continue
+            x = table[r].astype(np.float32)
+            fresh = pos[b] == capi.NO_POS
+            with np.errstate(invalid="ignore"):
+                take = np.where(fresh, ~np.isnan(x) | first, x > val[b])
+            val[b] = np.where(take, x, val[b])
+            pos[b] = np.where(take, p, pos[b])
+    return val, pos
+
+
+def _tricky_table(rng, rows, dim, dtype):
+    """Few distinct values (many ties), signed zeros and some NaN rows."""
+    t = rng.integers(-2, 3, (rows, dim)).astype(dtype)
+    t[rng.random((rows, dim)) < 0.15] = -0.0
+    t[::17] = np.nan
+    return t
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_max_with_positions_matches_the_sequential_rule(dtype):
+    rng = np.random.default_rng(31)
+    rows, dim, nb = 300, 40, 257                      # dim 40: fp32 rows of 160 B, 10 chunks
+    table = _tricky_table(rng, rows, dim, dtype)
+    bags = workloads.ragged_bags(rows, rng.integers(0, 45, nb), rng)
+    bags.indices[::5] = 7
+    lo, n = 100, 120                                  # a row window in the middle
+    out = torch.empty((nb, dim, 2), dtype=torch.float32, device=DEV)
+    p = capi.make_params(_cuda(table[lo:lo + n]), _cuda(bags.indices), _cuda(bags.offsets),
+                         out=out.view(nb, 2 * dim)[:, :dim], mode=capi.MODE_MAX, padding_idx=7, row_lo=lo)
+    p.out, p.out_dtype, p.out_stride = out.data_ptr(), capi.F32_POS, 0
+    capi.forward(p)
+    torch.cuda.synchronize()
+    got = out.cpu().numpy()
+    val, pos = _maxpos_reference(table[lo:lo + n], bags.indices, bags.offsets, lo, n, 7)
+    assert np.array_equal(got[..., 1].view(np.int32), pos)
+    assert np.array_equal(got[..., 0].view(np.uint32), val.view(np.uint32))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_row_shard_max_equals_torch_on_the_whole_table(dtype):
+    """Sharded MAX (staged exchange, {value, position} partials) against torch CPU EmbeddingBag on
+    the unsharded table, bit for bit: ties, signed zeros, a NaN as first entry, padding, empty bags."""
+    import torch.nn.functional as F
+    rng = np.random.default_rng(32)
+    world, rows, dim, nb = 4, 400, 64, 600
+    table = _tricky_table(rng, rows, dim, dtype)
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, capi.F32_POS)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    shards = [fd.shard_rows(rows, world, r) for r in range(world)]
+    tabs = [_cuda(table[lo:lo + n]) for lo, n in shards]
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    for epoch in (1, 2):
+        bags = workloads.ragged_bags(rows, rng.integers(0, 30, nb), rng)
+        bags.indices[::9] = 3
+        i, o = _cuda(bags.indices), _cuda(bags.offsets)
+        for r in range(world):
+            xs[r].epoch = epoch
+            stage = torch.empty((nb, 2 * dim), dtype=torch.float32, device=DEV)
+            p = capi.make_params(tabs[r], i, o, out=stage[:, :dim], mode=capi.MODE_MAX, padding_idx=3,
+                                 row_lo=shards[r][0])
+            p.out, p.out_dtype, p.out_stride = stage.data_ptr(), capi.F32_POS, 0
+            capi.forward(p)
+            capi.check(lib.fwd_eb_shard_send_staged(C.byref(xs[r]), dim, nb, stage.data_ptr(), stream))
+        for r in range(world):
+            capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
+        expect = F.embedding_bag(torch.from_numpy(bags.indices.astype(np.int64)), torch.from_numpy(table),
+                                 torch.from_numpy(bags.offsets.astype(np.int64)), mode="max",
+                                 padding_idx=3).numpy()
+        bits = np.uint16 if dtype == np.float16 else np.uint32
+        for r in range(world):
+            lo, mine = fd.owned_bags(nb, world, r)
+            out = torch.empty((per, dim), dtype=tdt, device=DEV)
+            capi.check(lib.fwd_eb_shard_combine(C.byref(xs[r]), dim, mine, out.data_ptr(),
+                                                capi.F16 if dtype == np.float16 else capi.F32, stream))
+            torch.cuda.synchronize()
+            got = out[:mine].cpu().numpy()
+            same = got.view(bits) == expect[lo:lo + mine].view(bits)
+            both_nan = np.isnan(got) & np.isnan(expect[lo:lo + mine])   # NaN payloads may differ
+            assert (same | both_nan).all()
+    assert all(int(k.item()) == 0 for k in keep)
+
+
 def test_table_wise_push_lands_in_result_layout():
     rng = np.random.default_rng(9)
     world, ntab, dim, nb, L = 2, 5, 32, 96, 4
