@@ -1030,9 +1030,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto",
                     choices=["auto", "c2", "tablewise", "rowshard", "c5", "c3", "c4"])
-    ap.add_argument("--exchange", default="push", choices=["push", "stage", "a2a", "nccl"],
-                    help="N>1: how pooled rows / partial bags reach their owners (stage: row shards "
-                         "only, copy engines instead of the pooling kernel's own peer stores)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "stage", "a2a", "nccl"],
+                    help="N>1: how pooled rows / partial bags reach their owners.  push: the pooling "
+                         "kernel's own peer stores; stage (row shards only): plain pooling, then "
+                         "copy-engine transfers; a2a / nccl: NCCL collectives.  auto = stage for row "
+                         "shards (the faster one there), push for table-wise placement")
     ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
                     help="row shards with --exchange push: element type of the partials on NVLink")
     ap.add_argument("--no-e2e", action="store_true")
@@ -1044,6 +1046,10 @@ def main():
                     help="untimed launches before the counted warm-up, to bring clocks up")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.exchange == "auto":
+        args.exchange = "stage" if args.workload in ("rowshard", "c5") else "push"
+    if args.exchange == "stage" and args.workload not in ("rowshard", "c5"):
+        raise SystemExit("--exchange stage is for the row-sharded workloads (rowshard, c5)")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
