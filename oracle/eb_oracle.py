@@ -142,6 +142,60 @@ def combine_partials(parts: np.ndarray, out_dtype=np.float32) -> np.ndarray:
     return out
 
 
+NO_POS = 0x7FFFFFFF
+
+
+def max_with_positions(table: np.ndarray, indices: np.ndarray, offsets: np.ndarray, *, row_lo: int = 0,
+                       padding_idx: int = -1):
+    """A row shard's partial of a max: per bag and column {value (fp32), position inside the bag
+    of the index that supplied it}, NO_POS where no row of the bag lies in [row_lo, row_lo+rows).
+
+    The sequential rule torch CPU's max follows (a probe, not a reference file: the reference
+    plugin has no sharding and its max op code is wrong, embedding_bag_plugin.cu:51-63): the
+    bag's first non-padding entry is taken as is, a later entry only when strictly greater; so a
+    NaN counts only when its entry is that first one.  Entries outside the window are skipped but
+    still count as "seen".  Plain Python loops: small cases only."""
+    nb, dim = offsets.size, table.shape[1]
+    ends = np.append(offsets, indices.size)
+    val = np.zeros((nb, dim), dtype=np.float32)
+    pos = np.full((nb, dim), NO_POS, dtype=np.int32)
+    for b in range(nb):
+        seen = False
+        for p, j in enumerate(range(int(ends[b]), int(ends[b + 1]))):
+            idx = int(indices[j])
+            if idx == padding_idx:
+                continue
+            first = not seen
+            seen = True
+            r = idx - row_lo
+            if r < 0 or r >= table.shape[0]:
+                continue
+            x = table[r].astype(np.float32)
+            fresh = pos[b] == NO_POS
+            with np.errstate(invalid="ignore"):
+                take = np.where(fresh, ~np.isnan(x) | first, x > val[b])
+            val[b] = np.where(take, x, val[b])
+            pos[b] = np.where(take, p, pos[b])
+    return val, pos
+
+
+def fold_max_partials(values: np.ndarray, positions: np.ndarray) -> np.ndarray:
+    """values / positions: [shards, bags, dim] from max_with_positions -> the whole-table max
+    [bags, dim] fp32: the greater value, the earlier position among equal values, a NaN partial
+    (which exists only where the NaN was the bag's first entry) as is; 0 for a bag without rows."""
+    best = np.zeros(values.shape[1:], dtype=np.float32)
+    bpos = np.full(values.shape[1:], NO_POS, dtype=np.int32)
+    for v, p in zip(values, positions):
+        have = p != NO_POS
+        with np.errstate(invalid="ignore"):
+            later = np.where(np.isnan(best), False,
+                             np.where(np.isnan(v), True, (v > best) | ((v == best) & (p < bpos))))
+        take = have & np.where(bpos == NO_POS, True, later)
+        best = np.where(take, v, best)
+        bpos = np.where(take, p, bpos)
+    return best
+
+
 def torch_pool(table, indices, offsets=None, *, mode: int = MODE_SUM, fixed_len: int = 0,
                per_sample_weights=None, include_last_offset: bool = False,
                padding_idx: int = -1, num_threads: int | None = None):

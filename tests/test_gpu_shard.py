@@ -117,34 +117,6 @@ def test_row_shard_staged_send_equals_push(wire):
     assert all(int(k.item()) == 0 for k in keep)
 
 
-def _maxpos_reference(table, indices, offsets, row_lo, num_rows, padding_idx):
-    """Sequential restatement of the {value, position} partial of one row window (numpy, small
-    cases): the bag's first non-padding entry is taken as is, later entries only when strictly
-    greater, a NaN only when its entry is that first one; entries outside the window are skipped."""
-    nb, dim = offsets.size, table.shape[1]
-    ends = np.append(offsets, indices.size)
-    val = np.zeros((nb, dim), dtype=np.float32)
-    pos = np.full((nb, dim), capi.NO_POS, dtype=np.int32)
-    for b in range(nb):
-        seen = False
-        for p, j in enumerate(range(ends[b], ends[b + 1])):
-            idx = int(indices[j])
-            if idx == padding_idx:
-                continue
-            first = not seen
-            seen = True
-            r = idx - row_lo
-            if r < 0 or r >= num_rows:
-                continue
-            x = table[r].astype(np.float32)
-            fresh = pos[b] == capi.NO_POS
-            with np.errstate(invalid="ignore"):
-                take = np.where(fresh, ~np.isnan(x) | first, x > val[b])
-            val[b] = np.where(take, x, val[b])
-            pos[b] = np.where(take, p, pos[b])
-    return val, pos
-
-
 def _tricky_table(rng, rows, dim, dtype):
     """Few distinct values (many ties), signed zeros and some NaN rows."""
     t = rng.integers(-2, 3, (rows, dim)).astype(dtype)
@@ -168,7 +140,7 @@ def test_max_with_positions_matches_the_sequential_rule(dtype):
     capi.forward(p)
     torch.cuda.synchronize()
     got = out.cpu().numpy()
-    val, pos = _maxpos_reference(table[lo:lo + n], bags.indices, bags.offsets, lo, n, 7)
+    val, pos = O.max_with_positions(table[lo:lo + n], bags.indices, bags.offsets, row_lo=lo, padding_idx=7)
     assert np.array_equal(got[..., 1].view(np.int32), pos)
     assert np.array_equal(got[..., 0].view(np.uint32), val.view(np.uint32))
 

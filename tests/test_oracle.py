@@ -127,3 +127,33 @@ def test_table_generator_is_seeded_and_roughly_normal():
     assert np.array_equal(t, O.table_rows(rows, 64, seed=4, scale=0.05, dtype=np.float32))
     assert not np.array_equal(t, O.table_rows(rows, 64, seed=5, scale=0.05, dtype=np.float32))
     assert abs(t.mean()) < 1e-3 and abs(t.std() - 0.05) < 1e-3
+
+
+def test_sharded_max_rule_equals_torch_on_the_whole_table():
+    """Per-shard {value, position} partials folded by "greater value, earlier position among equals,
+    NaN only as the bag's first entry" reproduce torch CPU's max on the unsharded table bit for bit:
+    ties, signed zeros, NaN rows, padding, empty bags; 1 to 5 shards."""
+    import torch
+    import torch.nn.functional as F
+    rng = np.random.default_rng(32)
+    rows, dim, nb = 200, 8, 150
+    for dtype in (np.float32, np.float16):
+        table = rng.integers(-2, 3, (rows, dim)).astype(dtype)
+        table[rng.random((rows, dim)) < 0.15] = -0.0
+        table[::17] = np.nan
+        lengths = rng.integers(0, 25, nb)
+        offsets = np.zeros(nb, dtype=np.int32)
+        offsets[1:] = np.cumsum(lengths[:-1])
+        indices = rng.integers(0, rows, int(lengths.sum())).astype(np.int32)
+        indices[::9] = 3
+        expect = F.embedding_bag(torch.from_numpy(indices.astype(np.int64)), torch.from_numpy(table),
+                                 torch.from_numpy(offsets.astype(np.int64)), mode="max",
+                                 padding_idx=3).numpy().astype(np.float32)
+        assert np.isnan(expect).any() and (np.signbit(expect) & (expect == 0)).any()
+        for shards in (1, 2, 5):
+            cuts = np.linspace(0, rows, shards + 1).astype(int)
+            parts = [O.max_with_positions(table[a:b], indices, offsets, row_lo=int(a), padding_idx=3)
+                     for a, b in zip(cuts[:-1], cuts[1:])]
+            got = O.fold_max_partials(np.stack([v for v, _ in parts]), np.stack([p for _, p in parts]))
+            same = got.view(np.uint32) == expect.view(np.uint32)
+            assert (same | (np.isnan(got) & np.isnan(expect))).all(), (dtype, shards)
