@@ -142,7 +142,9 @@ def test_max_with_positions_matches_the_sequential_rule(dtype):
     got = out.cpu().numpy()
     val, pos = O.max_with_positions(table[lo:lo + n], bags.indices, bags.offsets, row_lo=lo, padding_idx=7)
     assert np.array_equal(got[..., 1].view(np.int32), pos)
-    assert np.array_equal(got[..., 0].view(np.uint32), val.view(np.uint32))
+    gv = np.ascontiguousarray(got[..., 0])
+    same = gv.view(np.uint32) == val.view(np.uint32)
+    assert (same | (np.isnan(gv) & np.isnan(val))).all()      # NaN payloads may differ
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
