@@ -195,8 +195,10 @@ def describe(workload: str, world: int, args):
                     bags_per_step=C2["bags"] * world, table_rows=C2["rows"] * world, dim=C2["dim"],
                     parallelism=f"rowshard{world}", exchange=args.exchange, wire=args.wire)
     elif workload == "c5":
+        window = f"; this GPU holds 1 of {args.c5_window} row windows and pools its partial bags only" \
+            if (world == 1 and getattr(args, "c5_window", 1) > 1) else ""
         base.update(workload="c5: EmbeddingBag sum, table 1000000000x64 fp16 (128 GB) split by rows, "
-                             "131072 bags/step of 1..100 uniform indices",
+                             "131072 bags/step of 1..100 uniform indices" + window,
                     bags_per_step=C5["bags"], table_rows=C5["rows"], dim=C5["dim"],
                     parallelism=f"rowshard{world}" if world > 1 else "single",
                     exchange=args.exchange if world > 1 else None, wire=args.wire)
@@ -375,6 +377,11 @@ class GpuWorkload:
             self.row_lo, rows = fd.shard_rows(C5["rows"], world, rank)
             self.batches = make_batches(workload, world)
             local_filter = (self.row_lo, self.row_lo + rows) if world > 1 else None
+            if world == 1 and args.c5_window > 1:
+                # one GPU doing the pooling of ONE rank of a G-way row split (no exchange): the
+                # per-rank kernel of the sharded runs, where ncu can look at it
+                self.row_lo, rows = fd.shard_rows(C5["rows"], args.c5_window, args.c5_window // 2)
+                local_filter = (self.row_lo, self.row_lo + rows)
         else:
             self.dim, rows, self.mode, self.pad = C3["dim"], C3["rows"], capi.MODE_MAX, 0
             self.batches = make_batches(workload, world)
@@ -393,6 +400,7 @@ class GpuWorkload:
                 keep &= (b.indices >= local_filter[0]) & (b.indices < local_filter[1])
             self.gathered.append(int(np.count_nonzero(keep)))
         self._last = None
+        self.local_filter = local_filter
         self._build_step()
 
     def _build_step(self):
@@ -402,8 +410,8 @@ class GpuWorkload:
         bags_n = self.batches[0].num_bags
         if self.world == 1:
             out = torch.empty((bags_n, self.dim), dtype=torch.float16, device=dev)
-            params = [capi.make_params(self.table, i, o, out=out, mode=self.mode, padding_idx=self.pad)
-                      for i, o in self.d_batches]
+            params = [capi.make_params(self.table, i, o, out=out, mode=self.mode, padding_idx=self.pad,
+                                       row_lo=self.row_lo) for i, o in self.d_batches]
             self._params = params
 
             def step(k, events=None):
@@ -456,7 +464,8 @@ class GpuWorkload:
             out = self._last if self._last is not None else self.torch.empty(
                 (self.batches[0].num_bags, self.dim), dtype=self.torch.float16, device=self.dev)
             self._params = [self.capi.make_params(self.table, i, o, out=out, mode=self.mode,
-                                                  padding_idx=self.pad) for i, o in d_batches]
+                                                  padding_idx=self.pad, row_lo=self.row_lo)
+                            for i, o in d_batches]
 
     def result(self):
         return self._last
@@ -901,6 +910,15 @@ def verify(wl, workload, world, rank):
     lens = np.array([ends[t + 1] - ends[t] for t in take])
     offs = np.zeros(take.size, dtype=np.int32)
     offs[1:] = np.cumsum(lens[:-1])
+    if world == 1 and getattr(wl, "local_filter", None):
+        # one GPU holding one row window: the expected result is that window's partial
+        flo, fhi = wl.local_filter
+        keep = (idx >= flo) & (idx < fhi)
+        bag_of = np.repeat(np.arange(take.size), lens)
+        lens = np.bincount(bag_of[keep], minlength=take.size)
+        idx = idx[keep]
+        offs = np.zeros(take.size, dtype=np.int32)
+        offs[1:] = np.cumsum(lens[:-1])
     uniq, inv = np.unique(idx, return_inverse=True)
     seed, scale = table_seed(workload, rank)
     compact = O.table_rows(uniq, wl.dim, seed=seed, scale=scale, dtype=np.float16)
@@ -936,7 +954,7 @@ def run_e2e(args, wl):
     bags_n = wl.batches[0].num_bags
     s = Session(table_dtype=capi.F16, dim=wl.dim, num_rows=wl.table.shape[0], mode=wl.mode,
                 max_indices=max_n, max_bags=bags_n, depth=depth, external_table=True,
-                padding_idx=wl.pad)
+                padding_idx=wl.pad, row_lo=wl.row_lo)
     s.adopt_table(wl.table.data_ptr())
     views = [s.slot(k) for k in range(depth)]
     sizes = []
@@ -1037,6 +1055,9 @@ def main():
                          "shards (the faster one there), push for table-wise placement")
     ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
                     help="row shards with --exchange push: element type of the partials on NVLink")
+    ap.add_argument("--c5-window", type=int, default=1,
+                    help="c5 at N=1: hold only one of this many row windows of the table and pool "
+                         "that rank's partial bags (the per-rank kernel of a sharded run; no exchange)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-depth", type=int, default=4, help="N=1 e2e: calls in flight (1..16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
