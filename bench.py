@@ -158,7 +158,7 @@ def make_batches(workload: str, world: int, table_id: int = 0):
     if workload == "rowshard":
         return c2_batches(C2["rows"] * world, C2["bags"] * world, seed=1)
     if workload == "c5":
-        return [workloads.config5_bags(seed=4 + b) for b in range(4)]
+        return [workloads.config5_bags(seed=4 + b, num_rows=C5["rows"]) for b in range(4)]
     if workload == "c3":
         return [workloads.config3_bags(seed=2 + b) for b in range(NUM_BATCHES)]
     raise ValueError(workload)
@@ -197,7 +197,8 @@ def describe(workload: str, world: int, args):
     elif workload == "c5":
         window = f"; this GPU holds 1 of {args.c5_window} row windows and pools its partial bags only" \
             if (world == 1 and getattr(args, "c5_window", 1) > 1) else ""
-        base.update(workload="c5: EmbeddingBag sum, table 1000000000x64 fp16 (128 GB) split by rows, "
+        base.update(workload=f"c5: EmbeddingBag sum, table {C5['rows']}x64 fp16 "
+                             f"({C5['rows'] * 128 / 1e9:.0f} GB) split by rows, "
                              "131072 bags/step of 1..100 uniform indices" + window,
                     bags_per_step=C5["bags"], table_rows=C5["rows"], dim=C5["dim"],
                     parallelism=f"rowshard{world}" if world > 1 else "single",
@@ -1055,6 +1056,8 @@ def main():
                          "shards (the faster one there), push for table-wise placement")
     ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
                     help="row shards with --exchange push: element type of the partials on NVLink")
+    ap.add_argument("--c5-rows", type=int, default=C5["rows"],
+                    help="c5: rows of the whole table (default 1e9; a smaller table for profiler captures)")
     ap.add_argument("--c5-window", type=int, default=1,
                     help="c5 at N=1: hold only one of this many row windows of the table and pool "
                          "that rank's partial bags (the per-rank kernel of a sharded run; no exchange)")
@@ -1067,6 +1070,7 @@ def main():
                     help="untimed launches before the counted warm-up, to bring clocks up")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    C5["rows"] = args.c5_rows
     if args.exchange == "auto":
         args.exchange = "stage" if args.workload in ("rowshard", "c5") else "push"
     if args.exchange == "stage" and args.workload not in ("rowshard", "c5"):
