@@ -46,7 +46,7 @@ def tf():
 def parse(tf, path, outputs):
     err = C.create_string_buffer(512)
     p = tf.fwd_eb_tf_parse(str(path).encode(), outputs.encode(), err, 512)
-    return p, err.value.decode()
+    return p, err.value.decode("utf-8", "replace")
 
 
 def descs(tf, p):
@@ -239,3 +239,31 @@ def test_parsed_patterns_match_the_oracle_at_size(tf, tmp_path, half):
     got = _run(tf, p, 0, idx, 64, (2048, 20, 64), torch.float32)
     tf.fwd_eb_tf_free(p)
     assert np.array_equal(got, w[idx].astype(np.float32))
+
+
+def test_damaged_graphs_are_refused_or_parsed_never_crash(tf, tmp_path):
+    """Truncations and byte flips of a valid GraphDef: the reader must come back with a handle or
+    an error text for every one of them (a wild read would take the test process down)."""
+    w = table(20, 4)
+    good = G.fm_graph(w, 3)
+    rng = np.random.default_rng(77)
+    path = tmp_path / "fuzz.pb"
+    seen_error = seen_ok = 0
+    cases = [good[:n] for n in range(0, len(good), 7)]
+    for _ in range(300):
+        b = bytearray(good)
+        for _ in range(int(rng.integers(1, 4))):
+            b[int(rng.integers(0, len(b)))] = int(rng.integers(0, 256))
+        cases.append(bytes(b))
+    for data in cases:
+        path.write_bytes(data)
+        p, err = parse(tf, path, "sub")
+        if p:
+            seen_ok += 1
+            for d in descs(tf, p):
+                assert d["weights"].size == d["count"] * d["dim"]
+            tf.fwd_eb_tf_free(p)
+        else:
+            seen_error += 1
+            assert err
+    assert seen_error > 0 and seen_ok > 0
