@@ -276,3 +276,35 @@ def test_long_bags_use_the_built_in_scratch_because_the_plugin_gets_no_workspace
     assert rc == 0 and np.array_equal(got, O.pool(table, idx, off, mode=O.MODE_MAX))
     assert capi.lib().fwd_eb_launch_count() - before == 2      # split pass + fold pass
     host.fwd_eb_host_free(h)
+
+
+def test_damaged_blobs_are_refused_or_loaded_never_crash(host):
+    """Random header fields, byte flips and truncations of a valid engine blob: deserializePlugin
+    must come back with a plugin or with nullptr (and a logged reason) for every one of them."""
+    rng = np.random.default_rng(5)
+    t = rng.standard_normal((6, 8)).astype(np.float32)
+    h = build(host, t, op=0, idx_dims=(10,), off_dims=(3,))
+    blob = blob_of(host, h)
+    cases = [blob[:n] for n in range(0, len(blob), 5)]
+    for _ in range(300):
+        b = bytearray(blob)
+        if rng.random() < 0.5:      # one of the five header fields replaced by an arbitrary value
+            field = int(rng.integers(0, 5))
+            if field < 4:
+                struct.pack_into("<i", b, 4 * field, int(rng.integers(-2**31, 2**31)))
+            else:
+                struct.pack_into("<Q", b, 16, int(rng.integers(0, 2**63)))
+        else:
+            for _ in range(int(rng.integers(1, 4))):
+                b[int(rng.integers(0, len(b)))] = int(rng.integers(0, 256))
+        cases.append(bytes(b))
+    loaded = refused = 0
+    for data in cases:
+        got = host.fwd_eb_host_load(data, len(data), h)
+        if got:
+            loaded += 1
+            host.fwd_eb_host_free(got)
+        else:
+            refused += 1
+    assert loaded > 0 and refused > 0
+    host.fwd_eb_host_free(h)
