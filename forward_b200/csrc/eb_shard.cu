@@ -19,7 +19,7 @@
 namespace fwd_eb {
 
 struct PushArgs {
-  char* peer_slots[FWD_EB_MAX_PEERS];  // already offset to this call's buffer half
+  char* peer_slots[FWD_EB_MAX_PEERS];  // already offset to this call's buffer part
   uint32_t* peer_flags[FWD_EB_MAX_PEERS];
   long long bags_per_rank;
   long long row_base;    // destination row of this rank's first bag inside the owner's buffer
@@ -236,16 +236,16 @@ static int check_exchange(const fwd_eb_shard_exchange* x) {
   return 0;
 }
 
-static size_t half_bytes(const fwd_eb_shard_exchange* x, int dim) {
+static size_t part_bytes(const fwd_eb_shard_exchange* x, int dim) {
   const size_t blocks = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (size_t)x->num_tables : (size_t)x->world;
   return blocks * (size_t)x->bags_per_rank * (size_t)dim * wire_bytes(x->wire_dtype);
 }
 
 static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
   memset(out, 0, sizeof(*out));
-  const size_t half = half_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
+  const size_t part = part_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
   for (int r = 0; r < x->world; ++r) {
-    out->peer_slots[r] = static_cast<char*>(x->peer_slots[r]) + half;
+    out->peer_slots[r] = static_cast<char*>(x->peer_slots[r]) + part;
     out->peer_flags[r] = x->peer_flags[r];
   }
   if (x->layout == FWD_EB_LAYOUT_TABLE_WISE) {
@@ -373,7 +373,7 @@ int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_resu
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "wait kernel launch");
   if (d_result)
-    *d_result = static_cast<char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
+    *d_result = static_cast<char*>(x->peer_slots[x->rank]) + part_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
   return 0;
 }
 
@@ -398,7 +398,7 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
     return fail(FWD_EB_EINVAL, "unknown out_dtype %d", out_dtype);
   const long long count = (long long)num_bags * dim;
   const long long slot_stride = (long long)x->bags_per_rank * dim;
-  const char* slots = static_cast<const char*>(x->peer_slots[x->rank]) + half_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
+  const char* slots = static_cast<const char*>(x->peer_slots[x->rank]) + part_bytes(x, dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
   const FlagSet flags = flag_set(x);
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
   const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
@@ -556,7 +556,7 @@ int fwd_eb_shard_send_staged(const fwd_eb_shard_exchange* x, int32_t dim, int64_
   if (dim <= 0 || num_bags < 0 || num_bags > x->bags_per_rank * x->world || !d_stage)
     return fail(FWD_EB_EINVAL, "bad send_staged arguments");
   const size_t row_bytes = (size_t)dim * wire_bytes(x->wire_dtype);
-  const size_t part = half_bytes(x, dim) * (size_t)(x->epoch % FWD_EB_SHARD_BUFFERS);
+  const size_t part = part_bytes(x, dim) * (size_t)(x->epoch % FWD_EB_SHARD_BUFFERS);
   for (int i = 0; i < x->world; ++i) {
     const int r = (x->rank + 1 + i) % x->world;  // peers first, own block last
     long long rows = num_bags - (long long)r * x->bags_per_rank;
