@@ -92,3 +92,41 @@ def test_two_gloo_ranks_exchange_and_fold(method, tmp_path):
         np.testing.assert_allclose(got, expect, rtol=1e-6, atol=1e-7)
     whole = O.pool(table, bags.indices, bags.offsets, mode=O.MODE_MEAN, out_dtype=np.float32)
     np.testing.assert_allclose(got, whole, rtol=1e-5, atol=1e-6)
+
+
+def _validation_worker(rank, world, port, tmp):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    from forward_b200 import capi
+    from forward_b200 import dist as fd2
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    table = torch.zeros((10, 8), dtype=torch.float16)
+    seen = []
+    for kw in (dict(mode=capi.MODE_MAX, exchange="push"),            # max travels staged only
+               dict(mode=capi.MODE_MAX, exchange="nccl"),
+               dict(mode=capi.MODE_SUM, exchange="stage", wire_dtype=capi.F32_POS),
+               dict(mode=capi.MODE_SQUARE_SUM, exchange="push")):
+        try:
+            fd2.RowShardedBag(table, 0, max_bags=16, **kw)
+            seen.append("accepted")
+        except ValueError as e:
+            seen.append(str(e))
+    with open(os.path.join(tmp, f"validation_{rank}.txt"), "w") as f:
+        f.write("\n".join(seen))
+    dist.destroy_process_group()
+
+
+def test_sharded_bag_refuses_combinations_it_cannot_honour(tmp_path):
+    """Argument checks of RowShardedBag run before anything touches a GPU (two gloo ranks)."""
+    import torch.multiprocessing as mp
+    world = 2
+    port = 29850 + (os.getpid() % 100)
+    mp.spawn(_validation_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        lines = (tmp_path / f"validation_{r}.txt").read_text().splitlines()
+        assert len(lines) == 4 and "accepted" not in lines
+        assert "exchange='stage'" in lines[0] and "exchange='stage'" in lines[1]
+        assert "belongs to max" in lines[2] and "sum, mean and max" in lines[3]
