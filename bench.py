@@ -301,6 +301,21 @@ class CpuWorkload:
         return done
 
 
+def host_info() -> dict:
+    """CPU model string and torch version, for the CPU-arm lines."""
+    import torch
+    model = ""
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("model name"):
+                    model = line.split(":", 1)[1].strip()
+                    break
+    except OSError:
+        pass
+    return {"cpu_model": model, "torch": torch.__version__}
+
+
 def cpu_baseline(workload: str, world: int, budget_s: float):
     cw = CpuWorkload(workload, world)
     for k in range(2):
@@ -314,7 +329,7 @@ def cpu_baseline(workload: str, world: int, budget_s: float):
         reps += 1
     return {"value": lookups / secs, "unit": "lookups/s", "cores": cw.cores, "kind": "port",
             "sample": f"torch CPU EmbeddingBag on whole {workload} steps{cw.note}: {reps} steps, "
-                      f"{secs:.1f} s"}
+                      f"{secs:.1f} s", **host_info()}
 
 
 def run_reference(args, world: int, rank: int):
@@ -341,7 +356,7 @@ def run_reference(args, world: int, rank: int):
         "config": describe(workload, world, args),
         "cpu_baseline": {"value": value, "unit": "lookups/s", "cores": cw.cores, "kind": "port",
                          "sample": f"torch CPU EmbeddingBag on whole {workload} steps{cw.note}, "
-                                   f"{args.steps} steps"},
+                                   f"{args.steps} steps", **host_info()},
         "e2e": {"value": value, "unit": "lookups/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
