@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this directory.
 
-Run where the Forward reference tree is mounted (default /root/reference):
+Run where the Forward reference tree is mounted (pass its root, or rely on the default):
 
     python tests/golden/make_golden.py [reference_root]
 
