@@ -1,5 +1,5 @@
 // Description-creator interface of Forward's TensorFlow parser
-// (source/fwd_tf/tf_cvt/tf_desc_creators/i_tf_layer_creator.h:36-68), same names.
+// (source/fwd_tf/tf_cvt/tf_desc_creators/i_tf_layer_creator.h:40-69), same names.
 #pragma once
 
 #include <memory>

@@ -1,6 +1,6 @@
 // Ordered list of description creators; the first whose Check() accepts an operation wins
 // (Forward: source/fwd_tf/tf_cvt/tf_desc_manager.{h,cpp}; the EmbeddingBag creator is registered
-// at tf_desc_manager.cpp:37, ahead of the plain Gather and Reduce creators, so a Sum or GatherV2
+// at tf_desc_manager.cpp:66, ahead of the plain Gather and Reduce creators, so a Sum or GatherV2
 // that fits the pattern never reaches those).
 #pragma once
 

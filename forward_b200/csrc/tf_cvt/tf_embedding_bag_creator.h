@@ -1,7 +1,7 @@
 // TensorFlow node patterns -> TrtEmbeddingBagDesc.
 //
 // Same role and the same three patterns as Forward's
-// source/fwd_tf/tf_cvt/tf_desc_creators/tf_embedding_bag_creator.h:43-139:
+// source/fwd_tf/tf_cvt/tf_desc_creators/tf_embedding_bag_creator.h:41-140:
 //
 //   Sum(Mul([Identity](GatherV2(table, indices, axis 0)), m))            -> op 0   (SUM)
 //   Sum(Square(Mul([Identity](GatherV2(table, indices, axis 0)), m)))    -> op 3   (SQUARE_SUM)
@@ -9,13 +9,13 @@
 //
 // i.e. the first- and second-order terms of a factorisation machine over a fixed number of
 // feature ids per sample (indices [batch, L]; the plugin's fixed-length form).  The table is the
-// constant feeding GatherV2, or the node "<scope>_weights" when the graph has one (:103-113).
+// constant feeding GatherV2, or the node "<scope>_weights" when the graph has one (:108-119).
 //
 // As in the reference, the second Mul operand `m` (a sequence mask or feature values) is NOT
 // applied: the conversion is exact only where `m` is one for every looked-up id, which is how
 // the reference's fixture builds it (a full-length sequence mask).  A warning is logged.
 // Stricter than the reference, to fail instead of converting wrongly: a Sum must reduce axis 1
-// without keep_dims (the reference does not look, :75-86), the table must be fp32 or fp16 and of
+// without keep_dims (the reference does not look, :80-92), the table must be fp32 or fp16 and of
 // rank 1 or 2, and every constant it needs must really be constant.
 #pragma once
 
@@ -58,7 +58,7 @@ class TLayerDescCreator<TrtEmbeddingBagDesc> : public ILayerDescCreator {
       return nullptr;
     }
 
-    // a weights node generated from a file takes precedence (reference :103-113)
+    // a weights node generated from a file takes precedence (reference :108-119)
     std::string scope = table.Name();
     scope = scope.substr(0, scope.find_last_of('/')) + "_weights";
     Tensor weights;

@@ -1,7 +1,7 @@
 // A frozen TensorFlow GraphDef, read straight from its protobuf wire format.
 //
 // Forward walks TensorFlow graphs through the TensorFlow C API (TF_Graph / TF_Operation,
-// wrapped by Operation / Output / Tensor / Graph in source/fwd_tf/tf_cvt/tf_cpp_api.h:67-260 and
+// wrapped by Operation / Output / Tensor / Graph in source/fwd_tf/tf_cvt/tf_cpp_api.h:67-203 and
 // tf_graph.h).  This repository converts one node pattern only and must not depend on
 // libtensorflow, so the same four wrappers are provided over a small reader of the GraphDef
 // message: GraphDef.node(1) -> NodeDef{name(1), op(2), input(3), device(4), attr(5)},
@@ -125,7 +125,7 @@ class Operation {
   const NodeDef* node_{nullptr};
 };
 
-// One output of a node (tf_cpp_api.h:171-215).
+// One output of a node (tf_cpp_api.h:171-203).
 class Output : public Operation {
  public:
   Output() = default;
