@@ -267,3 +267,23 @@ def test_damaged_graphs_are_refused_or_parsed_never_crash(tf, tmp_path):
             seen_error += 1
             assert err
     assert seen_error > 0 and seen_ok > 0
+
+
+@pytest.mark.skipif(not os.path.exists(REF_FIXTURE), reason="reference tree not mounted")
+def test_reference_recommender_graphs_yield_their_gather_descriptions(tf):
+    """The reference's larger fixtures (source/unit_test/test_tf_recommender.h:56-71 DeepFM.pb, output
+    "Softmax"; test_tf_nodes.h embedding.pb): the walk passes through the dense layers and finds the
+    one embedding lookup each holds, as a GATHER description over the graph's own table."""
+    root = os.path.dirname(REF_FIXTURE)
+    for name, output, node, feed, shape in (
+            ("DeepFM.pb", "Softmax", "DNN/GatherV2", "Placeholder_2", (1706, 40)),
+            ("embedding.pb", "embedding_4/embedding_lookup/Identity_1", "embedding_4/embedding_lookup",
+             "input1_1", (1000, 64))):
+        p, err = parse(tf, os.path.join(root, name), output)
+        assert p, err
+        d = descs(tf, p)
+        assert len(d) == 1
+        assert (d[0]["node"], d[0]["input"], d[0]["op"]) == (node, feed, 999)
+        assert (d[0]["count"], d[0]["dim"]) == shape and d[0]["weights"].shape == shape
+        assert np.isfinite(d[0]["weights"]).all() and d[0]["weights"].std() > 0
+        tf.fwd_eb_tf_free(p)
