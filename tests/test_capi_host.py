@@ -120,3 +120,29 @@ def test_session_symbols_and_no_gpu_failure():
             session.Session(table_dtype=capi.F16, dim=8, num_rows=4, mode=capi.MODE_SUM,
                             max_indices=4, max_bags=2)
         assert e.value.code == capi.ENOGPU
+
+
+def test_headers_are_plain_c_and_a_c_host_links(tmp_path):
+    """The boundary is a C ABI: a C99 translation unit including every public header compiles
+    with -pedantic -Werror, links against libfwd_eb.so and calls into it."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if not gcc:
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    libdir = os.path.join(root, "forward_b200", "lib")
+    src = tmp_path / "host.c"
+    src.write_text('#include "fwd_eb.h"\n#include "fwd_eb_session.h"\n#include "fwd_eb_shard.h"\n'
+                   "#include <stdio.h>\n"
+                   "int main(void) {\n"
+                   "  fwd_eb_params p;\n"
+                   '  printf("%d %d\\n", fwd_eb_version(), (int)(fwd_eb_params_size() == sizeof p));\n'
+                   "  return fwd_eb_forward(NULL, NULL) == FWD_EB_EINVAL ? 0 : 1;\n"
+                   "}\n")
+    exe = tmp_path / "host"
+    subprocess.check_call([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic",
+                           "-I", os.path.join(root, "include"), str(src), "-o", str(exe),
+                           "-L", libdir, "-lfwd_eb", "-Wl,-rpath," + libdir])
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.split() == ["1", "1"]
