@@ -1,0 +1,72 @@
+"""A model of the exchange pipeline's ordering rules (include/fwd_eb_shard.h, fwd_eb_pipeline_*),
+run under random schedules on the CPU: with three buffer parts no rank ever writes into a part of a
+peer's receive buffer that the peer has not folded yet, and no rank deadlocks; with two parts the
+same rules do let such a write happen (so the model can tell the difference).
+
+Rules modelled, per rank, for call e = 1, 2, ...:
+  main stream   P(e): pool and write this rank's rows into part e % parts of every peer
+                      — may start only after X(e-2) of the same rank has completed
+  side stream   X(e): raise flag e on every peer; wait until every rank's flag >= e has arrived here;
+                      fold part e % parts of the own buffer — starts after P(e) and after X(e-1)
+The schedule picks, at random, any operation whose predecessors have completed; operations of
+different ranks and streams interleave freely.
+"""
+import random
+
+import pytest
+
+
+def simulate(world: int, parts: int, steps: int, seed: int):
+    rng = random.Random(seed)
+    pooled = [0] * world          # last P completed per rank
+    folded = [0] * world          # last X completed per rank (fold done)
+    flags = [[0] * world for _ in range(world)]   # flags[owner][source]
+    # what each part of each owner's buffer currently holds, per source: the call number written
+    holds = [[[0] * world for _ in range(parts)] for _ in range(world)]
+    hazards = []
+    while min(folded) < steps:
+        ready = []
+        for r in range(world):
+            e = pooled[r] + 1
+            if e <= steps and folded[r] >= e - 2:
+                ready.append(("P", r, e))
+            e = folded[r] + 1
+            if e <= steps and pooled[r] >= e:
+                ready.append(("X", r, e))
+        if not ready:
+            return "deadlock", hazards
+        kind, r, e = rng.choice(ready)
+        if kind == "P":
+            for owner in range(world):
+                slot = holds[owner][e % parts]
+                # the part must have been folded by its owner before it is overwritten
+                if slot[r] != 0 and folded[owner] < slot[r]:
+                    hazards.append((r, owner, e, slot[r], folded[owner]))
+                slot[r] = e
+            pooled[r] = e
+        else:
+            for owner in range(world):
+                flags[owner][r] = max(flags[owner][r], e)
+            if all(f >= e for f in flags[r]):
+                # every source's rows of call e must be what the part holds now
+                if any(holds[r][e % parts][src] != e for src in range(world)):
+                    hazards.append(("stale", r, e, list(holds[r][e % parts])))
+                folded[r] = e
+            # else: the wait kernel keeps spinning; it is re-picked later (flags only grow)
+    return "done", hazards
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_three_parts_never_overwrite_an_unfolded_part(world):
+    for seed in range(200):
+        state, hazards = simulate(world, parts=3, steps=12, seed=seed)
+        assert state == "done" and not hazards, (seed, state, hazards[:3])
+
+
+def test_two_parts_are_not_enough_under_the_same_rules():
+    found = 0
+    for seed in range(200):
+        state, hazards = simulate(4, parts=2, steps=12, seed=seed)
+        assert state == "done"
+        found += bool(hazards)
+    assert found > 0
