@@ -8,6 +8,8 @@ Rules modelled, per rank, for call e = 1, 2, ...:
                       — may start only after X(e-2) of the same rank has completed
   side stream   X(e): raise flag e on every peer; wait until every rank's flag >= e has arrived here;
                       fold part e % parts of the own buffer — starts after P(e) and after X(e-1)
+A variant not built yet is modelled too: issuing the main stream's wait only on every k-th call (so
+that consecutive pooling grids are not separated by a wait) needs k + 2 parts.
 The schedule picks, at random, any operation whose predecessors have completed; operations of
 different ranks and streams interleave freely.
 """
@@ -16,7 +18,7 @@ import random
 import pytest
 
 
-def simulate(world: int, parts: int, steps: int, seed: int):
+def simulate(world: int, parts: int, steps: int, seed: int, wait_every: int = 1):
     rng = random.Random(seed)
     pooled = [0] * world          # last P completed per rank
     folded = [0] * world          # last X completed per rank (fold done)
@@ -28,7 +30,10 @@ def simulate(world: int, parts: int, steps: int, seed: int):
         ready = []
         for r in range(world):
             e = pooled[r] + 1
-            if e <= steps and folded[r] >= e - 2:
+            # the wait for X(e-2) is issued on every `wait_every`-th call only (1 = the pipeline as
+            # built); the main stream being in order, later calls inherit the last wait
+            waited_for = e - (e % wait_every) - 2
+            if e <= steps and folded[r] >= waited_for:
                 ready.append(("P", r, e))
             e = folded[r] + 1
             if e <= steps and pooled[r] >= e:
@@ -70,3 +75,13 @@ def test_two_parts_are_not_enough_under_the_same_rules():
         assert state == "done"
         found += bool(hazards)
     assert found > 0
+
+
+@pytest.mark.parametrize("wait_every,parts,safe", [(2, 3, False), (2, 4, True), (3, 4, False), (3, 5, True)])
+def test_waiting_on_every_kth_call_needs_k_plus_two_parts(wait_every, parts, safe):
+    hazardous = 0
+    for seed in range(200):
+        state, hazards = simulate(4, parts=parts, steps=24, seed=seed, wait_every=wait_every)
+        assert state == "done"
+        hazardous += bool(hazards)
+    assert (hazardous == 0) == safe
