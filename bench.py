@@ -50,11 +50,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 NUM_BATCHES = 8
-EVENT_STRIDE = 16   # every 16th step is also timed on its own
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the pooling kernel, from the ncu
-# captures summarised under profiles/ (None where no capture of that workload exists yet).
-NCU_DRAM_BYTES_PER_LAUNCH = {"c2": 35.9e6, "tablewise": None, "rowshard": None, "c5": None, "c3": 129.9e6,
-                             "c4": None}
+NCU_TRAFFIC_FILE = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
 C2 = dict(rows=1_000_000, dim=128, bags=16384)
 C5 = dict(rows=1_000_000_000, dim=64, bags=131072)
 C3 = dict(rows=4_000_000, dim=256, bags=8192)
@@ -120,6 +116,20 @@ class ClockSampler:
         }
 
 
+def ncu_traffic(workload: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's pooling kernel, as
+    the last committed ncu capture measured it (profiles/ncu_dram_traffic.json names the capture
+    and the source revision it was taken on); (None, None) where no capture of that workload exists."""
+    try:
+        with open(NCU_TRAFFIC_FILE) as f:
+            entry = json.load(f)["workloads"].get(workload)
+        if entry:
+            return float(entry["dram_bytes_per_launch"]), f"{entry['capture']} @ {entry['revision']}"
+    except Exception:
+        pass
+    return None, None
+
+
 def measured_peak():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -133,7 +143,7 @@ def measured_peak():
 def resolve_workload(name: str, world: int) -> str:
     if name == "auto":
         return "c2" if world == 1 else "tablewise"
-    if name in ("c2", "c3") and world != 1:
+    if name in ("c2", "c2u", "c3") and world != 1:
         raise SystemExit(f"workload {name} is a single-GPU workload")
     if name in ("tablewise", "rowshard") and world == 1:
         raise SystemExit(f"workload {name} needs more than one GPU (launch under torchrun)")
@@ -153,6 +163,10 @@ def make_batches(workload: str, world: int, table_id: int = 0):
     from forward_b200 import workloads
     if workload == "c2":
         return c2_batches(C2["rows"], C2["bags"], seed=1)
+    if workload == "c2u":     # c2's shape and bag lengths, uniform indices: no cache help
+        rng = np.random.default_rng(11)
+        return [workloads.ragged_bags(C2["rows"], np.clip(rng.poisson(40.0, C2["bags"]), 1, 200), rng)
+                for _ in range(NUM_BATCHES)]
     if workload == "tablewise":
         return c2_batches(C2["rows"], C2["bags"], seed=1 + 7919 * table_id)
     if workload == "rowshard":
@@ -166,7 +180,7 @@ def make_batches(workload: str, world: int, table_id: int = 0):
 
 def table_seed(workload: str, table_id: int) -> tuple[int, float]:
     """(seed, scale) of the counter-generated table."""
-    if workload in ("c2", "tablewise"):
+    if workload in ("c2", "c2u", "tablewise"):
         return 1 + table_id, 0.1
     if workload == "rowshard":
         return 1, 0.1
@@ -182,6 +196,10 @@ def describe(workload: str, world: int, args):
     if workload == "c2":
         base.update(workload="c2: EmbeddingBag mean, table 1000000x128 fp16, 16384 bags/step, lengths "
                              "Poisson(40) clipped [1,200], Zipf(1.05) indices",
+                    bags_per_step=C2["bags"], table_rows=C2["rows"], dim=C2["dim"], parallelism="single")
+    elif workload == "c2u":
+        base.update(workload="c2u: the c2 shape (table 1000000x128 fp16, 16384 bags/step, lengths Poisson(40) "
+                             "clipped [1,200], mean) with UNIFORM indices: the HBM-bound variant",
                     bags_per_step=C2["bags"], table_rows=C2["rows"], dim=C2["dim"], parallelism="single")
     elif workload == "tablewise":
         base.update(workload=f"tablewise: {world} tables of the c2 shape (1000000x128 fp16, mean), one "
@@ -255,8 +273,8 @@ class CpuWorkload:
         torch.set_num_threads(self.cores)
         self.note = ""
         self.mode, self.pad = "mean", None
-        if workload in ("c2", "tablewise"):
-            n_tab = 1 if workload == "c2" else world
+        if workload in ("c2", "c2u", "tablewise"):
+            n_tab = 1 if workload != "tablewise" else world
             self.tables = [torch.from_numpy(host_table(C2["rows"], C2["dim"], 0, *table_seed(workload, t)))
                            for t in range(n_tab)]
             self.batches = [make_batches(workload, world, t) for t in range(n_tab)]
@@ -387,7 +405,7 @@ class GpuWorkload:
         self.out_itemsize = 2
         self.row_lo = 0
         local_filter = None
-        if workload in ("c2", "tablewise"):
+        if workload in ("c2", "c2u", "tablewise"):
             self.dim, rows, self.mode, self.pad = C2["dim"], C2["rows"], capi.MODE_MEAN, -1
             self.batches = make_batches(workload, world, rank)
         elif workload == "rowshard":
@@ -458,9 +476,10 @@ class GpuWorkload:
                 self._last = self.bag.forward(self._prepared[k % self.nb], pool_events=events)
         else:
             wire = capi.F16 if args.wire == "f16" else capi.F32
+            max_n = max(b.num_indices for b in self.batches)
             self.bag = fd.RowShardedBag(self.table, self.row_lo, mode=self.mode, max_bags=bags_n,
-                                        exchange=args.exchange, wire_dtype=wire)
-            self.out_itemsize = 2 if (args.exchange in ("push", "stage") and args.wire == "f16") else 4
+                                        exchange=args.exchange, wire_dtype=wire, max_indices=max_n)
+            self.out_itemsize = 2 if (args.exchange in ("push", "stage", "compact") and args.wire == "f16") else 4
 
             self._prepared = [self.bag.prepare(i, o) for i, o in self.d_batches]
 
@@ -473,7 +492,23 @@ class GpuWorkload:
 
         lp = [capi.make_params(self.table, i, o, out=local_out, mode=self.mode, padding_idx=self.pad,
                                row_lo=self.row_lo) for i, o in self.d_batches]
-        self.pool_only = lambda k: capi.forward(lp[k % self.nb], stream.cuda_stream)
+        if self.workload != "tablewise" and args.exchange == "compact":
+            # the same two kernels as the step (window compaction, pooling of the dense sub-bags)
+            # with local stores and no flags or fold
+            max_n = max(b.num_indices for b in self.batches)
+            kept = torch.empty(max_n, dtype=torch.int32, device=dev)
+            bounds = torch.empty((bags_n, 2), dtype=torch.int32, device=dev)
+            wire_dt = torch.float16 if args.wire == "f16" else torch.float32
+            local_w = torch.empty((bags_n, self.dim), dtype=wire_dt, device=dev)
+            cp = capi.make_compacted_params(self.table, kept, bounds, out=local_w, mode=capi.MODE_SUM)
+            self._po_keep = (kept, bounds, local_w)
+
+            def pool_only(k):
+                capi.compact_window(lp[k % self.nb], kept, bounds, stream=stream.cuda_stream)
+                capi.forward(cp, stream.cuda_stream)
+            self.pool_only = pool_only
+        else:
+            self.pool_only = lambda k: capi.forward(lp[k % self.nb], stream.cuda_stream)
 
     def set_device_batches(self, d_batches):
         """Point the step at other device copies of the same batches (the e2e loop's)."""
@@ -720,23 +755,60 @@ def total_lookups(wl, steps: int, dev) -> float:
     return n
 
 
-def run_ours(args, world: int, rank: int, local_rank: int):
+REGIONS = 25            # timed regions of --steps steps each; `value` is the median region
+
+
+def timed_regions(wl, steps: int, regions: int, barrier, multi: bool):
+    """`regions` timed regions of exactly `steps` steps each.  Every region is bracketed by a
+    barrier + synchronize on both sides and the start event is recorded directly after the
+    barrier returns (nothing host-side in between, so ranks enter the region together).
+    Returns the per-region milliseconds of THIS rank."""
+    import torch
+    begin = [torch.cuda.Event(enable_timing=True) for _ in range(regions)]
+    end = [torch.cuda.Event(enable_timing=True) for _ in range(regions)]
+    step = wl.step
+    sync_result = wl.bag.sync_result if multi else None
+    for r in range(regions):
+        barrier()
+        begin[r].record()
+        for k in range(steps):
+            step(k)
+        if sync_result:
+            sync_result()    # the last step's fold / flag wait (side stream) is inside the region
+        end[r].record()
+    barrier()
+    return np.array([begin[r].elapsed_time(end[r]) for r in range(regions)])
+
+
+def isolated_launch_us(wl, samples: int = 40):
+    """One step at a time between its own pair of events, outside the timed regions: the pooling
+    launch(es) of a step alone.  A few microseconds above the back-to-back figure (the events'
+    own cost, and an event between two grids keeps the second from overlapping the first one's
+    drain)."""
+    import torch
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+          for _ in range(samples)]
+    for k in range(samples):
+        wl.step(k, events=ev[k])
+    if wl.bag is not None:
+        wl.bag.sync_result()
+    torch.cuda.synchronize()
+    return np.array([a.elapsed_time(b) for a, b in ev]) * 1e3
+
+
+def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, steps: int,
+            regions: int, want_e2e: bool, want_cpu: bool, want_ref_kernel: bool, preheat_ms: float):
+    """Build `workload` on this rank, time it, verify it, and return the pieces of a bench line
+    (every rank computes them; rank 0 prints)."""
     import torch
 
     from forward_b200 import capi
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the package has no CPU path")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    dist = None
     multi = world > 1
+    dist = None
     if multi:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    workload = resolve_workload(args.workload, world)
     wl = C4Workload(world, rank, dev, args) if workload == "c4" else \
         GpuWorkload(workload, world, rank, dev, args)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps)]
 
     def barrier():
         if multi:
@@ -745,12 +817,12 @@ def run_ours(args, world: int, rank: int, local_rank: int):
 
     # bring clocks up before the counted warm-up; a fixed count when ranks must stay in step
     if multi:
-        for k in range(200 if workload == "c4" else int(args.preheat_ms * 4)):
+        for k in range(100 if workload == "c4" else int(preheat_ms * 4)):
             wl.step(k)
             if k % 64 == 63:
                 torch.cuda.synchronize()
     else:
-        t_end = time.perf_counter() + args.preheat_ms * 1e-3
+        t_end = time.perf_counter() + preheat_ms * 1e-3
         k = 0
         while time.perf_counter() < t_end:
             wl.step(k)
@@ -763,7 +835,7 @@ def run_ours(args, world: int, rank: int, local_rank: int):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for k in range(20):
             wl.pool_only(k)
-        n_po = max(20, min(args.steps, 200))
+        n_po = max(20, min(steps, 200))
         a.record()
         for k in range(n_po):
             wl.pool_only(k)
@@ -772,99 +844,165 @@ def run_ours(args, world: int, rank: int, local_rank: int):
         pool_only_us = a.elapsed_time(b) * 1e3 / n_po
     for k in range(args.warmup):
         wl.step(k)
-    barrier()
-
-    # several ranks share the host's cores: poll less often so the launch loops are not starved
-    sampler = ClockSampler(local_rank, 0.0005 if not multi else 0.005)
     launches0 = capi.lib().fwd_eb_launch_count()
-    t_begin, t_finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
-    t_begin.record()
-    for k in range(args.steps):
-        # every EVENT_STRIDE-th step is bracketed by events of its own (an event between two
-        # launches keeps the second from overlapping the first one's drain, so few are taken)
-        wl.step(k, events=(ev[2 * k], ev[2 * k + 1]) if k % EVENT_STRIDE == 0 else None)
-    if multi:
-        wl.bag.sync_result()    # the last step's fold / flag wait (side stream) is inside the region
-    t_finish.record()
-    barrier()
-    clocks = sampler.stop()
-    launches = capi.lib().fwd_eb_launch_count() - launches0
-    total_ms = t_begin.elapsed_time(t_finish)
-    kernel_ms = np.array([ev[2 * k].elapsed_time(ev[2 * k + 1])
-                          for k in range(0, args.steps, EVENT_STRIDE)])
-    lookups = total_lookups(wl, args.steps, dev)
+    if sampler:
+        sampler.start()
+    region_ms = timed_regions(wl, steps, regions, barrier, multi)
+    clocks = sampler.stop() if sampler else None
+    launches = (capi.lib().fwd_eb_launch_count() - launches0) // regions
+    iso_us = isolated_launch_us(wl)
+    lookups = total_lookups(wl, steps, dev)
     exchange = None
     if multi:
         if wl.bag.check_status() != 0:
-            raise RuntimeError("a bounded flag wait gave up during the timed region")
-        tt = torch.tensor([total_ms, pool_only_us], dtype=torch.float64, device=dev)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        total_ms, pool_only_us = float(tt[0].item()), float(tt[1].item())
-        step_us = total_ms * 1e3 / args.steps
+            raise RuntimeError("a bounded flag wait gave up during the timed regions")
+        tt = torch.tensor(list(region_ms) + [pool_only_us], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)      # every region: the slowest rank's time
+        region_ms, pool_only_us = tt[:-1].cpu().numpy(), float(tt[-1].item())
+    total_ms = float(np.median(region_ms))
+    if multi:
+        step_us = total_ms * 1e3 / steps
         bags_n = wl.batches[0].num_bags
         egress = wl.egress_bytes() if hasattr(wl, "egress_bytes") else \
             bags_n * (world - 1) // world * wl.dim * wl.out_itemsize
-        exchange = {"method": args.exchange, "wire": "f16" if wl.out_itemsize == 2 else "f32",
+        extra_us = max(step_us - pool_only_us, 1e-3)
+        exchange = {"method": wl.exchange_name if hasattr(wl, "exchange_name") else args.exchange,
+                    "wire": "f16" if wl.out_itemsize == 2 else "f32",
                     "pool_only_us": pool_only_us, "step_us": step_us,
                     "overhead_frac": (step_us - pool_only_us) / pool_only_us,
                     "nvlink_egress_bytes_per_rank": int(egress),
-                    "nvlink_floor_us_at_770GBs": egress / 770e9 * 1e6}
+                    "nvlink_floor_us_at_770GBs": egress / 770e9 * 1e6,
+                    # egress over the part of a step the exchange adds, against 900 GB/s per direction
+                    "nvlink_frac": egress / (extra_us * 1e-6) / 900e9,
+                    "nvlink_frac_of_step": egress / (step_us * 1e-6) / 900e9}
     value = lookups / (total_ms * 1e-3)
 
     peak, peak_kind = measured_peak()
     if multi:
-        # the pooling kernel with its peer stores, bracketed by events (a step also waits for peers)
-        alg = float(np.mean([wl.algorithmic_bytes(k) for k in range(0, args.steps, EVENT_STRIDE)]))
-        launch_ms = float(kernel_ms.mean())
-        timed_by = "events around single steps"
+        # the pooling kernel(s) of a step with their peer stores, from the isolated launches
+        alg = float(np.mean([wl.algorithmic_bytes(k) for k in range(len(iso_us))]))
+        launch_ms = float(np.median(iso_us)) * 1e-3
+        timed_by = "events around single steps, median of %d (outside the timed regions)" % len(iso_us)
     else:
-        # the timed region holds nothing but the K pooling steps: average duration over the region
-        alg = float(np.mean([wl.algorithmic_bytes(k) for k in range(args.steps)]))
-        launch_ms = total_ms / args.steps
-        timed_by = "events around the whole timed region / steps"
+        # a timed region holds nothing but the K pooling steps: average duration over the region
+        alg = float(np.mean([wl.algorithmic_bytes(k) for k in range(steps)]))
+        launch_ms = total_ms / steps
+        timed_by = "events around the median timed region / steps"
     achieved = alg / (launch_ms * 1e-3) / 1e9
+    traffic, traffic_src = ncu_traffic(workload)
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(workload),
+                "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
                 "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
                 "kernel_us_mean": launch_ms * 1e3, "timed_by": timed_by,
-                "kernel_us_bracketed_mean": float(kernel_ms.mean() * 1e3),
-                "kernel_us_bracketed_median": float(np.median(kernel_ms) * 1e3),
+                "kernel_us_isolated_median": float(np.median(iso_us)),
+                "kernel_us_isolated_samples": int(len(iso_us)),
                 "algorithmic_bytes_per_launch": alg}
-
     if workload == "c4":
         roofline["launches_per_step"] = wl.launches_per_step
         roofline["note"] = "kernel_us_* and the bytes cover one step = all of this rank's tables"
         verified = None if args.no_verify else wl.verify()
-        e2e = None if args.no_e2e else wl.run_e2e(args)
+        e2e = wl.run_e2e(args) if want_e2e else None
     else:
         verified = None if args.no_verify else verify(wl, workload, world, rank)
         e2e = None
-        if not args.no_e2e:
+        if want_e2e:
             e2e = run_e2e_multi(args, wl, rank, world, dev) if multi else run_e2e(args, wl)
-    cpu = None
-    if rank == 0 and not multi and not args.no_cpu_baseline:
-        cpu = cpu_baseline(workload, world, args.cpu_seconds)
-    ref_kernel = reference_kernel_side_by_side(wl) if (workload == "c2" and not multi) else None
-
-    if rank == 0:
-        line = {
-            "metric": "pooled_lookups_per_sec", "value": value, "unit": "lookups/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-            "scaling": scaling_kind(workload), "vs_baseline": None,
-            "dtype": compute_dtype(workload), "table_dtype": "f32" if workload == "c4" else "f16",
-            "data": "synthetic", "config": describe(workload, world, args), "roofline": roofline,
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "verified_against_oracle": verified,
-        }
-        if exchange:
-            line["exchange"] = exchange
-        if ref_kernel:
-            line["reference_kernel"] = ref_kernel
-        print(json.dumps(line), flush=True)
+            if not multi and not args.no_plugin_e2e:
+                e2e["through_plugin_enqueue"] = run_e2e_plugin(args, wl)
+    cpu = cpu_baseline(workload, world, args.cpu_seconds) if (want_cpu and rank == 0) else None
+    ref_kernel = reference_kernel_side_by_side(wl) if want_ref_kernel else None
+    out = {"value": value, "ms_per_step": total_ms / steps, "steps": steps, "regions": int(regions),
+           "region_ms_min": float(region_ms.min()), "region_ms_median": total_ms,
+           "region_ms_max": float(region_ms.max()),
+           "roofline": roofline, "exchange": exchange, "verified": verified, "e2e": e2e,
+           "cpu_baseline": cpu, "reference_kernel": ref_kernel, "gpu_launches": int(launches),
+           "clocks": clocks, "config": describe(workload, world, args)}
     if multi:
         wl.bag.close()
+    del wl
+    torch.cuda.empty_cache()
+    return out
+
+
+def extra_object(m: dict) -> dict:
+    """The short form of a secondary workload attached to the main line."""
+    o = {"workload": m["config"]["workload"], "lookups_per_sec": m["value"],
+         "us_per_step": m["ms_per_step"] * 1e3, "steps": m["steps"], "regions": m["regions"],
+         "region_ms_min": m["region_ms_min"], "region_ms_max": m["region_ms_max"],
+         "verified": m["verified"], "gpu_launches": m["gpu_launches"],
+         "roofline": {k: m["roofline"][k] for k in ("achieved", "peak", "frac", "frac_of_8000", "traffic",
+                                                     "kernel_us_mean", "algorithmic_bytes_per_launch",
+                                                     "peak_kind")}}
+    if m["exchange"]:
+        x = m["exchange"]
+        o.update(step_us=x["step_us"], pool_only_us=x["pool_only_us"], overhead_frac=x["overhead_frac"],
+                 nvlink_egress_bytes_per_rank=x["nvlink_egress_bytes_per_rank"],
+                 nvlink_frac=x["nvlink_frac"], exchange=x["method"], wire=x["wire"])
+    return o
+
+
+def run_ours(args, world: int, rank: int, local_rank: int):
+    import torch
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the package has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    multi = world > 1
+    if multi:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    # NVML is initialised here, long before any timed region; several ranks share the host's
+    # cores, so they poll less often
+    sampler = ClockSampler(local_rank, 0.001 if not multi else 0.004)
+    workload = resolve_workload(args.workload, world)
+    primary_steps = min(args.steps, 40) if workload == "c4" else args.steps
+    main = measure(workload, args, world, rank, dev, sampler, steps=primary_steps, regions=args.regions,
+                   want_e2e=not args.no_e2e, want_cpu=not multi and not args.no_cpu_baseline,
+                   want_ref_kernel=(workload == "c2" and not multi), preheat_ms=args.preheat_ms)
+    extras = {}
+    if args.workload == "auto" and not args.no_extras:
+        # the other configurations the metric is quoted on, in the same run: at N = 1 the
+        # HBM-bound variants of the single-GPU path, at N > 1 the two multi-GPU configurations
+        plan = [("roofline_uniform", "c2u", {}), ("c3", "c3", {})] if not multi else \
+            [("c5", "c5", {"exchange": "compact", "wire": "f16"}), ("c4", "c4", {"exchange": "push"})]
+        for key, name, over in plan:
+            sub = argparse.Namespace(**vars(args))
+            for k2, v2 in over.items():
+                setattr(sub, k2, v2)
+            try:
+                m = measure(name, sub, world, rank, dev, None,
+                            steps=min(args.steps, 20) if name == "c4" else min(args.steps, 400),
+                            regions=7 if name == "c4" else min(args.regions, 15), want_e2e=False,
+                            want_cpu=False, want_ref_kernel=False, preheat_ms=100.0)
+                extras[key] = extra_object(m)
+            except Exception as exc:    # a secondary workload must never cost the headline line
+                extras[key] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+                torch.cuda.synchronize()
+    if rank == 0:
+        line = {
+            "metric": "pooled_lookups_per_sec", "value": main["value"], "unit": "lookups/s",
+            "n_gpus": world, "steps": main["steps"], "warmup": args.warmup,
+            "ms_per_step": main["ms_per_step"], "higher_is_better": True,
+            "scaling": scaling_kind(workload), "vs_baseline": None,
+            "dtype": compute_dtype(workload), "table_dtype": "f32" if workload == "c4" else "f16",
+            "data": "synthetic (table values: counter-based generator, Irwin-Hall bell of the "
+                    "configuration's sigma; lengths and indices: the configuration's laws)",
+            "config": main["config"], "regions": main["regions"],
+            "region_ms_min": main["region_ms_min"], "region_ms_median": main["region_ms_median"],
+            "region_ms_max": main["region_ms_max"],
+            "roofline": main["roofline"], "cpu_baseline": main["cpu_baseline"], "e2e": main["e2e"],
+            "gpu_launches": main["gpu_launches"], "clocks": main["clocks"],
+            "verified_against_oracle": main["verified"],
+        }
+        if main["exchange"]:
+            line["exchange"] = main["exchange"]
+        if main["reference_kernel"]:
+            line["reference_kernel"] = main["reference_kernel"]
+        line.update(extras)
+        print(json.dumps(line), flush=True)
+    if multi:
+        import torch.distributed as dist
         dist.destroy_process_group()
 
 
@@ -912,8 +1050,12 @@ def reference_kernel_side_by_side(wl):
 
 
 def verify(wl, workload, world, rank):
-    """One more step after the timed region, checked on every rank against the CPU oracle on a
-    sample of the bags that rank ends up with (all ranks must agree for `true`)."""
+    """One more step after the timed regions, checked on every rank against the CPU oracle on a
+    sample of the bags that rank ends up with (all ranks must agree for `true`).  The check is
+    bit for bit wherever the order of the additions is defined: single-GPU and table-wise results
+    (rows added in bag order), row shards (each window's partial in bag order, rounded to the wire
+    type, the partials added in rank order).  Only NCCL's reduce-scatter, whose order is the
+    library's, is compared within 1e-5."""
     import torch
 
     from oracle import eb_oracle as O
@@ -921,7 +1063,8 @@ def verify(wl, workload, world, rank):
     if wl.bag is not None:
         wl.bag.sync_result()
     torch.cuda.synchronize()
-    got = wl.result().float().cpu().numpy()
+    res = wl.result()
+    got = res.cpu().numpy()
     b = wl.batches[0]
     bags_n = b.num_bags
     per = -(-bags_n // world)
@@ -929,20 +1072,12 @@ def verify(wl, workload, world, rank):
     stride = max(1, per // 512)
     take = np.arange(lo, min(lo + per, bags_n))[::stride]
     ends = np.append(b.offsets, b.num_indices).astype(np.int64)
-    idx = np.concatenate([b.indices[ends[t]:ends[t + 1]] for t in take])
+    idx = np.concatenate([b.indices[ends[t]:ends[t + 1]] for t in take]).astype(np.int64)
     lens = np.array([ends[t + 1] - ends[t] for t in take])
     offs = np.zeros(take.size, dtype=np.int32)
     offs[1:] = np.cumsum(lens[:-1])
-    if world == 1 and getattr(wl, "local_filter", None):
-        # one GPU holding one row window: the expected result is that window's partial
-        flo, fhi = wl.local_filter
-        keep = (idx >= flo) & (idx < fhi)
-        bag_of = np.repeat(np.arange(take.size), lens)
-        lens = np.bincount(bag_of[keep], minlength=take.size)
-        idx = idx[keep]
-        offs = np.zeros(take.size, dtype=np.int32)
-        offs[1:] = np.cumsum(lens[:-1])
     uniq, inv = np.unique(idx, return_inverse=True)
+    inv = inv.astype(np.int32)
     seed, scale = table_seed(workload, rank)
     compact = O.table_rows(uniq, wl.dim, seed=seed, scale=scale, dtype=np.float16)
     pad = -1
@@ -951,18 +1086,138 @@ def verify(wl, workload, world, rank):
         pad = hit if hit < uniq.size and uniq[hit] == wl.pad else -1
     mode = {wl.capi.MODE_MEAN: O.MODE_MEAN, wl.capi.MODE_SUM: O.MODE_SUM,
             wl.capi.MODE_MAX: O.MODE_MAX}[wl.mode]
-    exp = O.pool(compact, inv.astype(np.int32), offs, mode=mode, padding_idx=pad, out_dtype=np.float32)
+
+    def window(flo, fhi, m):
+        """Partial of the logical row window [flo, fhi): `uniq` is sorted, so the window is a
+        slice of the compact table and the oracle's own row filter does the rest."""
+        a_, b_ = int(np.searchsorted(uniq, flo)), int(np.searchsorted(uniq, fhi))
+        return O.pool(compact[a_:b_], inv, offs, mode=m, padding_idx=pad, row_lo=a_, out_dtype=np.float32)
+
+    exact = True
     if workload == "tablewise":
         mine = got[take - lo, rank, :]        # column block of this rank's own table
+        exp = O.pool(compact, inv, offs, mode=mode, padding_idx=pad)
+    elif world == 1:
+        mine = got[take - lo]
+        if getattr(wl, "local_filter", None):   # one GPU holding one row window: that window's partial
+            exp = window(*wl.local_filter, mode).astype(np.float16)
+        else:
+            exp = O.pool(compact, inv, offs, mode=mode, padding_idx=pad)
     else:
         mine = got[take - lo]
-    ok = bool(np.allclose(mine, exp, rtol=2e-3, atol=2e-3))
+        ex = wl.args.exchange
+        sums_then_divide = ex == "compact" and mode == O.MODE_MEAN
+        total_rows = C5["rows"] if workload == "c5" else C2["rows"] * world
+        parts = []
+        for r in range(world):
+            if workload == "c5":
+                flo, n_r = wl.fd.shard_rows(total_rows, world, r)
+            else:
+                flo, n_r = r * C2["rows"], C2["rows"]
+            parts.append(window(flo, flo + n_r, O.MODE_SUM if sums_then_divide else mode))
+        parts = np.stack(parts)
+        if wl.out_itemsize == 2:
+            parts = parts.astype(np.float16)
+        exp = O.combine_partials(parts, np.float32)
+        if sums_then_divide:
+            exp = (exp / np.maximum(lens, 1)[:, None].astype(np.float32)).astype(np.float32)
+        exact = ex != "nccl"
+    if exact:
+        mine, exp = np.ascontiguousarray(mine), np.ascontiguousarray(exp)
+        if mine.dtype != exp.dtype:     # a variant that returns another type: compare values
+            ok = bool(np.allclose(mine.astype(np.float32), exp.astype(np.float32), rtol=1e-3, atol=1e-3))
+        else:
+            bits = np.uint16 if mine.dtype == np.float16 else np.uint32
+            ok = bool(np.array_equal(mine.view(bits), exp.view(bits)))
+    else:
+        ok = bool(np.allclose(mine, exp, rtol=1e-5, atol=1e-5))
     if world > 1:
         import torch.distributed as dist
         t = torch.tensor([1 if ok else 0], device=wl.dev)
         dist.all_reduce(t, op=dist.ReduceOp.MIN)
         ok = bool(t.item())
     return ok
+
+
+_HOST_TABLES = {}
+
+
+def run_e2e_plugin(args, wl):
+    """N = 1, the same steps through the EmbeddingBag_TRT plugin object instead of the session:
+    the plugin is built from a host copy of the table (description -> layer creator -> createPlugin
+    -> clone -> configurePlugin, as TensorRT would), and every step copies one batch's indices and
+    offsets from pinned host memory, calls the plugin's enqueue on a stream of its own and copies
+    the pooled rows back; four steps in flight.  The plugin's tensors have fixed shapes, so every
+    step reuses batch 0."""
+    import ctypes as C
+
+    import torch
+    capi = wl.capi
+    lib_path = os.path.join(ROOT, "forward_b200", "lib", "libfwd_eb_plugin.so")
+    if not os.path.exists(lib_path):
+        return {"unavailable": "libfwd_eb_plugin.so is not built"}
+    h = C.CDLL(lib_path)
+    h.fwd_eb_host_build.restype = C.c_void_p
+    h.fwd_eb_host_build.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                    C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                    C.c_void_p, C.c_int, C.c_void_p]
+    h.fwd_eb_host_free.argtypes = [C.c_void_p]
+    h.fwd_eb_host_run.argtypes = [C.c_void_p] * 6
+    b = wl.batches[0]
+    seed, scale = table_seed(wl.workload, 0)
+    key = (wl.workload, seed)
+    if key not in _HOST_TABLES:
+        _HOST_TABLES[key] = host_table(wl.table.shape[0], wl.dim, wl.row_lo, seed, scale)
+    table = _HOST_TABLES[key]
+    idx_dims = (C.c_int * 1)(b.num_indices)
+    off_dims = (C.c_int * 1)(b.num_bags)
+    plugin = h.fwd_eb_host_build(table.ctypes.data, 1, table.shape[0], table.shape[1], 0, int(wl.mode),
+                                 int(wl.pad), 0, 1, 1, idx_dims, 1, off_dims, 0, None)
+    if not plugin:
+        return {"unavailable": "the plugin refused the configuration"}
+    depth = 4
+    dev = wl.dev
+    h_in = [torch.cat([torch.from_numpy(b.offsets), torch.from_numpy(b.indices)]).pin_memory()
+            for _ in range(depth)]
+    d_in = [torch.empty_like(x, device=dev) for x in h_in]
+    d_out = [torch.empty((b.num_bags, wl.dim), dtype=torch.float16, device=dev) for _ in range(depth)]
+    h_out = [torch.empty((b.num_bags, wl.dim), dtype=torch.float16).pin_memory() for _ in range(depth)]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(depth)]
+    done = [torch.cuda.Event() for _ in range(depth)]
+    nb = b.num_bags
+
+    def step(k):
+        j = k % depth
+        done[j].synchronize()                    # result of the step issued `depth` steps ago
+        _ = float(h_out[j][0, 0])                # touch it
+        with torch.cuda.stream(streams[j]):
+            d_in[j].copy_(h_in[j], non_blocking=True)
+            rc = h.fwd_eb_host_run(plugin, d_in[j][nb:].data_ptr(), d_in[j][:nb].data_ptr(), None,
+                                   d_out[j].data_ptr(), streams[j].cuda_stream)
+            if rc != 0:
+                raise RuntimeError(f"plugin enqueue returned {rc}")
+            h_out[j].copy_(d_out[j], non_blocking=True)
+            done[j].record(streams[j])
+
+    torch.cuda.synchronize()
+    for k in range(max(args.warmup, depth)):
+        step(k)
+    torch.cuda.synchronize()
+    steps = args.steps
+    t0 = time.perf_counter()
+    for k in range(steps):
+        step(k)
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    # the plugin's result on batch 0 must be the C-ABI path's, bit for bit
+    wl.step(0)
+    torch.cuda.synchronize()
+    same = bool(torch.equal(wl.result().view(torch.int16), d_out[(steps - 1) % depth].view(torch.int16)))
+    h.fwd_eb_host_free(plugin)
+    return {"value": b.num_indices * steps / dt, "unit": "lookups/s", "ms_per_step": dt / steps * 1e3,
+            "h2d_bytes_per_step": int(h_in[0].numel() * 4), "d2h_bytes_per_step": int(h_out[0].numel() * 2),
+            "calls_in_flight": depth, "equals_c_abi_result": same,
+            "api": "EmbeddingBagPlugin::enqueue (TensorRT call order; interface stand-in)"}
 
 
 def run_e2e(args, wl):
@@ -1066,16 +1321,24 @@ def run_e2e_multi(args, wl, rank, world, dev):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto",
-                    choices=["auto", "c2", "tablewise", "rowshard", "c5", "c3", "c4"])
-    ap.add_argument("--exchange", default="auto", choices=["auto", "push", "stage", "a2a", "nccl"],
+                    choices=["auto", "c2", "c2u", "tablewise", "rowshard", "c5", "c3", "c4"])
+    ap.add_argument("--regions", type=int, default=REGIONS,
+                    help="timed regions of --steps steps each (barrier before each); `value` is the "
+                         "median region")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="--workload auto: skip the secondary workloads attached to the line "
+                         "(N=1: uniform-index c2 and c3; N>1: c5 and c4)")
+    ap.add_argument("--no-plugin-e2e", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "compact", "push", "stage", "a2a", "nccl"],
                     help="N>1: how pooled rows / partial bags reach their owners.  push: the pooling "
-                         "kernel's own peer stores; stage (row shards only): plain pooling, then "
-                         "copy-engine transfers; a2a / nccl: NCCL collectives.  auto = stage for row "
-                         "shards (the faster one there), push for table-wise placement")
+                         "kernel's own peer stores; compact (row shards only): window compaction first, "
+                         "then push from the dense sub-bags; stage (row shards only): plain pooling, then "
+                         "copy-engine transfers; a2a / nccl: NCCL collectives.  auto = compact for row "
+                         "shards (the fastest there), push for table-wise placement")
     ap.add_argument("--wire", default="f32", choices=["f32", "f16"],
                     help="row shards with --exchange push: element type of the partials on NVLink")
     ap.add_argument("--c5-rows", type=int, default=C5["rows"],
@@ -1094,9 +1357,9 @@ def main():
     args.warmup = max(args.warmup, 3)
     C5["rows"] = args.c5_rows
     if args.exchange == "auto":
-        args.exchange = "stage" if args.workload in ("rowshard", "c5") else "push"
-    if args.exchange == "stage" and args.workload not in ("rowshard", "c5"):
-        raise SystemExit("--exchange stage is for the row-sharded workloads (rowshard, c5)")
+        args.exchange = "compact" if args.workload in ("rowshard", "c5") else "push"
+    if args.exchange in ("stage", "compact") and args.workload not in ("rowshard", "c5"):
+        raise SystemExit(f"--exchange {args.exchange} is for the row-sharded workloads (rowshard, c5)")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -18,8 +18,9 @@ F32, F16 = 0, 1
 F32_POS = 2          # MODE_MAX only: {fp32 value, int32 position} per column
 NO_POS = 0x7FFFFFFF
 I32, I64 = 0, 1
-STRATEGY_AUTO, STRATEGY_GROUP, STRATEGY_CTA, STRATEGY_SPLIT = 0, 1, 2, 3
+STRATEGY_AUTO, STRATEGY_GROUP, STRATEGY_CTA, STRATEGY_SPLIT, STRATEGY_STREAM = 0, 1, 2, 3, 4
 FLAG_MEAN_RAW_LENGTH, FLAG_GATHER_KEEP_SKIPPED, FLAG_MEAN_SINGLE_ROUNDING = 1, 2, 4
+FLAG_OFFSET_PAIRS, FLAG_PAIRS_RUN32 = 8, 16
 EINVAL, EUNSUPPORTED, EALIGN, EWORKSPACE, ENOGPU, ETOOBIG = -1, -2, -3, -4, -5, -6
 
 
@@ -53,6 +54,8 @@ SIGNATURES = {
     "fwd_eb_forward": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "fwd_eb_workspace_size": (C.c_size_t, [C.POINTER(Params)]),
     "fwd_eb_pick_strategy": (C.c_int, [C.POINTER(Params)]),
+    "fwd_eb_compact_window": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_void_p]),
     "fwd_eb_launch_count": (C.c_uint64, []),
     "fwd_eb_gather_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                     C.c_int, C.c_int, C.c_void_p]),
@@ -202,6 +205,31 @@ def embedding_bag(table, indices, offsets=None, *, mode=MODE_SUM, fixed_len=0,
             p.workspace_bytes = need
     forward(p)
     return out
+
+
+def compact_window(params: Params, kept, bounds, *, kept_weights=None, counts=None,
+                   stream: int | None = None) -> None:
+    """fwd_eb_compact_window: keep the indices of `params` that fall inside its row window (and are
+    not padding) as dense sub-bags.  kept: int32 [num_indices]; bounds: int32 [num_bags, 2];
+    kept_weights: fp32 [num_indices] when params carries per_sample_weights; counts: optional
+    int32 [num_bags] (non-padding entries of each whole bag).  Pool the result with
+    make_compacted_params()."""
+    check(lib().fwd_eb_compact_window(
+        C.byref(params), C.c_void_p(kept.data_ptr()),
+        C.c_void_p(kept_weights.data_ptr()) if kept_weights is not None else None,
+        C.c_void_p(bounds.data_ptr()), C.c_void_p(counts.data_ptr()) if counts is not None else None,
+        C.c_void_p(stream if stream is not None else current_stream_ptr())))
+
+
+def make_compacted_params(table, kept, bounds, *, out, mode=MODE_SUM, kept_weights=None,
+                          strategy=STRATEGY_AUTO, flags=0) -> Params:
+    """Params that pool what compact_window wrote: local row numbers, {start, end} pairs."""
+    p = make_params(table, kept, None, out=out, mode=mode, per_sample_weights=kept_weights,
+                    fixed_len=1, strategy=strategy, flags=flags | FLAG_OFFSET_PAIRS | FLAG_PAIRS_RUN32)
+    p.fixed_len = 0
+    p.offsets = bounds.data_ptr()
+    p.num_bags = bounds.shape[0]
+    return p
 
 
 def fill_table(table, row_lo: int, seed: int, scale: float) -> None:

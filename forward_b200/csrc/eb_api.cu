@@ -11,8 +11,12 @@
 #include <cstdio>
 #include <cstring>
 
+#include <cstdlib>
+
+#include "eb_compact.cuh"
 #include "eb_internal.h"
 #include "eb_kernels.cuh"
+#include "eb_stream.cuh"
 #include "fwd_eb.h"
 
 namespace fwd_eb {
@@ -56,14 +60,25 @@ static int ceil_log2(int x) {
   return l;
 }
 
-static constexpr int kSmCount = 148;
+// Streaming multiprocessors of the current device, asked once per device ordinal (grid caps
+// and the split / run-length heuristics scale with it); 148 (B200) if the query fails.
+int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  cached[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
 
 // Split factor for the SPLIT strategy: enough CTAs for about four per SM, no
 // slice shorter than 256 indices, at most 64 splits.
 static int choose_splits(const fwd_eb_params* p) {
   if (p->num_bags <= 0) return 1;
   long long avg = p->fixed_len > 0 ? p->fixed_len : p->num_indices / p->num_bags;
-  long long want = (4LL * kSmCount + p->num_bags - 1) / p->num_bags;
+  long long want = (4LL * sm_count() + p->num_bags - 1) / p->num_bags;
   long long cap = avg / 256;
   if (want > cap) want = cap;
   if (want > 64) want = 64;
@@ -134,8 +149,13 @@ static int validate(const fwd_eb_params* p) {
   }
   if (p->per_sample_weights && p->mode != FWD_EB_MODE_SUM)
     return fail(FWD_EB_EINVAL, "per_sample_weights need mode SUM (torch rule)");
-  if (p->strategy < FWD_EB_STRATEGY_AUTO || p->strategy > FWD_EB_STRATEGY_SPLIT)
+  if (p->strategy < FWD_EB_STRATEGY_AUTO || p->strategy > FWD_EB_STRATEGY_STREAM)
     return fail(FWD_EB_EINVAL, "unknown strategy %d", p->strategy);
+  if (p->flags & FWD_EB_FLAG_OFFSET_PAIRS) {
+    if (p->fixed_len > 0) return fail(FWD_EB_EINVAL, "offset pairs and fixed_len exclude each other");
+    if (p->strategy == FWD_EB_STRATEGY_CTA || p->strategy == FWD_EB_STRATEGY_SPLIT)
+      return fail(FWD_EB_EUNSUPPORTED, "offset pairs run with the GROUP and STREAM strategies");
+  }
   return 0;
 }
 
@@ -146,12 +166,47 @@ static int pick_strategy(const fwd_eb_params* p) {
   // Many bags, or bags too short to share: a lane group each keeps enough rows in flight.
   if (avg < 64 || p->num_bags >= 8192) return FWD_EB_STRATEGY_GROUP;
   // Few long bags: split them when scratch is on offer and a CTA per bag would leave SMs idle.
-  if (p->num_bags < 2 * kSmCount && avg >= 1024) {
+  if (p->num_bags < 2 * sm_count() && avg >= 1024) {
     int splits = choose_splits(p);
     if (splits > 1 && p->workspace && p->workspace_bytes >= split_workspace_bytes(p, splits))
       return FWD_EB_STRATEGY_SPLIT;
   }
   return FWD_EB_STRATEGY_CTA;
+}
+
+// Shapes the streaming kernel covers (see eb_stream.cuh).
+static bool stream_ok(const fwd_eb_params* p, const Plan* pl) {
+  return pl->vec && pl->cpl == 1 && pl->tiles == 1 && pl->a.lanes_log2 >= 3 &&
+         p->index_dtype == FWD_EB_I32 && p->num_indices <= INT_MAX && p->num_bags <= INT_MAX &&
+         p->mode != FWD_EB_MODE_GATHER && p->out_dtype != FWD_EB_F32_POS;
+}
+
+// Consecutive bags per lane group: about a hundred rows per run, so the start-up chain
+// (bounds, first index block, first rows) is paid once per run instead of once per bag, but
+// never so many that the grid falls below two waves of resident groups.  With offset pairs a
+// run must stay inside one aligned block of 32 bags (a power of two), and only when the caller
+// vouches for their contiguity.
+static int choose_stream_k(const fwd_eb_params* p, int lanes_log2) {
+  if (p->num_bags <= 0) return 1;
+  const bool pairs = (p->flags & FWD_EB_FLAG_OFFSET_PAIRS) != 0;
+  if (pairs && !(p->flags & FWD_EB_FLAG_PAIRS_RUN32)) return 1;
+  long long avg = p->fixed_len > 0 ? p->fixed_len : p->num_indices / p->num_bags;
+  if (avg < 1) avg = 1;
+  long long k = 96 / avg;
+  if (k > kStreamMaxK) k = kStreamMaxK;
+  if (k < 1) k = 1;
+  const long long slots = (long long)sm_count() * ((FWD_EB_STREAM_MIN_CTAS * kCtaThreads) >> lanes_log2);
+  while (k > 1 && (p->num_bags + k - 1) / k < 2 * slots) --k;
+#ifdef FWD_EB_TUNE
+  if (const char* e = getenv("FWD_EB_STREAM_K")) k = atoi(e) > 0 ? atoi(e) : k;
+  if (k > kStreamMaxK) k = kStreamMaxK;
+#endif
+  if (pairs) {
+    long long p2 = 1;
+    while (p2 * 2 <= k) p2 *= 2;
+    k = p2;
+  }
+  return (int)k;
 }
 
 static int make_plan(const fwd_eb_params* p, Plan* pl) {
@@ -170,6 +225,11 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
   pl->ve = pl->vec ? 16 / tsize : 1;
   a.nchunks = pl->vec ? (int)(row_bytes / 16) : p->dim;
   a.lanes_log2 = ceil_log2(a.nchunks < 32 ? a.nchunks : 32);
+#ifdef FWD_EB_TUNE_HALFWARP
+  if (pl->vec && a.nchunks == 32 && p->mode != FWD_EB_MODE_GATHER &&
+      p->num_bags * 32 < (long long)sm_count() * 2048)
+    a.lanes_log2 = 4;
+#endif
   const int lanes = 1 << a.lanes_log2;
   const int per_lane = (a.nchunks + lanes - 1) / lanes;
   if (pl->vec) {
@@ -204,6 +264,8 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
   a.mean_raw_len = (p->flags & FWD_EB_FLAG_MEAN_RAW_LENGTH) != 0;
   a.mean_double_round = (p->flags & FWD_EB_FLAG_MEAN_SINGLE_ROUNDING) == 0;
   a.splits = 1;
+  a.pairs = (p->flags & FWD_EB_FLAG_OFFSET_PAIRS) != 0;
+  a.stream_k = 1;
   // 32-bit filter constants for int32 indices
   a.lo32 = (unsigned)p->row_lo;
   // (idx - row_lo) in wrap-around 32-bit arithmetic is exact whenever row_lo itself fits an int;
@@ -232,6 +294,25 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
     return 0;
   }
   pl->strategy = pick_strategy(p);
+  if (a.pairs && pl->strategy != FWD_EB_STRATEGY_STREAM) pl->strategy = FWD_EB_STRATEGY_GROUP;
+  // AUTO: where a lane group per bag is the plan, the streaming kernel takes the shapes it
+  // measured faster on: 512-byte and 128-byte rows (B200: 32.3 against 33.8 us on 8192 bags of
+  // 0..64 rows of 512 B; 63 against 78 us on 65536 x 20 weighted fp32 rows; 36 against 44 us
+  // on 131072 bags of ~6 rows of 128 B).  256-byte rows stay with the group kernel (22.8
+  // against 28.0 us on 16384 bags of ~40 rows).
+  if (p->strategy == FWD_EB_STRATEGY_AUTO && pl->strategy == FWD_EB_STRATEGY_GROUP &&
+      stream_ok(p, pl) && a.lanes_log2 != 4)
+    pl->strategy = FWD_EB_STRATEGY_STREAM;
+  if (pl->strategy == FWD_EB_STRATEGY_STREAM) {
+    if (!stream_ok(p, pl)) {
+      if (p->strategy == FWD_EB_STRATEGY_STREAM)
+        return fail(FWD_EB_EUNSUPPORTED, "STREAM needs 16-byte aligned rows of 128..512 bytes, int32 "
+                    "indices and fewer than 2^31 of them");
+      pl->strategy = FWD_EB_STRATEGY_GROUP;
+    } else {
+      a.stream_k = choose_stream_k(p, a.lanes_log2);
+    }
+  }
   if (pl->strategy == FWD_EB_STRATEGY_SPLIT) {
     int splits = choose_splits(p);
     if (splits <= 1) {
@@ -253,12 +334,20 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
   return 0;
 }
 
-int plan_group(const fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* tiles) {
+int plan_group(const fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* tiles, int* stream) {
   Plan pl;
   fwd_eb_params q = *p;
   q.strategy = FWD_EB_STRATEGY_GROUP;
   int rc = make_plan(&q, &pl);
   if (rc) return rc;
+  // the same choice AUTO makes between the two lane-group kernels
+  const bool want_stream = p->strategy == FWD_EB_STRATEGY_STREAM ||
+                           (p->strategy == FWD_EB_STRATEGY_AUTO && pl.a.lanes_log2 != 4);
+  *stream = 0;
+  if (want_stream && stream_ok(&q, &pl)) {
+    pl.a.stream_k = choose_stream_k(&q, pl.a.lanes_log2);
+    *stream = 1;
+  }
   *args = pl.a;
   *vec = pl.vec ? 1 : 0;
   *cpl = pl.cpl;
@@ -267,6 +356,58 @@ int plan_group(const fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* 
 }
 
 // ---- kernel dispatch ---------------------------------------------------------
+
+template <typename TW, int VE, int LL, int OP>
+static cudaError_t launch_stream_ll(const Plan& pl, cudaStream_t st) {
+  const PoolArgs& a = pl.a;
+  const long long groups = (a.num_bags + a.stream_k - 1) / a.stream_k;
+  const long long threads = groups << LL;
+  const long long blocks = (threads + kCtaThreads - 1) / kCtaThreads;
+  if (blocks == 0) return cudaSuccess;
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3((unsigned)kCtaThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PushArgs none;
+  memset(&none, 0, sizeof(none));
+  cudaError_t le = cudaLaunchKernelEx(
+      &cfg, eb_pool_stream_kernel<TW, VE, LL, OP, stream_u(LL), false>, a, none);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return le != cudaSuccess ? le : cudaGetLastError();
+}
+
+template <typename TW, int OP>
+static cudaError_t launch_stream_op(const Plan& pl, cudaStream_t st) {
+  constexpr int VE = 16 / (int)sizeof(TW);
+  switch (pl.a.lanes_log2) {
+    case 3:
+      return launch_stream_ll<TW, VE, 3, OP>(pl, st);
+    case 4:
+      return launch_stream_ll<TW, VE, 4, OP>(pl, st);
+    default:
+      return launch_stream_ll<TW, VE, 5, OP>(pl, st);
+  }
+}
+
+template <typename TW>
+static cudaError_t launch_stream(const Plan& pl, cudaStream_t st) {
+  switch (pl.op) {
+    case kOpSum:
+      return launch_stream_op<TW, kOpSum>(pl, st);
+    case kOpWeighted:
+      return launch_stream_op<TW, kOpWeighted>(pl, st);
+    case kOpMax:
+      return launch_stream_op<TW, kOpMax>(pl, st);
+    default:
+      return launch_stream_op<TW, kOpSquareSum>(pl, st);
+  }
+}
 
 template <typename TW, int VE, int CPL, int OP, int U, int IPL>
 static cudaError_t launch_pool(const Plan& pl, cudaStream_t st) {
@@ -335,6 +476,9 @@ static cudaError_t launch_shape(const Plan& pl, cudaStream_t st) {
   if (!pl.vec) return launch_op<TW, 1, 4, 4, 1>(pl, st);
   switch (pl.cpl) {
     case 1:
+#ifdef FWD_EB_TUNE
+      if (getenv("FWD_EB_IPL1")) return launch_op<TW, VE, 1, FWD_EB_U1, 1>(pl, st);
+#endif
       // rows of 256 B / 128 B: blocks of 32 indices (two / four index loads per lane)
       if (pl.a.lanes_log2 == 4) return launch_op<TW, VE, 1, FWD_EB_U1, 2>(pl, st);
       if (pl.a.lanes_log2 == 3) return launch_op<TW, VE, 1, FWD_EB_U1, 4>(pl, st);
@@ -395,27 +539,26 @@ const char* fwd_eb_last_error_string(void) { return g_err; }
 uint64_t fwd_eb_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int fwd_eb_pick_strategy(const fwd_eb_params* p) {
-  Plan pl;
-  fwd_eb_params q;
   if (!p) return fail(FWD_EB_EINVAL, "params is null");
-  q = *p;
+  fwd_eb_params q = *p;
   if (q.strategy == FWD_EB_STRATEGY_SPLIT) q.strategy = FWD_EB_STRATEGY_AUTO;
-  int rc = validate(&q);
+  Plan pl;
+  int rc = make_plan(&q, &pl);
   if (rc) return rc;
-  (void)pl;
-  if (q.mode == FWD_EB_MODE_GATHER) return FWD_EB_STRATEGY_GROUP;
-  return pick_strategy(&q);
+  return pl.strategy;
 }
 
 size_t fwd_eb_workspace_size(const fwd_eb_params* p) {
   if (!p || validate(p) != 0 || p->mode == FWD_EB_MODE_GATHER) return 0;
-  if (p->strategy == FWD_EB_STRATEGY_GROUP || p->strategy == FWD_EB_STRATEGY_CTA) return 0;
+  if (p->strategy == FWD_EB_STRATEGY_GROUP || p->strategy == FWD_EB_STRATEGY_CTA ||
+      p->strategy == FWD_EB_STRATEGY_STREAM)
+    return 0;
   // AUTO: what SPLIT would need if AUTO could choose it for this shape.
   if (p->strategy == FWD_EB_STRATEGY_AUTO) {
     if (p->num_bags <= 0) return 0;
     const long long avg = p->fixed_len > 0 ? p->fixed_len : p->num_indices / p->num_bags;
     if (avg < 64 || p->num_bags >= 8192) return 0;
-    if (!(p->num_bags < 2 * kSmCount && avg >= 1024)) return 0;
+    if (!(p->num_bags < 2 * sm_count() && avg >= 1024)) return 0;
   }
   return split_workspace_bytes(p, choose_splits(p));
 }
@@ -431,10 +574,73 @@ int fwd_eb_forward(const fwd_eb_params* p, void* stream) {
     e = pl.table_f16 ? launch_gather<__half>(pl, keep, st) : launch_gather<float>(pl, keep, st);
   } else if (p->out_dtype == FWD_EB_F32_POS) {
     e = pl.table_f16 ? launch_maxpos<__half>(pl, st) : launch_maxpos<float>(pl, st);
+  } else if (pl.strategy == FWD_EB_STRATEGY_STREAM) {
+    e = pl.table_f16 ? launch_stream<__half>(pl, st) : launch_stream<float>(pl, st);
   } else {
     e = pl.table_f16 ? launch_shape<__half>(pl, st) : launch_shape<float>(pl, st);
   }
   if (e != cudaSuccess) return cuda_fail(e, "kernel launch");
+  g_err[0] = '\0';
+  return 0;
+}
+
+int fwd_eb_compact_window(const fwd_eb_params* p, int32_t* d_kept, float* d_kept_weights,
+                          int32_t* d_bounds, int32_t* d_counts, void* stream) {
+  if (!p) return fail(FWD_EB_EINVAL, "params is null");
+  if (p->num_rows < 0 || p->num_indices < 0 || p->num_bags < 0) return fail(FWD_EB_EINVAL, "negative size");
+  if (p->num_rows > INT_MAX)
+    return fail(FWD_EB_ETOOBIG, "num_rows per device is limited to 2^31-1 (got %lld)", (long long)p->num_rows);
+  if (p->num_indices > INT_MAX)
+    return fail(FWD_EB_ETOOBIG, "window compaction takes fewer than 2^31 indices per call (got %lld)",
+                (long long)p->num_indices);
+  if (p->index_dtype != FWD_EB_I32 && p->index_dtype != FWD_EB_I64)
+    return fail(FWD_EB_EINVAL, "unknown index_dtype %d", p->index_dtype);
+  if (p->flags & FWD_EB_FLAG_OFFSET_PAIRS)
+    return fail(FWD_EB_EUNSUPPORTED, "window compaction reads plain offsets or fixed_len, not pairs");
+  if (p->fixed_len < 0) return fail(FWD_EB_EINVAL, "fixed_len is negative");
+  if (p->fixed_len > 0 && p->num_indices != p->num_bags * (int64_t)p->fixed_len)
+    return fail(FWD_EB_EINVAL, "num_indices (%lld) != num_bags (%lld) * fixed_len (%d)",
+                (long long)p->num_indices, (long long)p->num_bags, p->fixed_len);
+  if (p->num_bags == 0) return 0;
+  if (p->fixed_len == 0 && !p->offsets) return fail(FWD_EB_EINVAL, "offsets is null and fixed_len is 0");
+  if (p->num_indices > 0 && (!p->indices || !d_kept)) return fail(FWD_EB_EINVAL, "indices / d_kept is null");
+  if (!d_bounds) return fail(FWD_EB_EINVAL, "d_bounds is null");
+  if (reinterpret_cast<uintptr_t>(d_bounds) & 7u) return fail(FWD_EB_EALIGN, "d_bounds must be 8-byte aligned");
+  if (p->per_sample_weights && !d_kept_weights)
+    return fail(FWD_EB_EINVAL, "per_sample_weights given but d_kept_weights is null");
+  CompactArgs c;
+  memset(&c, 0, sizeof(c));
+  c.indices = p->indices;
+  c.offsets = p->offsets;
+  c.psw = p->per_sample_weights;
+  c.num_indices = p->num_indices;
+  c.num_bags = p->num_bags;
+  c.row_lo = p->row_lo;
+  c.num_rows = p->num_rows;
+  c.padding_idx = p->padding_idx;
+  c.fixed_len = p->fixed_len;
+  c.idx64 = p->index_dtype == FWD_EB_I64;
+  c.include_last = p->include_last_offset != 0;
+  c.kept = d_kept;
+  c.kept_w = d_kept_weights;
+  c.bounds = d_bounds;
+  c.counts = d_counts;
+  const long long warps = (p->num_bags + kCompactRun - 1) / kCompactRun;
+  const long long blocks = (warps * 32 + kCtaThreads - 1) / kCtaThreads;
+  if (blocks > INT_MAX) return fail(FWD_EB_ETOOBIG, "too many bags for one compaction launch");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3((unsigned)kCtaThreads);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];  // see launch_pool: overlaps its launch with the drain of a pooling grid ahead
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, eb_window_compact_kernel, c);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "compaction kernel launch");
   g_err[0] = '\0';
   return 0;
 }
@@ -501,7 +707,7 @@ int fwd_eb_fill_table(void* d_table, int32_t table_dtype, int64_t num_rows, int3
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const long long total = (long long)num_rows * dim;
   long long blocks = (total + kCtaThreads - 1) / kCtaThreads;
-  const long long cap = (long long)kSmCount * 32;
+  const long long cap = (long long)sm_count() * 32;
   if (blocks > cap) blocks = cap;
   if (table_dtype == FWD_EB_F16) {
     eb_fill_table_kernel<__half><<<(unsigned)blocks, kCtaThreads, 0, st>>>(
@@ -524,7 +730,7 @@ int fwd_eb_combine_partials(const void* d_parts, int32_t part_dtype, int32_t num
   if (count == 0) return 0;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
-  const long long cap = (long long)kSmCount * 16;
+  const long long cap = (long long)sm_count() * 16;
   if (blocks > cap) blocks = cap;
   const unsigned g = (unsigned)blocks;
   if (part_dtype == FWD_EB_F32 && out_dtype == FWD_EB_F32) {

@@ -14,22 +14,11 @@
 
 #include "eb_internal.h"
 #include "eb_kernels.cuh"
+#include "eb_stream.cuh"
 #include "fwd_eb_shard.h"
 
 namespace fwd_eb {
 
-struct PushArgs {
-  char* peer_slots[FWD_EB_MAX_PEERS];  // already offset to this call's buffer part
-  uint32_t* peer_flags[FWD_EB_MAX_PEERS];
-  long long bags_per_rank;
-  long long row_base;    // destination row of this rank's first bag inside the owner's buffer
-  long long col_offset;  // destination column of this call's first column
-  long long first_bag;   // bag the grid starts with; later bags follow, wrapping at num_bags
-  int world;
-  int rank;
-  int small;             // bag numbers and bags_per_rank fit 32 bits
-  uint32_t epoch;
-};
 
 __device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -149,7 +138,7 @@ __global__ void eb_shard_wait_kernel(const FlagSet f, int rank, int world, uint3
 template <typename TP, typename TO, bool VEC>
 __global__ void __launch_bounds__(kCtaThreads)
 eb_shard_combine_kernel(const TP* slots, int world, long long slot_stride, long long count, TO* out,
-                        const int* status) {
+                        const int* status, const int* counts, int dim) {
   // The flag exchange ran in eb_shard_wait_kernel just before this grid (one warp, so no
   // spinning CTA ever sits on an SM beside the next call's pooling); a wait that gave up has
   // left its mark in the status word and the output is then left alone.
@@ -183,6 +172,12 @@ eb_shard_combine_kernel(const TP* slots, int world, long long slot_stride, long 
       }
 #pragma unroll
       for (int e = 0; e < PK; ++e) acc[e] = __fadd_rn(acc[e], v[e]);
+    }
+    if (counts) {  // sharded mean whose partials are plain sums: divide by the bag's count
+      const int c = counts[(i * PK) / dim];  // a packet never straddles two bags (dim % PK == 0)
+      const float d = (float)(c < 1 ? 1 : c);
+#pragma unroll
+      for (int e = 0; e < PK; ++e) acc[e] = __fdiv_rn(acc[e], d);
     }
     TO* dst = out + i * PK;
     if (VEC && sizeof(TO) == 4) {
@@ -305,6 +300,41 @@ static cudaError_t launch_push_shape(const PoolArgs& a, const PushArgs& x, bool 
   return launch_push<TW, VE, 4, 2, 1>(a, x, tiles, weighted, st);
 }
 
+// The streaming kernel (eb_stream.cuh) with the push epilogue.
+template <typename TW, int LL>
+static cudaError_t launch_push_stream_ll(const PoolArgs& a, const PushArgs& x, bool weighted,
+                                         cudaStream_t st) {
+  constexpr int VE = 16 / (int)sizeof(TW);
+  const long long groups = (a.num_bags + a.stream_k - 1) / a.stream_k;
+  const long long blocks = ((groups << LL) + kCtaThreads - 1) / kCtaThreads;
+  if (blocks == 0) return cudaSuccess;
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3((unsigned)kCtaThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];  // see launch_pool in eb_api.cu
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = weighted
+      ? cudaLaunchKernelEx(&cfg, eb_pool_stream_kernel<TW, VE, LL, kOpWeighted, stream_u(LL), true>, a, x)
+      : cudaLaunchKernelEx(&cfg, eb_pool_stream_kernel<TW, VE, LL, kOpSum, stream_u(LL), true>, a, x);
+  count_launch();
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <typename TW>
+static cudaError_t launch_push_stream(const PoolArgs& a, const PushArgs& x, bool weighted,
+                                      cudaStream_t st) {
+  if (a.lanes_log2 == 3) return launch_push_stream_ll<TW, 3>(a, x, weighted, st);
+  if (a.lanes_log2 == 4) return launch_push_stream_ll<TW, 4>(a, x, weighted, st);
+  return launch_push_stream_ll<TW, 5>(a, x, weighted, st);
+}
+
+static_assert(FWD_EB_MAX_PEERS == 16, "PushArgs (eb_stream.cuh) holds 16 peers");
+
 }  // namespace fwd_eb
 
 using namespace fwd_eb;
@@ -331,15 +361,14 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
                 x->world, (long long)x->bags_per_rank);
   // Reuse the single-GPU planner for shapes and checks; the output it plans for is replaced.
   fwd_eb_params q = *p;
-  q.strategy = FWD_EB_STRATEGY_GROUP;
   q.out = x->peer_slots[x->rank];
   q.out_dtype = x->wire_dtype;
   if (x->layout == FWD_EB_LAYOUT_ROW_SHARD)
     q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean torch would round
   q.out_stride = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (int64_t)x->num_tables * p->dim : 0;
   PoolArgs a;
-  int vec = 0, cpl = 0, tiles = 0;
-  rc = plan_group(&q, &a, &vec, &cpl, &tiles);
+  int vec = 0, cpl = 0, tiles = 0, stream_kernel = 0;
+  rc = plan_group(&q, &a, &vec, &cpl, &tiles, &stream_kernel);
   if (rc) return rc;
   PushArgs px;
   fill_push(x, p->dim, &px);
@@ -348,9 +377,15 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
   px.small = p->num_bags <= 0x7fffffffLL && x->bags_per_rank <= 0x7fffffffLL;
   const bool weighted = p->per_sample_weights != nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  cudaError_t e = p->table_dtype == FWD_EB_F16
-                      ? launch_push_shape<__half>(a, px, vec != 0, cpl, tiles, weighted, st)
-                      : launch_push_shape<float>(a, px, vec != 0, cpl, tiles, weighted, st);
+  cudaError_t e;
+  if (stream_kernel) {
+    e = p->table_dtype == FWD_EB_F16 ? launch_push_stream<__half>(a, px, weighted, st)
+                                     : launch_push_stream<float>(a, px, weighted, st);
+  } else {
+    e = p->table_dtype == FWD_EB_F16
+            ? launch_push_shape<__half>(a, px, vec != 0, cpl, tiles, weighted, st)
+            : launch_push_shape<float>(a, px, vec != 0, cpl, tiles, weighted, st);
+  }
   if (e != cudaSuccess) return cuda_fail(e, "push kernel launch");
   clear_error();
   return 0;
@@ -390,6 +425,11 @@ int fwd_eb_shard_signal(const fwd_eb_shard_exchange* x, void* stream) {
 
 int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
                          void* d_out, int32_t out_dtype, void* stream) {
+  return fwd_eb_shard_combine_div(x, dim, num_bags, nullptr, d_out, out_dtype, stream);
+}
+
+int fwd_eb_shard_combine_div(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                             const int32_t* d_counts, void* d_out, int32_t out_dtype, void* stream) {
   int rc = check_exchange(x);
   if (rc) return rc;
   if (dim <= 0 || num_bags < 0 || num_bags > x->bags_per_rank || (num_bags > 0 && !d_out))
@@ -403,9 +443,10 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
   const bool wire16 = x->wire_dtype == FWD_EB_F16, out16 = out_dtype == FWD_EB_F16;
   if (x->wire_dtype == FWD_EB_F32_POS) {
+    if (d_counts) return fail(FWD_EB_EINVAL, "a divisor makes no sense for a sharded MAX");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     if (blocks < 1) blocks = 1;
     eb_shard_wait_kernel<<<1, 32, 0, st>>>(flags, x->rank, x->world, x->epoch, x->status, spins);
     count_launch();
@@ -425,12 +466,12 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
     return 0;
   }
   const int pk = wire16 ? 8 : 4;
-  const bool vec = count % pk == 0 && slot_stride % pk == 0 &&
+  const bool vec = count % pk == 0 && slot_stride % pk == 0 && dim % pk == 0 &&
                    (reinterpret_cast<uintptr_t>(slots) & 15u) == 0 &&
                    (reinterpret_cast<uintptr_t>(d_out) & 15u) == 0;
   const long long packets = vec ? count / pk : count;
   long long blocks = (packets + kCtaThreads - 1) / kCtaThreads;
-  if (blocks > 148 * 4) blocks = 148 * 4;
+  if (blocks > sm_count() * 4) blocks = sm_count() * 4;
   if (blocks < 1) blocks = 1;
   const unsigned g = (unsigned)blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -440,7 +481,7 @@ int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t nu
 #define FWD_EB_COMBINE(TP, TO, V)                                                                \
   eb_shard_combine_kernel<TP, TO, V><<<g, kCtaThreads, 0, st>>>(                                 \
       reinterpret_cast<const TP*>(slots), x->world, slot_stride, count, static_cast<TO*>(d_out), \
-      x->status)
+      x->status, d_counts, dim)
   if (vec) {
     if (!wire16 && !out16) FWD_EB_COMBINE(float, float, true);
     else if (!wire16 && out16) FWD_EB_COMBINE(float, __half, true);
@@ -471,7 +512,19 @@ struct fwd_eb_pipeline {
   uint32_t epoch = 0;
 };
 
+// A step that fails its host-side checks before anything was launched must not leave this rank
+// one call number ahead of its peers (their next wait would accept this rank's NEXT flag and
+// fold a buffer part it never wrote): such a return takes the number back.
+static int pipeline_abort(fwd_eb_pipeline* pl, int rc) {
+  pl->epoch -= 1;
+  return rc;
+}
+
 static int pipeline_begin(fwd_eb_pipeline* pl, fwd_eb_shard_exchange* x, cudaStream_t main) {
+  // Call numbers are 32-bit flag values and pick the buffer part modulo 3: refuse the step that
+  // would wrap them (2^32 steps: more than a day at 25 us a step) instead of going out of phase.
+  if (pl->epoch >= 0xfffffff0u)
+    return fail(FWD_EB_ETOOBIG, "this pipeline has run 2^32 steps: drain it on every rank and create a new one");
   pl->epoch += 1;
   x->epoch = pl->epoch;
   if (pl->epoch > 2) {
@@ -534,12 +587,67 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   int rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
-  rc = fwd_eb_shard_push(p, x, main);
-  if (rc) return rc;
+  rc = fwd_eb_shard_push(p, x, main);   // validates before it launches
+  if (rc) return pipeline_abort(pl, rc);
   rc = pipeline_handover(pl, main);
   if (rc) return rc;
   const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
   rc = fwd_eb_shard_combine(x, p->dim, num_bags_owned, d_out[k], out_dtype, pl->side);
+  if (rc) return rc;
+  cudaError_t e = cudaEventRecord(pl->done[k], pl->side);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord (side)");
+  if (which) *which = k;
+  return 0;
+}
+
+int fwd_eb_pipeline_step_rowshard_compact(fwd_eb_pipeline* pl, const fwd_eb_params* p,
+                                          fwd_eb_shard_exchange* x, int64_t num_bags_owned,
+                                          const fwd_eb_compact_scratch* scratch,
+                                          void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
+                                          void* main_stream, int32_t* which) {
+  if (!pl || !p || !x || !d_out || !scratch) return fail(FWD_EB_EINVAL, "null argument");
+  if (x->layout != FWD_EB_LAYOUT_ROW_SHARD)
+    return fail(FWD_EB_EINVAL, "window compaction is for the row-shard layout");
+  if (p->mode != FWD_EB_MODE_SUM && p->mode != FWD_EB_MODE_MEAN)
+    return fail(FWD_EB_EUNSUPPORTED, "compacted row shards support SUM and MEAN (got mode %d); a sharded "
+                "MAX goes through the staged exchange", p->mode);
+  const bool mean = p->mode == FWD_EB_MODE_MEAN;
+  if (!scratch->kept || !scratch->bounds || (mean && !scratch->counts) ||
+      (p->per_sample_weights && !scratch->kept_weights))
+    return fail(FWD_EB_EINVAL, "compaction scratch is incomplete");
+  cudaStream_t main = static_cast<cudaStream_t>(main_stream);
+  int rc = pipeline_begin(pl, x, main);
+  if (rc) return rc;
+  const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
+  if (!d_out[k]) return pipeline_abort(pl, fail(FWD_EB_EINVAL, "null output buffer"));
+  // 1. the window filter as one streaming pass; a mean also keeps each bag's full count, in the
+  //    part of `counts` that belongs to this step (the fold reads it beside the next step)
+  const int64_t all_bags = (int64_t)x->world * x->bags_per_rank;
+  int32_t* counts = mean ? scratch->counts + (int64_t)k * all_bags : nullptr;
+  rc = fwd_eb_compact_window(p, scratch->kept, scratch->kept_weights, scratch->bounds, counts, main);
+  if (rc) return pipeline_abort(pl, rc);
+  // 2. pool the dense sub-bags, partial rows pushed to their owners (partials of a mean are sums)
+  fwd_eb_params q = *p;
+  q.indices = scratch->kept;
+  q.index_dtype = FWD_EB_I32;
+  q.offsets = scratch->bounds;
+  q.flags = (p->flags | FWD_EB_FLAG_OFFSET_PAIRS | FWD_EB_FLAG_PAIRS_RUN32);
+  q.fixed_len = 0;
+  q.include_last_offset = 0;
+  q.row_lo = 0;
+  q.padding_idx = -1;
+  q.mode = FWD_EB_MODE_SUM;
+  if (p->per_sample_weights) q.per_sample_weights = scratch->kept_weights;
+  if (q.strategy != FWD_EB_STRATEGY_GROUP && q.strategy != FWD_EB_STRATEGY_STREAM)
+    q.strategy = FWD_EB_STRATEGY_AUTO;
+  rc = fwd_eb_shard_push(&q, x, main);
+  if (rc) return rc;   // the compaction has run: the step cannot be taken back
+  rc = pipeline_handover(pl, main);
+  if (rc) return rc;
+  // 3. flags, bounded wait, fold (and the mean's division) on the side stream
+  rc = fwd_eb_shard_combine_div(x, p->dim, num_bags_owned,
+                                mean ? counts + (int64_t)x->rank * x->bags_per_rank : nullptr, d_out[k],
+                                out_dtype, pl->side);
   if (rc) return rc;
   cudaError_t e = cudaEventRecord(pl->done[k], pl->side);
   if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord (side)");
@@ -592,9 +700,9 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
   rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
   rc = check_exchange(x);
-  if (rc) return rc;
+  if (rc) return pipeline_abort(pl, rc);
   const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
-  if (!d_stage[k] || !d_out[k]) return fail(FWD_EB_EINVAL, "null staging or output buffer");
+  if (!d_stage[k] || !d_out[k]) return pipeline_abort(pl, fail(FWD_EB_EINVAL, "null staging or output buffer"));
   // 1. pool every bag's partial into local staging (the plain lane-group kernel)
   fwd_eb_params q = *p;
   q.strategy = FWD_EB_STRATEGY_GROUP;
@@ -602,8 +710,8 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
   q.out_dtype = x->wire_dtype;  // fp32 / fp16 partial sums, or {value, position} pairs for MAX
   q.out_stride = 0;
   q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean
-  rc = fwd_eb_forward(&q, main);
-  if (rc) return rc;
+  rc = fwd_eb_forward(&q, main);   // validates before it launches
+  if (rc) return pipeline_abort(pl, rc);
   rc = pipeline_handover(pl, main);
   if (rc) return rc;
   // 2. one copy-engine transfer per owner: its block of partial bags -> slot [rank] over there
@@ -630,7 +738,7 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
   for (int i = 0; i < count; ++i) {
     x->table_index = table_index[i];
     rc = fwd_eb_shard_push(params[i], x, main);
-    if (rc) return rc;
+    if (rc) return i == 0 ? pipeline_abort(pl, rc) : rc;   // nothing launched yet: take the number back
   }
   rc = pipeline_handover(pl, main);
   if (rc) return rc;

@@ -11,6 +11,9 @@ batch, pools what it owns into partial bags, and bag b ends up, summed, on rank 
   exchange="push"  fwd_eb_pipeline_step_rowshard: partial rows go straight into the owner's slots
                    over NVLink from inside the pooling kernel; the flag exchange and the fold run on
                    a side stream beside the next call's pooling
+  exchange="compact" fwd_eb_pipeline_step_rowshard_compact (sum / mean; the fastest): a streaming
+                   pass keeps this rank's indices as dense sub-bags, the pooling kernel walks those
+                   and pushes the partial rows to their owners; flags and fold as "push"
   exchange="stage" fwd_eb_pipeline_step_rowshard_staged: the plain pooling kernel writes the partial
                    bags locally and the copy engines carry each owner's block over NVLink (side
                    stream, beside the next call's pooling); same flags and fold as "push"
@@ -68,6 +71,12 @@ def place_tables(table_bytes: list[int], world: int, lookups: list[int] | None =
 
 # ---- C structs -----------------------------------------------------------------------------------
 
+class CompactScratch(C.Structure):
+    """Mirror of struct fwd_eb_compact_scratch."""
+    _fields_ = [("kept", C.c_void_p), ("kept_weights", C.c_void_p), ("bounds", C.c_void_p),
+                ("counts", C.c_void_p)]
+
+
 class ShardExchange(C.Structure):
     """Mirror of struct fwd_eb_shard_exchange."""
     _fields_ = [
@@ -86,6 +95,12 @@ SIGNATURES = {
     "fwd_eb_shard_push": (C.c_int, [C.POINTER(capi.Params), C.POINTER(ShardExchange), C.c_void_p]),
     "fwd_eb_shard_combine": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.c_int64, C.c_void_p,
                                        C.c_int32, C.c_void_p]),
+    "fwd_eb_shard_combine_div": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.c_int64, C.c_void_p,
+                                           C.c_void_p, C.c_int32, C.c_void_p]),
+    "fwd_eb_pipeline_step_rowshard_compact": (C.c_int, [C.c_void_p, C.POINTER(capi.Params),
+                                                        C.POINTER(ShardExchange), C.c_int64,
+                                                        C.POINTER(CompactScratch), C.POINTER(C.c_void_p),
+                                                        C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]),
     "fwd_eb_shard_wait": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.POINTER(C.c_void_p),
                                     C.c_void_p]),
     "fwd_eb_shard_signal": (C.c_int, [C.POINTER(ShardExchange), C.c_void_p]),
@@ -210,7 +225,7 @@ class RowShardedBag:
 
     def __init__(self, table_local, row_lo: int, *, mode: int, max_bags: int, group=None,
                  exchange: str = "push", wire_dtype: int = capi.F32, padding_idx: int = -1,
-                 out_dtype=None):
+                 out_dtype=None, max_indices: int = 0):
         import torch
         import torch.distributed as dist
         if mode == capi.MODE_MAX:
@@ -235,7 +250,9 @@ class RowShardedBag:
         self.out = torch.empty((self.per, self.dim), dtype=self.out_dtype, device=dev)
         self.side = None
         self.ready = None
-        self.piped = exchange in ("push", "stage")
+        self.piped = exchange in ("push", "stage", "compact")
+        if exchange == "compact" and max_indices <= 0:
+            raise ValueError("exchange='compact' needs max_indices (its scratch is sized up front)")
         if self.piped:
             # The fold runs on the pipeline's side stream so that the next call's pooling does
             # not queue behind this call's flag exchange; results rotate through three buffers.
@@ -249,6 +266,16 @@ class RowShardedBag:
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
             self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status)
+            if exchange == "compact":
+                # scratch of the window compaction: kept indices, sub-bag bounds, and for a mean
+                # the bags' full counts (three parts: a fold reads them beside the next step)
+                nb_all = self.per * self.world
+                self._kept = torch.empty(max_indices, dtype=torch.int32, device=dev)
+                self._bounds = torch.empty((nb_all, 2), dtype=torch.int32, device=dev)
+                self._counts = torch.zeros((3, nb_all), dtype=torch.int32, device=dev)
+                self._scratch = CompactScratch(self._kept.data_ptr(), None, self._bounds.data_ptr(),
+                                               self._counts.data_ptr())
+                self.max_indices = max_indices
             if exchange == "stage":
                 # "stage": the plain pooling kernel writes all partial bags here and the copy
                 # engines carry each owner's block over NVLink beside the next call's pooling
@@ -277,6 +304,8 @@ class RowShardedBag:
         num_bags = offsets.numel()
         if num_bags > self.max_bags:
             raise ValueError("batch larger than max_bags")
+        if self.exchange == "compact" and indices.numel() > self.max_indices:
+            raise ValueError("batch holds more indices than max_indices")
         _, mine = owned_bags(self.per * self.world, self.world, self.rank)
         mine = max(0, min(mine, num_bags - self.rank * self.per))
         out = self.out if self.piped else self.partial
@@ -294,7 +323,11 @@ class RowShardedBag:
         if self.piped:
             if pool_events:
                 pool_events[0].record()
-            if self.exchange == "stage":
+            if self.exchange == "compact":
+                capi.check(_lib().fwd_eb_pipeline_step_rowshard_compact(
+                    self._pl, C.byref(p), C.byref(self.x), mine, C.byref(self._scratch), self._out_ptrs,
+                    capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))
+            elif self.exchange == "stage":
                 capi.check(_lib().fwd_eb_pipeline_step_rowshard_staged(
                     self._pl, C.byref(p), C.byref(self.x), mine, self._stage_ptrs, self._out_ptrs,
                     capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))

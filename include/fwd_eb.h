@@ -58,7 +58,13 @@ enum {
   FWD_EB_STRATEGY_AUTO = 0,
   FWD_EB_STRATEGY_GROUP = 1, /* a sub-warp lane group (16 B per lane) per bag    */
   FWD_EB_STRATEGY_CTA = 2,   /* one CTA per bag, lane groups split the bag       */
-  FWD_EB_STRATEGY_SPLIT = 3  /* several CTAs per bag + partials in `workspace`   */
+  FWD_EB_STRATEGY_SPLIT = 3, /* several CTAs per bag + partials in `workspace`   */
+  /* a lane group streams a run of consecutive bags: indices one block ahead in a
+   * shared-memory ring, a rolling queue of row loads that bag boundaries do not
+   * interrupt.  Rows of 128..512 bytes on the 16-byte vector path, int32 indices,
+   * fewer than 2^31 of them; a call outside those limits returns
+   * FWD_EB_EUNSUPPORTED when STREAM is asked for by name. */
+  FWD_EB_STRATEGY_STREAM = 4
 };
 
 /* Flags (fwd_eb_params.flags). */
@@ -72,7 +78,16 @@ enum {
   FWD_EB_FLAG_GATHER_KEEP_SKIPPED = 2,
   /* fp16 mean rounds the fp32 sum once after the division; default mimics
    * torch CPU (round the sum to fp16, divide, round again). */
-  FWD_EB_FLAG_MEAN_SINGLE_ROUNDING = 4
+  FWD_EB_FLAG_MEAN_SINGLE_ROUNDING = 4,
+  /* `offsets` holds a {start, end} pair per bag ([num_bags][2], the indices' type)
+   * instead of one start per bag: bags need not be back to back in `indices`.
+   * This is what fwd_eb_compact_window writes.  fixed_len must be 0;
+   * include_last_offset is ignored. */
+  FWD_EB_FLAG_OFFSET_PAIRS = 8,
+  /* with OFFSET_PAIRS: inside every aligned run of 32 bags (bags 32k .. 32k+31) each
+   * bag starts where the previous one ends, as fwd_eb_compact_window lays them
+   * out; lets the STREAM strategy walk several bags as one index stream. */
+  FWD_EB_FLAG_PAIRS_RUN32 = 16
 };
 
 /* Error codes. */
@@ -181,9 +196,41 @@ size_t fwd_eb_workspace_size(const fwd_eb_params* p);
  *     (different streams, no dependency) would overwrite each other's
  *     partials: keep calls to this entry point ordered on one stream, or
  *     serialise them with events.
+ *   - The cached address belongs to the device's current primary context.  A host
+ *     that calls cudaDeviceReset() invalidates it (and every other device pointer
+ *     it holds); this entry point must not be used across such a reset.
  */
 #define FWD_EB_STATIC_SCRATCH_BYTES (8u << 20)
 int fwd_eb_forward_static_scratch(const fwd_eb_params* p, void* stream);
+
+/*
+ * Window compaction: run the table-window / padding filter of `p` once, as a
+ * streaming pass, instead of inside the pooling loop.  The reference tests every
+ * index of every bag against `data_offset` / `count` in its bag loop
+ * (embedding_bag_plugin.cu:94); for a rank that holds one of G row windows of a
+ * sharded table that is G times more index traffic and G times more loop
+ * iterations than rows it will gather.
+ *
+ * Reads p->indices / offsets / fixed_len / include_last_offset / num_bags /
+ * num_indices / row_lo / num_rows / padding_idx / per_sample_weights (other fields
+ * are ignored) and writes
+ *   d_kept    int32 [num_indices]  the surviving indices as LOCAL row numbers
+ *             (index - row_lo), in bag order; the survivors of bags 32k..32k+31 are
+ *             back to back starting at the position where bag 32k starts in
+ *             p->indices (entries past a run's survivors are left untouched);
+ *   d_kept_weights fp32 [num_indices], the survivors' weights (NULL unless
+ *             p->per_sample_weights is set);
+ *   d_bounds  int32 [num_bags][2]  {start, end} of every bag's survivors in d_kept;
+ *   d_counts  int32 [num_bags] or NULL: non-padding entries of the WHOLE bag, inside
+ *             the window or not (the divisor of a sharded mean).
+ * Pool the result with indices = d_kept, index_dtype = FWD_EB_I32, offsets =
+ * d_bounds, flags |= FWD_EB_FLAG_OFFSET_PAIRS | FWD_EB_FLAG_PAIRS_RUN32, row_lo = 0,
+ * padding_idx = -1 and per_sample_weights = d_kept_weights: every index then passes
+ * the filter and the pooling kernels take their dense path.  num_indices must be
+ * below 2^31.  Launches one kernel on `stream`; allocates nothing.
+ */
+int fwd_eb_compact_window(const fwd_eb_params* p, int32_t* d_kept, float* d_kept_weights,
+                          int32_t* d_bounds, int32_t* d_counts, void* stream);
 
 /* Which strategy AUTO resolves to for `p` (a FWD_EB_STRATEGY_* value, or a
  * negative error).  `p->workspace_bytes` decides whether SPLIT is on offer. */

@@ -92,6 +92,12 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
 int fwd_eb_shard_combine(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
                          void* d_out, int32_t out_dtype, void* stream);
 
+/* fwd_eb_shard_combine followed by out[b, :] /= max(1, d_counts[b]): for a sharded MEAN whose
+ * partials are plain sums (d_counts: int32, one entry per bag this rank owns; NULL = no division,
+ * i.e. fwd_eb_shard_combine). */
+int fwd_eb_shard_combine_div(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                             const int32_t* d_counts, void* d_out, int32_t out_dtype, void* stream);
+
 /* ROW_SHARD, the copy-engine alternative to fwd_eb_shard_push: `d_stage` holds the partial
  * bags of ALL `num_bags` bags, [num_bags, dim] in the wire dtype, as fwd_eb_forward with this
  * rank's row window (and FWD_EB_FLAG_MEAN_SINGLE_ROUNDING for MEAN) wrote them; each owner's
@@ -150,6 +156,27 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
                                          void* const d_stage[FWD_EB_SHARD_BUFFERS],
                                          void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
                                          void* main_stream, int32_t* which);
+
+/* Row shards with the window filter taken out of the pooling loop (the fastest row-shard step).
+ * The reference tests every index against its row window inside the bag loop
+ * (embedding_bag_plugin.cu:94); with G windows that loop reads G times more indices than it
+ * gathers rows.  Here, on `main_stream`: (1) fwd_eb_compact_window streams over the batch once
+ * and keeps this rank's indices as dense sub-bags; (2) the pooling kernel walks those and pushes
+ * each partial row into slot [rank] of the bag's owner; then, on the side stream, (3) flags,
+ * bounded wait and fold as in fwd_eb_pipeline_step_rowshard.  Partials of a MEAN are plain sums
+ * and the owner divides by the bag's full count after the fold.  `p->out` is ignored.
+ * Scratch is the caller's (nothing is allocated): */
+typedef struct fwd_eb_compact_scratch {
+  int32_t* kept;          /* [max num_indices] */
+  float* kept_weights;    /* [max num_indices], or NULL when no per_sample_weights are used */
+  int32_t* bounds;        /* [max num_bags][2], 8-byte aligned */
+  int32_t* counts;        /* MEAN only: [3][world * bags_per_rank], one part per step in flight */
+} fwd_eb_compact_scratch;
+int fwd_eb_pipeline_step_rowshard_compact(fwd_eb_pipeline* pl, const fwd_eb_params* p,
+                                          fwd_eb_shard_exchange* x, int64_t num_bags_owned,
+                                          const fwd_eb_compact_scratch* scratch,
+                                          void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
+                                          void* main_stream, int32_t* which);
 
 /* Table-wise: push the `count` local tables (x->table_index is set from table_index[i]),
  * then the flag exchange on the side stream; *d_result receives this step's buffer part. */

@@ -30,11 +30,12 @@ def _worker(rank, world, port, tmp):
     lo, n = fd.shard_rows(rows, world, rank)
     local = torch.from_numpy(table[lo:lo + n]).to(dev)
     shards = [fd.shard_rows(rows, world, r) for r in range(world)]
-    for exchange, wire in (("push", capi.F32), ("push", capi.F16), ("stage", capi.F32),
+    for exchange, wire in (("compact", capi.F32), ("compact", capi.F16), ("push", capi.F32),
+                           ("push", capi.F16), ("stage", capi.F32),
                            ("stage", capi.F16), ("a2a", capi.F32), ("nccl", capi.F32)):
         for mode in (capi.MODE_SUM, capi.MODE_MEAN):
             bag = fd.RowShardedBag(local, lo, mode=mode, max_bags=nb, exchange=exchange,
-                                   wire_dtype=wire, padding_idx=3)
+                                   wire_dtype=wire, padding_idx=3, max_indices=80 * nb)
             for step in range(3):
                 brng = np.random.default_rng(100 + step)
                 bags = workloads.ragged_bags(rows, brng.integers(0, 80, nb), brng)
@@ -46,9 +47,19 @@ def _worker(rank, world, port, tmp):
                 parts = np.stack([O.pool(table[a:a + c], bags.indices, bags.offsets, mode=mode,
                                          padding_idx=3, row_lo=a, out_dtype=np.float32)
                                   for a, c in shards])
+                if exchange == "compact" and mode == capi.MODE_MEAN:
+                    # partials are sums; the owner divides by the bag's full count after the fold
+                    parts = np.stack([O.pool(table[a:a + c], bags.indices, bags.offsets, mode=O.MODE_SUM,
+                                             padding_idx=3, row_lo=a, out_dtype=np.float32)
+                                      for a, c in shards])
                 if wire == capi.F16:
                     parts = parts.astype(np.float16)
                 expect = O.combine_partials(parts, np.float32)
+                if exchange == "compact" and mode == capi.MODE_MEAN:
+                    ends = np.append(bags.offsets, bags.num_indices)
+                    full = np.array([np.count_nonzero(bags.indices[ends[b]:ends[b + 1]] != 3)
+                                     for b in range(nb)])
+                    expect = (expect / np.maximum(full, 1)[:, None].astype(np.float32)).astype(np.float32)
                 blo, mine = fd.owned_bags(nb, world, rank)
                 g = got.cpu().numpy()
                 if exchange == "nccl":

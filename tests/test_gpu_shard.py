@@ -117,6 +117,96 @@ def test_row_shard_staged_send_equals_push(wire):
     assert all(int(k.item()) == 0 for k in keep)
 
 
+@pytest.mark.parametrize("wire", [capi.F32, capi.F16])
+@pytest.mark.parametrize("mode", [capi.MODE_SUM, capi.MODE_MEAN])
+def test_row_shard_compacted_push_equals_the_replicated_scan(wire, mode):
+    """Window compaction first, then the pooling kernel pushes the dense sub-bags' partial rows:
+    for SUM the result is bit-identical to the fold of the ranks' partials (what the push and the
+    staged exchange give); a MEAN is folded as sums and divided by the bag's full count."""
+    rng = np.random.default_rng(28)
+    world, rows, dim, nb = 4, 8000, 64, 1000
+    table = rng.standard_normal((rows, dim)).astype(np.float16)
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, wire)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    shards = [fd.shard_rows(rows, world, r) for r in range(world)]
+    tabs = [_cuda(table[lo:lo + n]) for lo, n in shards]
+    for epoch in (1, 2):
+        bags = workloads.ragged_bags(rows, rng.integers(0, 60, nb), rng)
+        bags.indices[::7] = 5
+        i, o = _cuda(bags.indices), _cuda(bags.offsets)
+        counts = []
+        for r in range(world):
+            xs[r].epoch = epoch
+            kept = torch.empty(bags.num_indices, dtype=torch.int32, device=DEV)
+            bounds = torch.empty((nb, 2), dtype=torch.int32, device=DEV)
+            cnt = torch.zeros(nb, dtype=torch.int32, device=DEV)
+            p = capi.make_params(tabs[r], i, o, out=tabs[r][:1], mode=mode, padding_idx=5,
+                                 row_lo=shards[r][0])
+            capi.compact_window(p, kept, bounds, counts=cnt)
+            q = capi.make_compacted_params(tabs[r], kept, bounds, out=tabs[r][:1], mode=capi.MODE_SUM)
+            capi.check(lib.fwd_eb_shard_push(C.byref(q), C.byref(xs[r]), stream))
+            counts.append(cnt)
+            keep += [kept, bounds]
+        for r in range(world):
+            capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
+        parts = np.stack([O.pool(table[lo:lo + n], bags.indices, bags.offsets, mode=O.MODE_SUM,
+                                 padding_idx=5, row_lo=lo, out_dtype=np.float32) for lo, n in shards])
+        if wire == capi.F16:
+            parts = parts.astype(np.float16)
+        expect = O.combine_partials(parts, np.float32)
+        if mode == capi.MODE_MEAN:
+            ends = np.append(bags.offsets, bags.num_indices)
+            full = np.array([np.count_nonzero(bags.indices[ends[b]:ends[b + 1]] != 5) for b in range(nb)])
+            expect = (expect / np.maximum(full, 1)[:, None].astype(np.float32)).astype(np.float32)
+        for r in range(world):
+            lo, mine = fd.owned_bags(nb, world, r)
+            out = torch.full((per, dim), float("nan"), device=DEV)
+            cptr = C.c_void_p(counts[r][lo:].data_ptr()) if mode == capi.MODE_MEAN else None
+            capi.check(lib.fwd_eb_shard_combine_div(C.byref(xs[r]), dim, mine, cptr, out.data_ptr(),
+                                                    capi.F32, stream))
+            torch.cuda.synchronize()
+            assert np.array_equal(out[:mine].cpu().numpy(), expect[lo:lo + mine])
+    assert all(int(k.item()) == 0 for k in keep if k.numel() == 1 and k.dtype == torch.int32)
+
+
+def test_row_shard_config5_geometry_small_window():
+    """Config 5's numbers on a small physical window: logical rows up to 10^9 (int32 indices near
+    2^30), a shard whose row_lo lies beyond 5*10^8, G = 8 windows of which this GPU holds one.
+    The compacted path and the replicated scan must agree bit for bit with the CPU oracle."""
+    rng = np.random.default_rng(45)
+    G, dim, nb = 8, 64, 4096
+    logical = 1_000_000_000
+    per_rows = logical // G
+    rank = 5                                             # row_lo = 625,000,000
+    row_lo = rank * per_rows
+    phys = 50_000                                        # rows actually held: the head of the window
+    table = torch.empty((phys, dim), dtype=torch.float16, device=DEV)
+    capi.fill_table(table, row_lo, seed=4, scale=0.05)
+    lengths = rng.integers(1, 101, nb)
+    n = int(lengths.sum())
+    idx = rng.integers(0, logical, n)
+    near = rng.random(n) < 0.3                           # a third of the lookups land in the held rows
+    idx[near] = row_lo + rng.integers(0, phys, int(near.sum()))
+    idx[rng.random(n) < 0.01] = logical - 1              # the largest index of the table
+    idx = idx.astype(np.int32)
+    off = workloads.offsets_from_lengths(lengths).astype(np.int32)
+    host_rows = O.table_rows(np.arange(row_lo, row_lo + phys, dtype=np.int64), dim, seed=4, scale=0.05,
+                             dtype=np.float16)
+    exp = O.pool(host_rows, idx, off, mode=O.MODE_SUM, row_lo=row_lo, out_dtype=np.float32)
+    i, o = _cuda(idx), _cuda(off)
+    scan = capi.embedding_bag(table, i, o, row_lo=row_lo, out_dtype=torch.float32)
+    kept = torch.empty(n, dtype=torch.int32, device=DEV)
+    bounds = torch.empty((nb, 2), dtype=torch.int32, device=DEV)
+    out = torch.empty((nb, dim), dtype=torch.float32, device=DEV)
+    p = capi.make_params(table, i, o, out=out, row_lo=row_lo)
+    capi.compact_window(p, kept, bounds)
+    capi.forward(capi.make_compacted_params(table, kept, bounds, out=out))
+    torch.cuda.synchronize()
+    assert np.array_equal(scan.cpu().numpy(), exp)
+    assert np.array_equal(out.cpu().numpy(), exp)
+
+
 def _tricky_table(rng, rows, dim, dtype):
     """Few distinct values (many ties), signed zeros and some NaN rows."""
     t = rng.integers(-2, 3, (rows, dim)).astype(dtype)
