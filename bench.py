@@ -1035,8 +1035,10 @@ def reference_kernel_side_by_side(wl):
         torch.cuda.synchronize()
         return a.elapsed_time(b) * 1e3 / n
 
+    for i_, o_ in wl.d_batches:     # checked once (the check synchronises), timed unchecked
+        R.bag(i_, o_, out_ref, t32, 0, 0, stream)
     ref_us = timed(lambda k: R.bag(wl.d_batches[k % wl.nb][0], wl.d_batches[k % wl.nb][1], out_ref,
-                                   t32, 0, 0, stream), 50)
+                                   t32, 0, 0, stream, check=False), 50)
     ours_us = timed(lambda k: capi.forward(params[k % wl.nb], stream), 200)
     R.bag(wl.d_batches[0][0], wl.d_batches[0][1], out_ref, t32, 0, 0, stream)
     capi.forward(params[0], stream)

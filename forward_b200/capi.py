@@ -18,9 +18,9 @@ F32, F16 = 0, 1
 F32_POS = 2          # MODE_MAX only: {fp32 value, int32 position} per column
 NO_POS = 0x7FFFFFFF
 I32, I64 = 0, 1
-STRATEGY_AUTO, STRATEGY_GROUP, STRATEGY_CTA, STRATEGY_SPLIT, STRATEGY_STREAM = 0, 1, 2, 3, 4
+STRATEGY_AUTO, STRATEGY_GROUP, STRATEGY_CTA, STRATEGY_SPLIT, STRATEGY_STREAM, STRATEGY_LITE = 0, 1, 2, 3, 4, 5
 FLAG_MEAN_RAW_LENGTH, FLAG_GATHER_KEEP_SKIPPED, FLAG_MEAN_SINGLE_ROUNDING = 1, 2, 4
-FLAG_OFFSET_PAIRS, FLAG_PAIRS_RUN32 = 8, 16
+FLAG_OFFSET_PAIRS, FLAG_PAIRS_RUN16 = 8, 16
 EINVAL, EUNSUPPORTED, EALIGN, EWORKSPACE, ENOGPU, ETOOBIG = -1, -2, -3, -4, -5, -6
 
 
@@ -225,7 +225,7 @@ def make_compacted_params(table, kept, bounds, *, out, mode=MODE_SUM, kept_weigh
                           strategy=STRATEGY_AUTO, flags=0) -> Params:
     """Params that pool what compact_window wrote: local row numbers, {start, end} pairs."""
     p = make_params(table, kept, None, out=out, mode=mode, per_sample_weights=kept_weights,
-                    fixed_len=1, strategy=strategy, flags=flags | FLAG_OFFSET_PAIRS | FLAG_PAIRS_RUN32)
+                    fixed_len=1, strategy=strategy, flags=flags | FLAG_OFFSET_PAIRS | FLAG_PAIRS_RUN16)
     p.fixed_len = 0
     p.offsets = bounds.data_ptr()
     p.num_bags = bounds.shape[0]

@@ -16,6 +16,7 @@
 #include "eb_compact.cuh"
 #include "eb_internal.h"
 #include "eb_kernels.cuh"
+#include "eb_lite.cuh"
 #include "eb_stream.cuh"
 #include "fwd_eb.h"
 
@@ -149,7 +150,7 @@ static int validate(const fwd_eb_params* p) {
   }
   if (p->per_sample_weights && p->mode != FWD_EB_MODE_SUM)
     return fail(FWD_EB_EINVAL, "per_sample_weights need mode SUM (torch rule)");
-  if (p->strategy < FWD_EB_STRATEGY_AUTO || p->strategy > FWD_EB_STRATEGY_STREAM)
+  if (p->strategy < FWD_EB_STRATEGY_AUTO || p->strategy > FWD_EB_STRATEGY_LITE)
     return fail(FWD_EB_EINVAL, "unknown strategy %d", p->strategy);
   if (p->flags & FWD_EB_FLAG_OFFSET_PAIRS) {
     if (p->fixed_len > 0) return fail(FWD_EB_EINVAL, "offset pairs and fixed_len exclude each other");
@@ -184,12 +185,12 @@ static bool stream_ok(const fwd_eb_params* p, const Plan* pl) {
 // Consecutive bags per lane group: about a hundred rows per run, so the start-up chain
 // (bounds, first index block, first rows) is paid once per run instead of once per bag, but
 // never so many that the grid falls below two waves of resident groups.  With offset pairs a
-// run must stay inside one aligned block of 32 bags (a power of two), and only when the caller
+// run must stay inside one aligned block of 16 bags (a power of two), and only when the caller
 // vouches for their contiguity.
 static int choose_stream_k(const fwd_eb_params* p, int lanes_log2) {
   if (p->num_bags <= 0) return 1;
   const bool pairs = (p->flags & FWD_EB_FLAG_OFFSET_PAIRS) != 0;
-  if (pairs && !(p->flags & FWD_EB_FLAG_PAIRS_RUN32)) return 1;
+  if (pairs && !(p->flags & FWD_EB_FLAG_PAIRS_RUN16)) return 1;
   long long avg = p->fixed_len > 0 ? p->fixed_len : p->num_indices / p->num_bags;
   if (avg < 1) avg = 1;
   long long k = 96 / avg;
@@ -294,15 +295,24 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
     return 0;
   }
   pl->strategy = pick_strategy(p);
-  if (a.pairs && pl->strategy != FWD_EB_STRATEGY_STREAM) pl->strategy = FWD_EB_STRATEGY_GROUP;
-  // AUTO: where a lane group per bag is the plan, the streaming kernel takes the shapes it
-  // measured faster on: 512-byte and 128-byte rows (B200: 32.3 against 33.8 us on 8192 bags of
-  // 0..64 rows of 512 B; 63 against 78 us on 65536 x 20 weighted fp32 rows; 36 against 44 us
-  // on 131072 bags of ~6 rows of 128 B).  256-byte rows stay with the group kernel (22.8
-  // against 28.0 us on 16384 bags of ~40 rows).
+  if (a.pairs && pl->strategy != FWD_EB_STRATEGY_STREAM && pl->strategy != FWD_EB_STRATEGY_LITE)
+    pl->strategy = FWD_EB_STRATEGY_GROUP;
+  // AUTO: where a lane group per bag is the plan and the shape allows, one of the two leaner
+  // kernels runs it.  Measured on B200 (us per call, group / stream / lite): 16384 bags of ~40
+  // rows of 256 B, Zipf 23.0 / 28.0 / 22.7, uniform 29.4 / 34.4 / 28.4; 8192 bags of 0..64 rows of
+  // 512 B (max, 5 % padding) 33.8 / 32.5 / 30.9; 131072 dense bags of ~6 rows of 128 B 42.7 / 43.2 /
+  // 37.3; 65536 x 20 weighted fp32 rows of 512 B 77.9 / 63.9 / 70.0.  So: fixed-length bags stream,
+  // everything else goes lite.
+  // A table window that starts above row 0 says "one shard of a larger table": most indices
+  // will then miss the window, and both lean kernels spend a load slot on every index, kept or
+  // not, where the group kernel's survivor ring does not (142 against 80 us on a 1-in-8 window).
+  // Such calls stay with the group kernel unless the indices were compacted first.
   if (p->strategy == FWD_EB_STRATEGY_AUTO && pl->strategy == FWD_EB_STRATEGY_GROUP &&
-      stream_ok(p, pl) && a.lanes_log2 != 4)
-    pl->strategy = FWD_EB_STRATEGY_STREAM;
+      stream_ok(p, pl) && (a.pairs || p->row_lo == 0))
+    pl->strategy = p->fixed_len > 0 ? FWD_EB_STRATEGY_STREAM : FWD_EB_STRATEGY_LITE;
+  if (pl->strategy == FWD_EB_STRATEGY_LITE && !stream_ok(p, pl))
+    return fail(FWD_EB_EUNSUPPORTED, "LITE needs 16-byte aligned rows of 128..512 bytes, int32 "
+                "indices and fewer than 2^31 of them");
   if (pl->strategy == FWD_EB_STRATEGY_STREAM) {
     if (!stream_ok(p, pl)) {
       if (p->strategy == FWD_EB_STRATEGY_STREAM)
@@ -340,13 +350,16 @@ int plan_group(const fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* 
   q.strategy = FWD_EB_STRATEGY_GROUP;
   int rc = make_plan(&q, &pl);
   if (rc) return rc;
-  // the same choice AUTO makes between the two lane-group kernels
-  const bool want_stream = p->strategy == FWD_EB_STRATEGY_STREAM ||
-                           (p->strategy == FWD_EB_STRATEGY_AUTO && pl.a.lanes_log2 != 4);
+  // the same choice AUTO makes between the lane-group kernels
+  int want = 0;
+  if (p->strategy == FWD_EB_STRATEGY_STREAM) want = 1;
+  else if (p->strategy == FWD_EB_STRATEGY_LITE) want = 2;
+  else if (p->strategy == FWD_EB_STRATEGY_AUTO && (pl.a.pairs || p->row_lo == 0))
+    want = p->fixed_len > 0 ? 1 : 2;
   *stream = 0;
-  if (want_stream && stream_ok(&q, &pl)) {
-    pl.a.stream_k = choose_stream_k(&q, pl.a.lanes_log2);
-    *stream = 1;
+  if (want && stream_ok(&q, &pl)) {
+    if (want == 1) pl.a.stream_k = choose_stream_k(&q, pl.a.lanes_log2);
+    *stream = want;
   }
   *args = pl.a;
   *vec = pl.vec ? 1 : 0;
@@ -380,6 +393,55 @@ static cudaError_t launch_stream_ll(const Plan& pl, cudaStream_t st) {
       &cfg, eb_pool_stream_kernel<TW, VE, LL, OP, stream_u(LL), false>, a, none);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return le != cudaSuccess ? le : cudaGetLastError();
+}
+
+template <typename TW, int VE, int LL, int OP>
+static cudaError_t launch_lite_ll(const Plan& pl, cudaStream_t st) {
+  const PoolArgs& a = pl.a;
+  const long long blocks = ((a.num_bags << LL) + kCtaThreads - 1) / kCtaThreads;
+  if (blocks == 0) return cudaSuccess;
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3((unsigned)kCtaThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  PushArgs none;
+  memset(&none, 0, sizeof(none));
+  cudaError_t le = cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, OP, false>, a, none);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return le != cudaSuccess ? le : cudaGetLastError();
+}
+
+template <typename TW, int OP>
+static cudaError_t launch_lite_op(const Plan& pl, cudaStream_t st) {
+  constexpr int VE = 16 / (int)sizeof(TW);
+  switch (pl.a.lanes_log2) {
+    case 3:
+      return launch_lite_ll<TW, VE, 3, OP>(pl, st);
+    case 4:
+      return launch_lite_ll<TW, VE, 4, OP>(pl, st);
+    default:
+      return launch_lite_ll<TW, VE, 5, OP>(pl, st);
+  }
+}
+
+template <typename TW>
+static cudaError_t launch_lite(const Plan& pl, cudaStream_t st) {
+  switch (pl.op) {
+    case kOpSum:
+      return launch_lite_op<TW, kOpSum>(pl, st);
+    case kOpWeighted:
+      return launch_lite_op<TW, kOpWeighted>(pl, st);
+    case kOpMax:
+      return launch_lite_op<TW, kOpMax>(pl, st);
+    default:
+      return launch_lite_op<TW, kOpSquareSum>(pl, st);
+  }
 }
 
 template <typename TW, int OP>
@@ -551,7 +613,7 @@ int fwd_eb_pick_strategy(const fwd_eb_params* p) {
 size_t fwd_eb_workspace_size(const fwd_eb_params* p) {
   if (!p || validate(p) != 0 || p->mode == FWD_EB_MODE_GATHER) return 0;
   if (p->strategy == FWD_EB_STRATEGY_GROUP || p->strategy == FWD_EB_STRATEGY_CTA ||
-      p->strategy == FWD_EB_STRATEGY_STREAM)
+      p->strategy == FWD_EB_STRATEGY_STREAM || p->strategy == FWD_EB_STRATEGY_LITE)
     return 0;
   // AUTO: what SPLIT would need if AUTO could choose it for this shape.
   if (p->strategy == FWD_EB_STRATEGY_AUTO) {
@@ -576,6 +638,8 @@ int fwd_eb_forward(const fwd_eb_params* p, void* stream) {
     e = pl.table_f16 ? launch_maxpos<__half>(pl, st) : launch_maxpos<float>(pl, st);
   } else if (pl.strategy == FWD_EB_STRATEGY_STREAM) {
     e = pl.table_f16 ? launch_stream<__half>(pl, st) : launch_stream<float>(pl, st);
+  } else if (pl.strategy == FWD_EB_STRATEGY_LITE) {
+    e = pl.table_f16 ? launch_lite<__half>(pl, st) : launch_lite<float>(pl, st);
   } else {
     e = pl.table_f16 ? launch_shape<__half>(pl, st) : launch_shape<float>(pl, st);
   }
@@ -637,7 +701,13 @@ int fwd_eb_compact_window(const fwd_eb_params* p, int32_t* d_kept, float* d_kept
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, eb_window_compact_kernel, c);
+  cudaError_t e;
+  if (c.psw)
+    e = c.idx64 ? cudaLaunchKernelEx(&cfg, eb_window_compact_kernel<long long, true>, c)
+                : cudaLaunchKernelEx(&cfg, eb_window_compact_kernel<int, true>, c);
+  else
+    e = c.idx64 ? cudaLaunchKernelEx(&cfg, eb_window_compact_kernel<long long, false>, c)
+                : cudaLaunchKernelEx(&cfg, eb_window_compact_kernel<int, false>, c);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   if (e == cudaSuccess) e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "compaction kernel launch");

@@ -16,7 +16,8 @@ void count_launch();
 struct PoolArgs;
 // Validate `p` and fill the kernel arguments for the lane-group strategy (shared by the
 // single-GPU launcher and the row-shard push).  vec / cpl / tiles describe the chosen shape.
-// *stream = 1 when the streaming kernel (eb_stream.cuh) should run the shape; args->stream_k is then set.
+// *stream = 1 when the streaming kernel (eb_stream.cuh) should run the shape (args->stream_k is
+// then set), 2 for the lean kernel (eb_lite.cuh), 0 for eb_pool_group_kernel.
 int plan_group(const struct ::fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* tiles, int* stream);
 int sm_count();
 

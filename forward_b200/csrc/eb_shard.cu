@@ -14,6 +14,7 @@
 
 #include "eb_internal.h"
 #include "eb_kernels.cuh"
+#include "eb_lite.cuh"
 #include "eb_stream.cuh"
 #include "fwd_eb_shard.h"
 
@@ -333,6 +334,37 @@ static cudaError_t launch_push_stream(const PoolArgs& a, const PushArgs& x, bool
   return launch_push_stream_ll<TW, 5>(a, x, weighted, st);
 }
 
+// The lean kernel (eb_lite.cuh) with the push epilogue.
+template <typename TW, int LL>
+static cudaError_t launch_push_lite_ll(const PoolArgs& a, const PushArgs& x, bool weighted,
+                                       cudaStream_t st) {
+  constexpr int VE = 16 / (int)sizeof(TW);
+  const long long blocks = ((a.num_bags << LL) + kCtaThreads - 1) / kCtaThreads;
+  if (blocks == 0) return cudaSuccess;
+  if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)blocks);
+  cfg.blockDim = dim3((unsigned)kCtaThreads);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];  // see launch_pool in eb_api.cu
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = weighted
+      ? cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, kOpWeighted, true>, a, x)
+      : cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, kOpSum, true>, a, x);
+  count_launch();
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+template <typename TW>
+static cudaError_t launch_push_lite(const PoolArgs& a, const PushArgs& x, bool weighted, cudaStream_t st) {
+  if (a.lanes_log2 == 3) return launch_push_lite_ll<TW, 3>(a, x, weighted, st);
+  if (a.lanes_log2 == 4) return launch_push_lite_ll<TW, 4>(a, x, weighted, st);
+  return launch_push_lite_ll<TW, 5>(a, x, weighted, st);
+}
+
 static_assert(FWD_EB_MAX_PEERS == 16, "PushArgs (eb_stream.cuh) holds 16 peers");
 
 }  // namespace fwd_eb
@@ -363,8 +395,13 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
   fwd_eb_params q = *p;
   q.out = x->peer_slots[x->rank];
   q.out_dtype = x->wire_dtype;
-  if (x->layout == FWD_EB_LAYOUT_ROW_SHARD)
+  if (x->layout == FWD_EB_LAYOUT_ROW_SHARD) {
     q.flags |= FWD_EB_FLAG_MEAN_SINGLE_ROUNDING;  // a partial is not the final fp16 mean torch would round
+    // a row window filters most indices away unless they were compacted first: the group
+    // kernel's survivor ring is the one built for that (every rank, rank 0 included)
+    if (!(q.flags & FWD_EB_FLAG_OFFSET_PAIRS) && q.strategy == FWD_EB_STRATEGY_AUTO)
+      q.strategy = FWD_EB_STRATEGY_GROUP;
+  }
   q.out_stride = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (int64_t)x->num_tables * p->dim : 0;
   PoolArgs a;
   int vec = 0, cpl = 0, tiles = 0, stream_kernel = 0;
@@ -378,9 +415,12 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
   const bool weighted = p->per_sample_weights != nullptr;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t e;
-  if (stream_kernel) {
+  if (stream_kernel == 1) {
     e = p->table_dtype == FWD_EB_F16 ? launch_push_stream<__half>(a, px, weighted, st)
                                      : launch_push_stream<float>(a, px, weighted, st);
+  } else if (stream_kernel == 2) {
+    e = p->table_dtype == FWD_EB_F16 ? launch_push_lite<__half>(a, px, weighted, st)
+                                     : launch_push_lite<float>(a, px, weighted, st);
   } else {
     e = p->table_dtype == FWD_EB_F16
             ? launch_push_shape<__half>(a, px, vec != 0, cpl, tiles, weighted, st)
@@ -631,14 +671,15 @@ int fwd_eb_pipeline_step_rowshard_compact(fwd_eb_pipeline* pl, const fwd_eb_para
   q.indices = scratch->kept;
   q.index_dtype = FWD_EB_I32;
   q.offsets = scratch->bounds;
-  q.flags = (p->flags | FWD_EB_FLAG_OFFSET_PAIRS | FWD_EB_FLAG_PAIRS_RUN32);
+  q.flags = (p->flags | FWD_EB_FLAG_OFFSET_PAIRS | FWD_EB_FLAG_PAIRS_RUN16);
   q.fixed_len = 0;
   q.include_last_offset = 0;
   q.row_lo = 0;
   q.padding_idx = -1;
   q.mode = FWD_EB_MODE_SUM;
   if (p->per_sample_weights) q.per_sample_weights = scratch->kept_weights;
-  if (q.strategy != FWD_EB_STRATEGY_GROUP && q.strategy != FWD_EB_STRATEGY_STREAM)
+  if (q.strategy != FWD_EB_STRATEGY_GROUP && q.strategy != FWD_EB_STRATEGY_STREAM &&
+      q.strategy != FWD_EB_STRATEGY_LITE)
     q.strategy = FWD_EB_STRATEGY_AUTO;
   rc = fwd_eb_shard_push(&q, x, main);
   if (rc) return rc;   // the compaction has run: the step cannot be taken back

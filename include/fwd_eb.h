@@ -64,7 +64,10 @@ enum {
    * interrupt.  Rows of 128..512 bytes on the 16-byte vector path, int32 indices,
    * fewer than 2^31 of them; a call outside those limits returns
    * FWD_EB_EUNSUPPORTED when STREAM is asked for by name. */
-  FWD_EB_STRATEGY_STREAM = 4
+  FWD_EB_STRATEGY_STREAM = 4,
+  /* a lane group per bag with the least per-bag work: blocks of one index per lane, no
+   * survivor ring, passes of 8 row loads.  Same shapes as STREAM.  For short, dense bags. */
+  FWD_EB_STRATEGY_LITE = 5
 };
 
 /* Flags (fwd_eb_params.flags). */
@@ -84,10 +87,10 @@ enum {
    * This is what fwd_eb_compact_window writes.  fixed_len must be 0;
    * include_last_offset is ignored. */
   FWD_EB_FLAG_OFFSET_PAIRS = 8,
-  /* with OFFSET_PAIRS: inside every aligned run of 32 bags (bags 32k .. 32k+31) each
+  /* with OFFSET_PAIRS: inside every aligned run of 16 bags (bags 16k .. 16k+15) each
    * bag starts where the previous one ends, as fwd_eb_compact_window lays them
    * out; lets the STREAM strategy walk several bags as one index stream. */
-  FWD_EB_FLAG_PAIRS_RUN32 = 16
+  FWD_EB_FLAG_PAIRS_RUN16 = 16
 };
 
 /* Error codes. */
@@ -215,8 +218,8 @@ int fwd_eb_forward_static_scratch(const fwd_eb_params* p, void* stream);
  * num_indices / row_lo / num_rows / padding_idx / per_sample_weights (other fields
  * are ignored) and writes
  *   d_kept    int32 [num_indices]  the surviving indices as LOCAL row numbers
- *             (index - row_lo), in bag order; the survivors of bags 32k..32k+31 are
- *             back to back starting at the position where bag 32k starts in
+ *             (index - row_lo), in bag order; the survivors of bags 16k..16k+15 are
+ *             back to back starting at the position where bag 16k starts in
  *             p->indices (entries past a run's survivors are left untouched);
  *   d_kept_weights fp32 [num_indices], the survivors' weights (NULL unless
  *             p->per_sample_weights is set);
@@ -224,7 +227,7 @@ int fwd_eb_forward_static_scratch(const fwd_eb_params* p, void* stream);
  *   d_counts  int32 [num_bags] or NULL: non-padding entries of the WHOLE bag, inside
  *             the window or not (the divisor of a sharded mean).
  * Pool the result with indices = d_kept, index_dtype = FWD_EB_I32, offsets =
- * d_bounds, flags |= FWD_EB_FLAG_OFFSET_PAIRS | FWD_EB_FLAG_PAIRS_RUN32, row_lo = 0,
+ * d_bounds, flags |= FWD_EB_FLAG_OFFSET_PAIRS | FWD_EB_FLAG_PAIRS_RUN16, row_lo = 0,
  * padding_idx = -1 and per_sample_weights = d_kept_weights: every index then passes
  * the filter and the pooling kernels take their dense path.  num_indices must be
  * below 2^31.  Launches one kernel on `stream`; allocates nothing.

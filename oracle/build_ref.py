@@ -42,4 +42,9 @@ def main(ref_root: str) -> int:
 
 
 if __name__ == "__main__":
-    sys.exit(main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    sys.path.insert(0, os.path.dirname(HERE))
+    from oracle.refpath import reference_root
+    root = sys.argv[1] if len(sys.argv) > 1 else reference_root()
+    if not root:
+        sys.exit("no Forward reference tree found: pass its path or set FWD_REFERENCE_ROOT")
+    sys.exit(main(root))

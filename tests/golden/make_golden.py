@@ -132,7 +132,11 @@ def torch_cases() -> None:
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+    from oracle.refpath import reference_root
+    root = sys.argv[1] if len(sys.argv) > 1 else reference_root()
+    if not root:
+        sys.exit("no Forward reference tree found: pass its path or set FWD_REFERENCE_ROOT")
     reference_fixture(root)
     tf_reference_fixture(root)
     torch_cases()

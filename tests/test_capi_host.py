@@ -91,8 +91,15 @@ def test_null_params():
 def test_strategy_choice_and_workspace():
     lib = capi.lib()
     many_short = _params(num_bags=16384, num_indices=16384 * 40)
-    assert lib.fwd_eb_pick_strategy(C.byref(many_short)) == capi.STRATEGY_GROUP
+    # a lane group per bag; for rows of 128..512 bytes with int32 indices the lean kernel runs it
+    assert lib.fwd_eb_pick_strategy(C.byref(many_short)) == capi.STRATEGY_LITE
     assert lib.fwd_eb_workspace_size(C.byref(many_short)) == 0
+    shard = _params(num_bags=16384, num_indices=16384 * 40, row_lo=5000)    # a row window: survivor ring
+    assert lib.fwd_eb_pick_strategy(C.byref(shard)) == capi.STRATEGY_GROUP
+    wide = _params(num_bags=16384, num_indices=16384 * 40, dim=1024)        # rows beyond 512 bytes
+    assert lib.fwd_eb_pick_strategy(C.byref(wide)) == capi.STRATEGY_GROUP
+    fixed = _params(num_bags=1000, num_indices=20000, fixed_len=20, offsets=None)
+    assert lib.fwd_eb_pick_strategy(C.byref(fixed)) == capi.STRATEGY_STREAM
     some_long = _params(num_bags=1000, num_indices=1000 * 500)
     assert lib.fwd_eb_pick_strategy(C.byref(some_long)) == capi.STRATEGY_CTA
     few_huge = _params(num_bags=4, num_indices=4 * 100_000)

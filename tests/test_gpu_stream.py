@@ -1,4 +1,4 @@
-"""The streaming lane-group kernel (FWD_EB_STRATEGY_STREAM) and the window compaction, against
+"""The streaming and the lean lane-group kernels (FWD_EB_STRATEGY_STREAM / _LITE) and the window compaction, against
 the CPU oracle: bit for bit in every mode (the kernel adds rows in bag order, like the oracle)."""
 import numpy as np
 import pytest
@@ -49,16 +49,17 @@ def test_stream_equals_oracle_all_modes(dt, dim):
                           (capi.MODE_SQUARE_SUM, table)):
             for row_lo, nrows in ((0, rows), (500, 2500)):
                 t = _cuda(tab[row_lo:row_lo + nrows])
-                got = capi.embedding_bag(t, i, o, mode=mode, padding_idx=7, row_lo=row_lo,
-                                         strategy=capi.STRATEGY_STREAM)
                 exp = O.pool(tab[row_lo:row_lo + nrows], bags.indices, bags.offsets, mode=mode,
                              padding_idx=7, row_lo=row_lo)
-                assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp)), (nb, maxlen, mode, row_lo)
-        got = capi.embedding_bag(_cuda(table), i, o, mode=capi.MODE_SUM, per_sample_weights=_cuda(w_np),
-                                 strategy=capi.STRATEGY_STREAM, out_dtype=torch.float32)
+                for strat in (capi.STRATEGY_STREAM, capi.STRATEGY_LITE):
+                    got = capi.embedding_bag(t, i, o, mode=mode, padding_idx=7, row_lo=row_lo, strategy=strat)
+                    assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp)), (nb, maxlen, mode, row_lo, strat)
         exp = O.pool(table, bags.indices, bags.offsets, mode=O.MODE_SUM, per_sample_weights=w_np,
                      out_dtype=np.float32)
-        assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp))
+        for strat in (capi.STRATEGY_STREAM, capi.STRATEGY_LITE):
+            got = capi.embedding_bag(_cuda(table), i, o, mode=capi.MODE_SUM, per_sample_weights=_cuda(w_np),
+                                     strategy=strat, out_dtype=torch.float32)
+            assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp)), strat
 
 
 def test_stream_fixed_length_and_include_last_offset():
@@ -68,16 +69,17 @@ def test_stream_fixed_length_and_include_last_offset():
     idx = rng.integers(0, rows, (nb, L)).astype(np.int32)
     w = rng.random(nb * L).astype(np.float32)
     t = _cuda(table)
-    got = capi.embedding_bag(t, _cuda(idx), None, fixed_len=L, per_sample_weights=_cuda(w),
-                             strategy=capi.STRATEGY_STREAM)
     exp = O.pool(table, idx, fixed_len=L, per_sample_weights=w)
-    assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp))
+    for strat in (capi.STRATEGY_STREAM, capi.STRATEGY_LITE, capi.STRATEGY_AUTO):
+        got = capi.embedding_bag(t, _cuda(idx), None, fixed_len=L, per_sample_weights=_cuda(w), strategy=strat)
+        assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp)), strat
     bags = _batch(rng, rows, 300, 30, 0.2)
     off = np.append(bags.offsets, bags.num_indices).astype(np.int32)
-    got = capi.embedding_bag(t, _cuda(bags.indices), _cuda(off), mode=capi.MODE_MEAN,
-                             include_last_offset=True, strategy=capi.STRATEGY_STREAM)
     exp = O.pool(table, bags.indices, off, mode=O.MODE_MEAN, include_last_offset=True)
-    assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp))
+    for strat in (capi.STRATEGY_STREAM, capi.STRATEGY_LITE):
+        got = capi.embedding_bag(t, _cuda(bags.indices), _cuda(off), mode=capi.MODE_MEAN,
+                                 include_last_offset=True, strategy=strat)
+        assert np.array_equal(_bits(got.cpu().numpy()), _bits(exp)), strat
 
 
 def test_stream_refuses_shapes_outside_its_limits_and_auto_falls_back():
@@ -101,9 +103,10 @@ def test_stream_survives_malformed_offsets():
     table = _cuda(rng.standard_normal((500, 64)).astype(np.float32))
     idx = _cuda(rng.integers(0, 500, 400).astype(np.int32))
     off = _cuda(np.array([0, 50, 20, 900, 100, -5, 300, 399], dtype=np.int32))
-    out = capi.embedding_bag(table, idx, off, strategy=capi.STRATEGY_STREAM)
-    torch.cuda.synchronize()
-    assert out.shape == (8, 64)
+    for strat in (capi.STRATEGY_STREAM, capi.STRATEGY_LITE):
+        out = capi.embedding_bag(table, idx, off, strategy=strat)
+        torch.cuda.synchronize()
+        assert out.shape == (8, 64)
 
 
 @pytest.mark.parametrize("idx64", [False, True])
@@ -114,7 +117,7 @@ def test_window_compaction_then_pooling_equals_filtering_inside_the_pool(idx64, 
     table = rng.standard_normal((rows, dim)).astype(np.float16)
     lo, n = 3000, 2000                                           # this "rank" holds rows [3000, 5000)
     t = _cuda(table[lo:lo + n])
-    for nb, maxlen in ((1, 10), (31, 40), (32, 40), (33, 40), (1000, 100), (257, 3)):
+    for nb, maxlen in ((1, 10), (15, 40), (16, 40), (17, 40), (33, 40), (1000, 100), (257, 3)):
         bags = _batch(rng, rows, nb, maxlen, 0.2)
         idt = np.int64 if idx64 else np.int32
         i, o = _cuda(bags.indices.astype(idt)), _cuda(bags.offsets.astype(idt))
@@ -137,11 +140,11 @@ def test_window_compaction_then_pooling_equals_filtering_inside_the_pool(idx64, 
             sur = live[(live >= lo) & (live < lo + n)] - lo
             assert ch[b] == live.size
             assert np.array_equal(kh[bh[b, 0]:bh[b, 1]], sur)
-            if b % 32:
+            if b % 16:
                 assert bh[b, 0] == bh[b - 1, 1]                  # sub-bags of a run are back to back
         exp = O.pool(table[lo:lo + n], bags.indices, bags.offsets, mode=m, padding_idx=7, row_lo=lo,
                      per_sample_weights=w_np, out_dtype=np.float32)
-        for strat in (capi.STRATEGY_GROUP, capi.STRATEGY_STREAM, capi.STRATEGY_AUTO):
+        for strat in (capi.STRATEGY_GROUP, capi.STRATEGY_STREAM, capi.STRATEGY_LITE, capi.STRATEGY_AUTO):
             out.fill_(float("nan"))
             q = capi.make_compacted_params(t, kept, bounds, out=out, mode=m, kept_weights=kept_w,
                                            strategy=strat)
@@ -152,8 +155,8 @@ def test_window_compaction_then_pooling_equals_filtering_inside_the_pool(idx64, 
 
 def test_config3_and_config5_shapes_through_the_streaming_kernel():
     """512-byte rows, max with padding (config 3's shape, fewer rows) and 128-byte rows, short
-    dense bags (what config 5 pools after compaction): AUTO must pick the streaming kernel and
-    agree with the lane-group kernel bit for bit."""
+    dense bags (what config 5 pools after compaction): AUTO must pick the lean kernel and agree
+    with the lane-group kernel bit for bit."""
     import ctypes as C
     rng = np.random.default_rng(3)
     t3 = _cuda((rng.standard_normal((100_000, 256)) * 0.1).astype(np.float16))
@@ -161,7 +164,7 @@ def test_config3_and_config5_shapes_through_the_streaming_kernel():
     i, o = _cuda(bags.indices), _cuda(bags.offsets)
     out = torch.empty((8192, 256), dtype=torch.float16, device=DEV)
     p = capi.make_params(t3, i, o, out=out, mode=capi.MODE_MAX, padding_idx=0)
-    assert capi.lib().fwd_eb_pick_strategy(C.byref(p)) == capi.STRATEGY_STREAM
+    assert capi.lib().fwd_eb_pick_strategy(C.byref(p)) == capi.STRATEGY_LITE
     a = capi.embedding_bag(t3, i, o, mode=capi.MODE_MAX, padding_idx=0)
     b = capi.embedding_bag(t3, i, o, mode=capi.MODE_MAX, padding_idx=0, strategy=capi.STRATEGY_GROUP)
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))

@@ -16,7 +16,9 @@ from oracle import eb_oracle as O
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIBDIR = os.path.join(ROOT, "forward_b200", "lib")
-REF_FIXTURE = "/root/reference/data/tf_unit_tests/embedding_bag.pb"
+from oracle.refpath import reference_root  # noqa: E402
+
+REF_FIXTURE = os.path.join(reference_root() or "", "data", "tf_unit_tests", "embedding_bag.pb")
 
 
 @pytest.fixture(scope="module")

@@ -13,7 +13,9 @@ from forward_b200 import capi  # noqa: E402
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LIB = os.path.join(ROOT, "forward_b200", "lib", "libfwd_eb_torch.so")
-REF_FIXTURE = "/root/reference/data/torch_unit_tests/nodes/embedding_bag.pth"
+from oracle.refpath import reference_root  # noqa: E402
+
+REF_FIXTURE = os.path.join(reference_root() or "", "data", "torch_unit_tests", "nodes", "embedding_bag.pth")
 
 
 @pytest.fixture(scope="module")
