@@ -851,6 +851,17 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
     clocks = sampler.stop() if sampler else None
     launches = (capi.lib().fwd_eb_launch_count() - launches0) // regions
     iso_us = isolated_launch_us(wl)
+    host_us = None
+    if multi:
+        # what the host spends queueing one step (no synchronisation inside the loop): a step
+        # cannot run faster than this
+        barrier()
+        t0 = time.perf_counter()
+        for k in range(100):
+            wl.step(k)
+        host_us = (time.perf_counter() - t0) * 1e4
+        wl.bag.sync_result()
+        torch.cuda.synchronize()
     lookups = total_lookups(wl, steps, dev)
     exchange = None
     if multi:
@@ -874,7 +885,8 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
                     "nvlink_floor_us_at_770GBs": egress / 770e9 * 1e6,
                     # egress over the part of a step the exchange adds, against 900 GB/s per direction
                     "nvlink_frac": egress / (extra_us * 1e-6) / 900e9,
-                    "nvlink_frac_of_step": egress / (step_us * 1e-6) / 900e9}
+                    "nvlink_frac_of_step": egress / (step_us * 1e-6) / 900e9,
+                    "host_us_per_step_queued": host_us}
     value = lookups / (total_ms * 1e-3)
 
     peak, peak_kind = measured_peak()

@@ -139,6 +139,7 @@ eb_pool_lite_kernel(const PoolArgs a, const PushArgs x) {
     if (owner >= x.world) owner = x.world - 1;
     char* base = x.peer_slots[owner] + x.col_offset * (a.out_f16 ? 2 : 4);
     store_row<VE, 1, true>(a, base, x.row_base + (bag - owner * x.bags_per_rank), 0, v, live);
+    push_grid_done(x);
   } else {
     store_row<VE, 1, true>(a, a.out, bag, 0, v, live);
   }

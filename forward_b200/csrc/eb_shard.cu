@@ -77,6 +77,7 @@ eb_pool_push_kernel(const PoolArgs a, const PushArgs x) {
   // this rank's slot (row shards) or this table's column block (table-wise) at the owner
   char* base = x.peer_slots[owner] + x.col_offset * (a.out_f16 ? 2 : 4);
   store_row<VE, CPL, true>(a, base, x.row_base + local_bag, chunk0, s.v, live);
+  push_grid_done(x);
 }
 
 // Fold of a sharded MAX: slot r holds, per column of each bag, {value, position of the index
@@ -119,8 +120,8 @@ __global__ void eb_shard_signal_kernel(const FlagSet f, int world, int rank, uin
 
 // Bounded wait for all flags; nothing else (table-wise layout needs no folding).
 __global__ void eb_shard_wait_kernel(const FlagSet f, int rank, int world, uint32_t epoch,
-                                     int* status, long long max_spins) {
-  if (threadIdx.x == 0) raise_flags(f.peer_flags, world, rank, epoch);
+                                     int* status, long long max_spins, int raise) {
+  if (raise && threadIdx.x == 0) raise_flags(f.peer_flags, world, rank, epoch);
   const uint32_t* flags = f.peer_flags[rank];
   if (threadIdx.x < world) {
     long long spins = 0;
@@ -219,6 +220,8 @@ static int check_exchange(const fwd_eb_shard_exchange* x) {
   if (x->wire_dtype == FWD_EB_F32_POS && x->layout != FWD_EB_LAYOUT_ROW_SHARD)
     return fail(FWD_EB_EINVAL, "the value + position wire type is for row shards");
   if (x->epoch == 0) return fail(FWD_EB_EINVAL, "epoch starts at 1");
+  if (x->raise_from_push && !x->tickets)
+    return fail(FWD_EB_EINVAL, "raise_from_push needs the ticket words");
   if (!x->status) return fail(FWD_EB_EINVAL, "status word is null");
   for (int r = 0; r < x->world; ++r) {
     if (!x->peer_slots[r] || !x->peer_flags[r])
@@ -255,6 +258,7 @@ static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
   out->world = x->world;
   out->rank = x->rank;
   out->epoch = x->epoch;
+  out->ticket = (x->raise_from_push && x->tickets) ? x->tickets + (x->epoch % FWD_EB_SHARD_BUFFERS) : nullptr;
 }
 
 static FlagSet flag_set(const fwd_eb_shard_exchange* x) {
@@ -443,7 +447,7 @@ int fwd_eb_shard_wait(const fwd_eb_shard_exchange* x, int32_t dim, void** d_resu
   if (dim <= 0) return fail(FWD_EB_EINVAL, "dim must be positive");
   const long long spins = x->max_spins > 0 ? x->max_spins : (1LL << 22);
   eb_shard_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      flag_set(x), x->rank, x->world, x->epoch, x->status, spins);
+      flag_set(x), x->rank, x->world, x->epoch, x->status, spins, x->raise_from_push ? 0 : 1);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "wait kernel launch");
@@ -488,7 +492,8 @@ int fwd_eb_shard_combine_div(const fwd_eb_shard_exchange* x, int32_t dim, int64_
     long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
     if (blocks > sm_count() * 8) blocks = sm_count() * 8;
     if (blocks < 1) blocks = 1;
-    eb_shard_wait_kernel<<<1, 32, 0, st>>>(flags, x->rank, x->world, x->epoch, x->status, spins);
+    eb_shard_wait_kernel<<<1, 32, 0, st>>>(flags, x->rank, x->world, x->epoch, x->status, spins,
+                                         x->raise_from_push ? 0 : 1);
     count_launch();
     if (out16) {
       eb_shard_combine_max_kernel<__half><<<(unsigned)blocks, kCtaThreads, 0, st>>>(
@@ -516,7 +521,8 @@ int fwd_eb_shard_combine_div(const fwd_eb_shard_exchange* x, int32_t dim, int64_
   const unsigned g = (unsigned)blocks;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // flag exchange first, in a one-warp kernel of its own
-  eb_shard_wait_kernel<<<1, 32, 0, st>>>(flags, x->rank, x->world, x->epoch, x->status, spins);
+  eb_shard_wait_kernel<<<1, 32, 0, st>>>(flags, x->rank, x->world, x->epoch, x->status, spins,
+                                         x->raise_from_push ? 0 : 1);
   count_launch();
 #define FWD_EB_COMBINE(TP, TO, V)                                                                \
   eb_shard_combine_kernel<TP, TO, V><<<g, kCtaThreads, 0, st>>>(                                 \
@@ -567,14 +573,24 @@ static int pipeline_begin(fwd_eb_pipeline* pl, fwd_eb_shard_exchange* x, cudaStr
     return fail(FWD_EB_ETOOBIG, "this pipeline has run 2^32 steps: drain it on every rank and create a new one");
   pl->epoch += 1;
   x->epoch = pl->epoch;
-  if (pl->epoch > 2) {
-    // exchange of step e-2 done => every peer has finished with the part step e writes
+  const uint32_t every = x->tickets ? FWD_EB_PIPELINE_WAIT_EVERY_TICKETS : FWD_EB_PIPELINE_WAIT_EVERY;
+  static_assert(FWD_EB_PIPELINE_WAIT_EVERY + 2 <= FWD_EB_SHARD_BUFFERS, "k + 2 parts");
+  static_assert(2 * FWD_EB_PIPELINE_WAIT_EVERY_TICKETS + 2 <= FWD_EB_SHARD_BUFFERS, "2k + 2 parts");
+  if (pl->epoch > 2 && pl->epoch % every == 0) {
+    // this rank has folded step e-2, hence seen every rank's flag e-2; see FWD_EB_SHARD_BUFFERS
+    // for why looking back this rarely is enough with eight buffer parts
     cudaError_t e = cudaStreamWaitEvent(main, pl->done[(pl->epoch - 2) % FWD_EB_SHARD_BUFFERS], 0);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent (main)");
+    if (e != cudaSuccess) {
+      pl->epoch -= 1;
+      return cuda_fail(e, "cudaStreamWaitEvent (main)");
+    }
   }
   return 0;
 }
 
+// The side stream must not run ahead of the main stream's work of this step (staged exchange:
+// the copies read what the pooling wrote).  Steps whose pooling grid raises the flag itself need
+// no such hand-over: their side-stream kernel waits for flags, this rank's own included.
 static int pipeline_handover(fwd_eb_pipeline* pl, cudaStream_t main) {
   const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
   cudaError_t e = cudaEventRecord(pl->pushed[k], main);
@@ -627,10 +643,13 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   int rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
+  x->raise_from_push = x->tickets ? 1 : 0;
   rc = fwd_eb_shard_push(p, x, main);   // validates before it launches
   if (rc) return pipeline_abort(pl, rc);
-  rc = pipeline_handover(pl, main);
-  if (rc) return rc;
+  if (!x->raise_from_push) {
+    rc = pipeline_handover(pl, main);
+    if (rc) return rc;
+  }
   const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
   rc = fwd_eb_shard_combine(x, p->dim, num_bags_owned, d_out[k], out_dtype, pl->side);
   if (rc) return rc;
@@ -681,10 +700,13 @@ int fwd_eb_pipeline_step_rowshard_compact(fwd_eb_pipeline* pl, const fwd_eb_para
   if (q.strategy != FWD_EB_STRATEGY_GROUP && q.strategy != FWD_EB_STRATEGY_STREAM &&
       q.strategy != FWD_EB_STRATEGY_LITE)
     q.strategy = FWD_EB_STRATEGY_AUTO;
+  x->raise_from_push = x->tickets ? 1 : 0;
   rc = fwd_eb_shard_push(&q, x, main);
   if (rc) return rc;   // the compaction has run: the step cannot be taken back
-  rc = pipeline_handover(pl, main);
-  if (rc) return rc;
+  if (!x->raise_from_push) {
+    rc = pipeline_handover(pl, main);
+    if (rc) return rc;
+  }
   // 3. flags, bounded wait, fold (and the mean's division) on the side stream
   rc = fwd_eb_shard_combine_div(x, p->dim, num_bags_owned,
                                 mean ? counts + (int64_t)x->rank * x->bags_per_rank : nullptr, d_out[k],
@@ -740,6 +762,7 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
+  x->raise_from_push = 0;   // the flag follows the copies: raised by the kernel behind them
   rc = check_exchange(x);
   if (rc) return pipeline_abort(pl, rc);
   const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
@@ -776,13 +799,18 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   int rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
+  const bool from_push = x->tickets != nullptr && count > 0;
   for (int i = 0; i < count; ++i) {
     x->table_index = table_index[i];
+    x->raise_from_push = (from_push && i == count - 1) ? 1 : 0;   // the step's last grid raises the flag
     rc = fwd_eb_shard_push(params[i], x, main);
     if (rc) return i == 0 ? pipeline_abort(pl, rc) : rc;   // nothing launched yet: take the number back
   }
-  rc = pipeline_handover(pl, main);
-  if (rc) return rc;
+  x->raise_from_push = from_push ? 1 : 0;
+  if (!from_push) {
+    rc = pipeline_handover(pl, main);
+    if (rc) return rc;
+  }
   rc = fwd_eb_shard_wait(x, dim, d_result, pl->side);
   if (rc) return rc;
   cudaError_t e = cudaEventRecord(pl->done[pl->epoch % FWD_EB_SHARD_BUFFERS], pl->side);

@@ -60,7 +60,32 @@ struct PushArgs {
   int rank;
   int small;             // bag numbers and bags_per_rank fit 32 bits
   uint32_t epoch;
+  unsigned* ticket;      // non-null: the grid's last CTA raises this rank's flag on every peer
 };
+
+// End of a pooling grid that pushes its rows to peers: the CTA that finishes last publishes
+// `epoch` in this rank's flag word on every peer.  Every CTA makes its own stores visible system
+// wide (fence) before it takes a ticket; the CTA that draws the last ticket therefore knows that
+// all stores of the grid have been performed, fences again and writes the flags with release
+// semantics.  It also clears the ticket word for the next grid that uses it (grids that share a
+// word never overlap: a dependent grid's CTAs wait in griddepcontrol.wait until this grid has
+// completed).  Called by every thread of the CTA.
+__device__ __forceinline__ void push_grid_done(const PushArgs& x) {
+  if (!x.ticket) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned total = gridDim.x * gridDim.y * gridDim.z;
+    const unsigned t = atomicAdd(x.ticket, 1u);
+    if (t == total - 1u) {
+      *x.ticket = 0u;
+      __threadfence_system();
+      for (int r = 0; r < x.world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(x.peer_flags[r] + x.rank), "r"(x.epoch)
+                     : "memory");
+    }
+  }
+}
 
 template <typename TW, int VE, int LL, int OP, int U, bool PUSH>
 __global__ void __launch_bounds__(kCtaThreads, FWD_EB_STREAM_MIN_CTAS)
@@ -248,6 +273,7 @@ eb_pool_stream_kernel(const PoolArgs a, const PushArgs x) {
       }
     }
   }
+  if (PUSH) push_grid_done(x);
 }
 
 }  // namespace fwd_eb

@@ -28,6 +28,7 @@ import ctypes as C
 from . import capi
 
 MAX_PEERS = 16
+SHARD_BUFFERS = 8          # FWD_EB_SHARD_BUFFERS: parts of a receive buffer, results in rotation
 LAYOUT_ROW_SHARD, LAYOUT_TABLE_WISE = 0, 1
 SHARD_TIMEOUT = 1
 
@@ -85,7 +86,7 @@ class ShardExchange(C.Structure):
         ("peer_slots", C.c_void_p * MAX_PEERS), ("peer_flags", C.c_void_p * MAX_PEERS),
         ("status", C.c_void_p), ("max_spins", C.c_int64),
         ("layout", C.c_int32), ("num_tables", C.c_int32), ("table_index", C.c_int32),
-        ("reserved", C.c_int32),
+        ("raise_from_push", C.c_int32), ("tickets", C.c_void_p),
     ]
 
 
@@ -202,7 +203,7 @@ class PeerBuffers:
 
 
 def make_exchange(buffers: PeerBuffers, rank: int, per_rank_bags: int, wire_dtype: int,
-                  status, *, layout=LAYOUT_ROW_SHARD, num_tables=0, max_spins=0) -> ShardExchange:
+                  status, *, layout=LAYOUT_ROW_SHARD, num_tables=0, max_spins=0, tickets=None) -> ShardExchange:
     x = ShardExchange()
     x.world, x.rank = buffers.world, rank
     x.bags_per_rank = per_rank_bags
@@ -215,6 +216,8 @@ def make_exchange(buffers: PeerBuffers, rank: int, per_rank_bags: int, wire_dtyp
     x.max_spins = max_spins
     x.layout = layout
     x.num_tables = num_tables
+    # zeroed device words of this rank: with them the pipeline lets the pooling grid raise the flag
+    x.tickets = tickets.data_ptr() if tickets is not None else None
     return x
 
 
@@ -225,7 +228,7 @@ class RowShardedBag:
 
     def __init__(self, table_local, row_lo: int, *, mode: int, max_bags: int, group=None,
                  exchange: str = "push", wire_dtype: int = capi.F32, padding_idx: int = -1,
-                 out_dtype=None, max_indices: int = 0):
+                 out_dtype=None, max_indices: int = 0, flag_from_pool: bool = False):
         import torch
         import torch.distributed as dist
         if mode == capi.MODE_MAX:
@@ -255,9 +258,9 @@ class RowShardedBag:
             raise ValueError("exchange='compact' needs max_indices (its scratch is sized up front)")
         if self.piped:
             # The fold runs on the pipeline's side stream so that the next call's pooling does
-            # not queue behind this call's flag exchange; results rotate through three buffers.
-            self.outs = [self.out, torch.empty_like(self.out), torch.empty_like(self.out)]
-            self._out_ptrs = (C.c_void_p * 3)(*[o.data_ptr() for o in self.outs])
+            # not queue behind this call's flag exchange; results rotate through SHARD_BUFFERS buffers.
+            self.outs = [self.out] + [torch.empty_like(self.out) for _ in range(SHARD_BUFFERS - 1)]
+            self._out_ptrs = (C.c_void_p * SHARD_BUFFERS)(*[o.data_ptr() for o in self.outs])
             self._pl = C.c_void_p()
             capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
             self.side = torch.cuda.ExternalStream(_lib().fwd_eb_pipeline_side_stream(self._pl), device=dev)
@@ -265,14 +268,18 @@ class RowShardedBag:
             nbytes = _lib().fwd_eb_shard_slots_bytes(self.world, self.per, self.dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
-            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status)
+            # flag_from_pool: the pooling grid raises the flag itself (ticket counter); measured
+            # slower than the kernel behind the grid raising it, so off unless asked for
+            self.tickets = torch.zeros(SHARD_BUFFERS, dtype=torch.int32, device=dev) if flag_from_pool else None
+            self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status,
+                                   tickets=self.tickets)
             if exchange == "compact":
                 # scratch of the window compaction: kept indices, sub-bag bounds, and for a mean
-                # the bags' full counts (three parts: a fold reads them beside the next step)
+                # the bags' full counts (one part per step in flight: a fold reads them beside later steps)
                 nb_all = self.per * self.world
                 self._kept = torch.empty(max_indices, dtype=torch.int32, device=dev)
                 self._bounds = torch.empty((nb_all, 2), dtype=torch.int32, device=dev)
-                self._counts = torch.zeros((3, nb_all), dtype=torch.int32, device=dev)
+                self._counts = torch.zeros((SHARD_BUFFERS, nb_all), dtype=torch.int32, device=dev)
                 self._scratch = CompactScratch(self._kept.data_ptr(), None, self._bounds.data_ptr(),
                                                self._counts.data_ptr())
                 self.max_indices = max_indices
@@ -282,8 +289,8 @@ class RowShardedBag:
                 wire = torch.float16 if wire_dtype == capi.F16 else torch.float32
                 cols = self.dim * (2 if wire_dtype == capi.F32_POS else 1)   # pairs: 8 bytes a column
                 self.stages = [torch.empty((self.per * self.world, cols), dtype=wire, device=dev)
-                               for _ in range(3)]
-                self._stage_ptrs = (C.c_void_p * 3)(*[t.data_ptr() for t in self.stages])
+                               for _ in range(SHARD_BUFFERS)]
+                self._stage_ptrs = (C.c_void_p * SHARD_BUFFERS)(*[t.data_ptr() for t in self.stages])
         elif exchange in ("nccl", "a2a"):
             self.partial = torch.empty((self.per * self.world, self.dim), dtype=torch.float32,
                                        device=dev)
@@ -312,8 +319,8 @@ class RowShardedBag:
         return (self.params(indices, offsets, out), mine, num_bags)
 
     def forward(self, indices, offsets=None, pool_events=None):
-        """Returns this rank's [bags_owned, dim] slice of the pooled output (a buffer reused three
-        calls later).  `indices` may be a prepare()d argument block.  `pool_events` = (start, end)
+        """Returns this rank's [bags_owned, dim] slice of the pooled output (a buffer reused
+        SHARD_BUFFERS calls later).  `indices` may be a prepare()d argument block.  `pool_events` = (start, end)
         CUDA events recorded around the pooling launch."""
         import torch
         import torch.distributed as dist
@@ -418,7 +425,7 @@ class TableWiseBags:
 
     def __init__(self, local_tables: dict, owner: list[int], *, dim: int, max_bags: int, group=None,
                  exchange: str = "push", wire_dtype: int = capi.F32, mode: int = capi.MODE_SUM,
-                 fixed_len: int = 0, padding_idx: int = -1):
+                 fixed_len: int = 0, padding_idx: int = -1, flag_from_pool: bool = False):
         import torch
         import torch.distributed as dist
         self.group = group
@@ -446,8 +453,10 @@ class TableWiseBags:
             nbytes = _lib().fwd_eb_shard_tablewise_bytes(self.per, self.num_tables, dim, wire_dtype)
             self.buffers = PeerBuffers(nbytes, self.world, self.rank, group=group)
             self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.tickets = torch.zeros(SHARD_BUFFERS, dtype=torch.int32, device=dev) if flag_from_pool else None
             self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status,
-                                   layout=LAYOUT_TABLE_WISE, num_tables=self.num_tables)
+                                   layout=LAYOUT_TABLE_WISE, num_tables=self.num_tables,
+                                   tickets=self.tickets)
         else:
             tl = max(1, len(self.mine))
             self.send = torch.zeros((self.per * self.world, tl, dim), dtype=torch.float32, device=dev)

@@ -12,8 +12,8 @@
  *
  * Exchange layout.  Bags are owned in contiguous runs of `bags_per_rank`: rank o
  * owns bags [o*bags_per_rank, (o+1)*bags_per_rank).  Each rank exposes a receive
- * buffer of 3 x G x bags_per_rank x dim elements (three parts used in turn, call
- * number modulo 3, one slot per source rank) and G flag words, all mapped into every
+ * buffer of FWD_EB_SHARD_BUFFERS x G x bags_per_rank x dim elements (parts used in turn, call
+ * number modulo FWD_EB_SHARD_BUFFERS, one slot per source rank) and G flag words, all mapped into every
  * peer (CUDA IPC below, or any other peer mapping).  fwd_eb_shard_push pools, and
  * writes bag b's partial row straight into slot [part][rank] of b's owner with
  * plain peer stores.  fwd_eb_shard_combine, queued behind it on the same stream,
@@ -36,20 +36,32 @@ extern "C" {
 #endif
 
 #define FWD_EB_MAX_PEERS 16
-/* Parts of a receive buffer.  A rank raises flag f only after it has consumed the result of
- * call f-1, and a rank starts call e only after it has seen every peer's flag e-2; with three
- * parts the part call e writes (last used by call e-3) is therefore free, and the pooling of
- * call e never has to wait for the flag exchange of call e-1, which can run beside it. */
-#define FWD_EB_SHARD_BUFFERS 3
+/* Parts of a receive buffer, used in turn (call number modulo FWD_EB_SHARD_BUFFERS), and how
+ * often the pipeline makes a rank look back.  Only on every k-th call does the main stream wait
+ * until this rank has folded call e-2 (which implies it has seen every rank's flag e-2); the
+ * calls in between are queued without a wait on another stream.  Waiting on every call cost
+ * 4 us of a 29 us step on two B200s.
+ *   - Flag raised by the kernel behind the pooling grid, after this rank has folded the call
+ *     before (the default): seeing flag f of rank A proves A has folded f-1; a rank B writing
+ *     call g has seen flags >= g-k-1, so the part it overwrites must be older than g-k-2:
+ *     k + 2 parts.  k = FWD_EB_PIPELINE_WAIT_EVERY = 6.
+ *   - Flag raised by the pooling grid itself (x->tickets set): a flag no longer proves a fold;
+ *     seeing flag f of A only proves A had folded f-k-1, hence 2k + 2 parts.
+ *     k = FWD_EB_PIPELINE_WAIT_EVERY_TICKETS = 3.
+ * The CPU model of these rules (tests/test_exchange_protocol.py) finds no overwrite of an
+ * unfolded part with them and does find one with fewer parts. */
+#define FWD_EB_PIPELINE_WAIT_EVERY 6
+#define FWD_EB_PIPELINE_WAIT_EVERY_TICKETS 3
+#define FWD_EB_SHARD_BUFFERS 8
 #define FWD_EB_SHARD_TIMEOUT 1
 #define FWD_EB_IPC_HANDLE_BYTES 64
 
 /* Receive-buffer layouts (fwd_eb_shard_exchange.layout). */
 enum {
-  /* Row shards of one table: [3 parts][G source ranks][bags_per_rank][dim];
+  /* Row shards of one table: [parts][G source ranks][bags_per_rank][dim];
    * the owner folds the G slots with fwd_eb_shard_combine. */
   FWD_EB_LAYOUT_ROW_SHARD = 0,
-  /* Whole tables placed on different ranks: [3 parts][bags_per_rank][num_tables][dim];
+  /* Whole tables placed on different ranks: [parts][bags_per_rank][num_tables][dim];
    * the rank holding table t pools the whole batch and writes column block
    * `table_index` of every owner's buffer.  Nothing is folded: after
    * fwd_eb_shard_wait that part of the buffer IS the result (the all-to-all of pooled
@@ -63,7 +75,7 @@ typedef struct fwd_eb_shard_exchange {
   int64_t bags_per_rank;      /* owner of bag b is b / bags_per_rank */
   int32_t wire_dtype;         /* FWD_EB_F32, or FWD_EB_F16 to halve the NVLink bytes; a sharded
                                  MAX uses FWD_EB_F32_POS ({value, position}, 8 bytes a column) */
-  uint32_t epoch;             /* call number, starting at 1; epoch % 3 picks the buffer part */
+  uint32_t epoch;             /* call number, starting at 1; epoch % FWD_EB_SHARD_BUFFERS picks the part */
   void* peer_slots[FWD_EB_MAX_PEERS];      /* rank r's receive buffer as mapped here */
   uint32_t* peer_flags[FWD_EB_MAX_PEERS];  /* rank r's G flag words as mapped here */
   int32_t* status;            /* one device word of this rank; 0 = fine */
@@ -71,7 +83,14 @@ typedef struct fwd_eb_shard_exchange {
   int32_t layout;             /* FWD_EB_LAYOUT_* */
   int32_t num_tables;         /* TABLE_WISE: tables in the whole model */
   int32_t table_index;        /* TABLE_WISE: which of them this call pools */
-  int32_t reserved;
+  /* 1: fwd_eb_shard_push raises this rank's flag itself when its grid completes (the last CTA
+   * to finish, found with a ticket counter, publishes `epoch` after a system-scope fence), and
+   * the wait / fold that follows only waits.  0: the flag is raised by the kernel that follows
+   * the push on the stream (fwd_eb_shard_combine / _wait / _signal).  The pipeline sets it. */
+  int32_t raise_from_push;
+  /* this rank's own device memory: FWD_EB_SHARD_BUFFERS words, zero-initialised once; needed
+   * when raise_from_push is used (NULL otherwise) */
+  uint32_t* tickets;
 } fwd_eb_shard_exchange;
 
 /* Bytes of one rank's receive buffer: row-shard layout for `world` sources, or, with
@@ -122,8 +141,13 @@ int fwd_eb_shard_signal(const fwd_eb_shard_exchange* x, void* stream);
  * A pipeline owns a high-priority side stream and the events that order a step:
  *   main stream   [wait: exchange of step e-2 done]  pooling + push of step e
  *   side stream   [wait: push of step e issued]      flag exchange (+ fold) of step e
- * so the pooling of step e overlaps the flag exchange and fold of step e-1 (three buffer
- * parts make that safe, see FWD_EB_SHARD_BUFFERS), and a step costs the host one call.
+ * so the pooling of step e overlaps the flag exchange and fold of step e-1 (see
+ * FWD_EB_SHARD_BUFFERS for why that is safe), and a step costs the host one call.  With
+ * x->tickets set, the fused-push steps let the pooling grid raise the flag itself (its last
+ * CTA, found with a ticket counter): the main stream then carries nothing but pooling grids and
+ * the side stream's kernel only waits.  Measured slower on B200 (the per-CTA fence that must
+ * precede the ticket: 33.3 against 25.3 us per table-wise step on two GPUs), so the Python layer
+ * leaves tickets unset; the path is kept and tested.
  * It keeps the call number itself (x->epoch is overwritten).  Results complete on the side
  * stream: queue consumers there (fwd_eb_pipeline_side_stream) or call
  * fwd_eb_pipeline_sync_result on the stream that will read them; consume a result before
@@ -134,15 +158,16 @@ int fwd_eb_pipeline_create(fwd_eb_pipeline** out);
 void fwd_eb_pipeline_destroy(fwd_eb_pipeline* pl);
 void* fwd_eb_pipeline_side_stream(fwd_eb_pipeline* pl);
 
-/* Row shards: push `p` on `main_stream`, fold on the side stream into d_out[epoch % 3]
- * (three caller buffers of [bags_per_rank, dim]); *which receives epoch % 3. */
+/* Row shards: push `p` on `main_stream`, fold on the side stream into
+ * d_out[epoch % FWD_EB_SHARD_BUFFERS] (caller buffers of [bags_per_rank, dim]); *which receives that
+ * number. */
 int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
                                   fwd_eb_shard_exchange* x, int64_t num_bags_owned,
                                   void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
                                   void* main_stream, int32_t* which);
 
 /* Row shards, exchange by the copy engines instead of by the pooling kernel's own stores: the
- * plain pooling kernel writes every bag's partial into d_stage[epoch % 3] (three local buffers of
+ * plain pooling kernel writes every bag's partial into d_stage[epoch % FWD_EB_SHARD_BUFFERS] (local buffers of
  * [world * bags_per_rank, dim] in the wire dtype) on `main_stream`; the side stream then sends
  * each owner its block with one cudaMemcpyAsync over NVLink, raises the flags, waits (bounded)
  * and folds as above.  All of the exchange runs beside the next step's pooling and takes no SM
@@ -170,7 +195,7 @@ typedef struct fwd_eb_compact_scratch {
   int32_t* kept;          /* [max num_indices] */
   float* kept_weights;    /* [max num_indices], or NULL when no per_sample_weights are used */
   int32_t* bounds;        /* [max num_bags][2], 8-byte aligned */
-  int32_t* counts;        /* MEAN only: [3][world * bags_per_rank], one part per step in flight */
+  int32_t* counts;        /* MEAN only: [FWD_EB_SHARD_BUFFERS][world * bags_per_rank], one part per step in flight */
 } fwd_eb_compact_scratch;
 int fwd_eb_pipeline_step_rowshard_compact(fwd_eb_pipeline* pl, const fwd_eb_params* p,
                                           fwd_eb_shard_exchange* x, int64_t num_bags_owned,

@@ -8,8 +8,14 @@ Rules modelled, per rank, for call e = 1, 2, ...:
                       — may start only after X(e-2) of the same rank has completed
   side stream   X(e): raise flag e on every peer; wait until every rank's flag >= e has arrived here;
                       fold part e % parts of the own buffer — starts after P(e) and after X(e-1)
-A variant not built yet is modelled too: issuing the main stream's wait only on every k-th call (so
-that consecutive pooling grids are not separated by a wait) needs k + 2 parts.
+Issuing the main stream's wait only on every k-th call (so that consecutive pooling grids are not
+separated by a wait) needs k + 2 parts under these rules.
+
+The fused-push steps of the pipeline as built go further: the flag of call e is raised by the
+pooling grid itself when it completes (`flag_from_pool`), so the side stream's kernel only waits
+and needs no hand-over from the main stream.  A flag then no longer proves that its rank has
+folded the call before; the header's argument gives 2k + 2 parts as sufficient, and that variant
+uses k = 3 with 8 parts.  The default (flag after the fold) uses k = 6 with the same 8 parts.
 The schedule picks, at random, any operation whose predecessors have completed; operations of
 different ranks and streams interleave freely.
 """
@@ -18,7 +24,8 @@ import random
 import pytest
 
 
-def simulate(world: int, parts: int, steps: int, seed: int, wait_every: int = 1):
+def simulate(world: int, parts: int, steps: int, seed: int, wait_every: int = 1,
+             flag_from_pool: bool = False):
     rng = random.Random(seed)
     pooled = [0] * world          # last P completed per rank
     folded = [0] * world          # last X completed per rank (fold done)
@@ -36,7 +43,7 @@ def simulate(world: int, parts: int, steps: int, seed: int, wait_every: int = 1)
             if e <= steps and folded[r] >= waited_for:
                 ready.append(("P", r, e))
             e = folded[r] + 1
-            if e <= steps and pooled[r] >= e:
+            if e <= steps and (flag_from_pool or pooled[r] >= e):
                 ready.append(("X", r, e))
         if not ready:
             return "deadlock", hazards
@@ -49,9 +56,13 @@ def simulate(world: int, parts: int, steps: int, seed: int, wait_every: int = 1)
                     hazards.append((r, owner, e, slot[r], folded[owner]))
                 slot[r] = e
             pooled[r] = e
+            if flag_from_pool:
+                for owner in range(world):
+                    flags[owner][r] = max(flags[owner][r], e)
         else:
-            for owner in range(world):
-                flags[owner][r] = max(flags[owner][r], e)
+            if not flag_from_pool:
+                for owner in range(world):
+                    flags[owner][r] = max(flags[owner][r], e)
             if all(f >= e for f in flags[r]):
                 # every source's rows of call e must be what the part holds now
                 if any(holds[r][e % parts][src] != e for src in range(world)):
@@ -85,3 +96,33 @@ def test_waiting_on_every_kth_call_needs_k_plus_two_parts(wait_every, parts, saf
         assert state == "done"
         hazardous += bool(hazards)
     assert (hazardous == 0) == safe
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_the_pipeline_as_built_wait_every_sixth_call_eight_parts(world):
+    """The default: flag raised after the fold of the call before, a wait on every 6th call."""
+    for seed in range(300):
+        state, hazards = simulate(world, parts=8, steps=60, seed=seed, wait_every=6)
+        assert state == "done" and not hazards, (seed, state, hazards[:3])
+    bad = sum(bool(simulate(4, parts=7, steps=60, seed=seed, wait_every=6)[1]) for seed in range(300))
+    assert bad > 0          # one part fewer does let a rank overwrite an unfolded part
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_the_ticket_variant_flag_from_the_pooling_grid_wait_every_third_call_eight_parts(world):
+    for seed in range(300):
+        state, hazards = simulate(world, parts=8, steps=40, seed=seed, wait_every=3, flag_from_pool=True)
+        assert state == "done" and not hazards, (seed, state, hazards[:3])
+
+
+@pytest.mark.parametrize("wait_every,parts", [(1, 3), (2, 4), (3, 5)])
+def test_flag_from_the_pooling_grid_needs_more_parts_than_flag_after_the_fold(wait_every, parts):
+    """k + 2 parts, enough when a flag is raised only after the previous fold, are not enough once
+    the pooling grid raises it."""
+    hazardous = 0
+    for seed in range(300):
+        state, hazards = simulate(4, parts=parts, steps=30, seed=seed, wait_every=wait_every,
+                                  flag_from_pool=True)
+        assert state == "done"
+        hazardous += bool(hazards)
+    assert hazardous > 0

@@ -30,18 +30,24 @@ def _worker(rank, world, port, tmp):
     lo, n = fd.shard_rows(rows, world, rank)
     local = torch.from_numpy(table[lo:lo + n]).to(dev)
     shards = [fd.shard_rows(rows, world, r) for r in range(world)]
-    for exchange, wire in (("compact", capi.F32), ("compact", capi.F16), ("push", capi.F32),
-                           ("push", capi.F16), ("stage", capi.F32),
+    for exchange, wire in (("compact", capi.F32), ("compact", capi.F16), ("compact+tickets", capi.F32),
+                           ("push", capi.F32), ("push", capi.F16), ("push+tickets", capi.F16),
+                           ("stage", capi.F32),
                            ("stage", capi.F16), ("a2a", capi.F32), ("nccl", capi.F32)):
+        tickets = exchange.endswith("+tickets")      # the pooling grid raises the flag itself
+        exchange = exchange.split("+")[0]
         for mode in (capi.MODE_SUM, capi.MODE_MEAN):
             bag = fd.RowShardedBag(local, lo, mode=mode, max_bags=nb, exchange=exchange,
-                                   wire_dtype=wire, padding_idx=3, max_indices=80 * nb)
-            for step in range(3):
+                                   wire_dtype=wire, padding_idx=3, max_indices=80 * nb,
+                                   flag_from_pool=tickets)
+            for step in range(20 if exchange in ("compact", "push") else 3):   # beyond the eight buffer parts
                 brng = np.random.default_rng(100 + step)
                 bags = workloads.ragged_bags(rows, brng.integers(0, 80, nb), brng)
                 bags.indices[::11] = 3
                 got = bag.forward(torch.from_numpy(bags.indices).to(dev),
                                   torch.from_numpy(bags.offsets).to(dev))
+                if step % 5 != 4:
+                    continue      # several steps queued back to back, then one is checked
                 bag.sync_result()
                 torch.cuda.synchronize()
                 parts = np.stack([O.pool(table[a:a + c], bags.indices, bags.offsets, mode=mode,
@@ -92,11 +98,12 @@ def _worker(rank, world, port, tmp):
     owner = fd.place_tables([1] * ntab, world)
     trng = np.random.default_rng(17)
     tables = [trng.standard_normal((3000 + 100 * t, dim2)).astype(np.float32) for t in range(ntab)]
-    for exchange in ("push", "nccl"):
+    for exchange in ("push", "push+tickets", "nccl"):
         mine_t = [t for t in range(ntab) if owner[t] == rank]
         tw = fd.TableWiseBags({t: torch.from_numpy(tables[t]).to(dev) for t in mine_t}, owner,
-                              dim=dim2, max_bags=nb2, exchange=exchange, fixed_len=L)
-        for step in range(2):
+                              dim=dim2, max_bags=nb2, exchange=exchange.split("+")[0], fixed_len=L,
+                              flag_from_pool=exchange.endswith("+tickets"))
+        for step in range(12 if exchange != "nccl" else 2):
             irng = np.random.default_rng(200 + step)
             idx = [irng.integers(0, tables[t].shape[0], (nb2, L)).astype(np.int32) for t in range(ntab)]
             w = [irng.random(nb2 * L).astype(np.float32) for _ in range(ntab)]
