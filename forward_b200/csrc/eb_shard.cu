@@ -9,6 +9,7 @@
 // pooling grid has completed, so all of its peer stores have been performed — and then waits,
 // with a bound, for the peers' flags.
 #include <climits>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 
@@ -343,7 +344,18 @@ template <typename TW, int LL>
 static cudaError_t launch_push_lite_ll(const PoolArgs& a, const PushArgs& x, bool weighted,
                                        cudaStream_t st) {
   constexpr int VE = 16 / (int)sizeof(TW);
-  const long long blocks = ((a.num_bags << LL) + kCtaThreads - 1) / kCtaThreads;
+  // Bags per lane group.  A warp must wait for its peer stores before it can exit, and a second
+  // bag to walk would hide that wait; but two bags per group also halve the number of groups,
+  // and on two B200s the step got slower, not faster (32.5 against 24.5 us table-wise, 150
+  // against 133 us on config 5): one bag per group, the hardware hands out CTAs as slots free up.
+  long long per_group = 1;
+#ifdef FWD_EB_TUNE
+  if (const char* env = getenv("FWD_EB_PUSH_BAGS")) per_group = atoi(env) > 0 ? atoi(env) : per_group;
+#endif
+  PoolArgs b = a;
+  b.stream_k = (int)per_group;
+  const long long groups = (a.num_bags + per_group - 1) / per_group;
+  const long long blocks = ((groups << LL) + kCtaThreads - 1) / kCtaThreads;
   if (blocks == 0) return cudaSuccess;
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   cudaLaunchConfig_t cfg = {};
@@ -356,8 +368,8 @@ static cudaError_t launch_push_lite_ll(const PoolArgs& a, const PushArgs& x, boo
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   cudaError_t e = weighted
-      ? cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, kOpWeighted, true>, a, x)
-      : cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, kOpSum, true>, a, x);
+      ? cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, kOpWeighted, true>, b, x)
+      : cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, kOpSum, true>, b, x);
   count_launch();
   return e != cudaSuccess ? e : cudaGetLastError();
 }
