@@ -467,7 +467,7 @@ class GpuWorkload:
         if self.workload == "tablewise":
             self.bag = fd.TableWiseBags({self.rank: self.table}, list(range(self.world)), dim=self.dim,
                                         max_bags=bags_n, exchange=args.exchange, wire_dtype=capi.F16,
-                                        mode=self.mode)
+                                        mode=self.mode, ship=args.ship, lookback=args.lookback)
             self.out_itemsize = 2 if args.exchange == "push" else 4
 
             self._prepared = [self.bag.prepare({self.rank: (i, o, None)}) for i, o in self.d_batches]
@@ -478,7 +478,8 @@ class GpuWorkload:
             wire = capi.F16 if args.wire == "f16" else capi.F32
             max_n = max(b.num_indices for b in self.batches)
             self.bag = fd.RowShardedBag(self.table, self.row_lo, mode=self.mode, max_bags=bags_n,
-                                        exchange=args.exchange, wire_dtype=wire, max_indices=max_n)
+                                        exchange=args.exchange, wire_dtype=wire, max_indices=max_n,
+                                        ship=args.ship, lookback=args.lookback)
             self.out_itemsize = 2 if (args.exchange in ("push", "stage", "compact") and args.wire == "f16") else 4
 
             self._prepared = [self.bag.prepare(i, o) for i, o in self.d_batches]
@@ -601,7 +602,7 @@ class C4Workload:
             return
         self.bag = fd.TableWiseBags(self.tables, self.owner, dim=self.dim, max_bags=C4["bags"],
                                     exchange=args.exchange, wire_dtype=capi.F32, mode=self.mode,
-                                    fixed_len=self.L)
+                                    fixed_len=self.L, ship=args.ship, lookback=args.lookback)
         prepared = self.bag.prepare({t: (self.d_idx[t], None, self.d_w[t]) for t in self.mine})
 
         def step(k, events=None):
@@ -877,7 +878,7 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
         egress = wl.egress_bytes() if hasattr(wl, "egress_bytes") else \
             bags_n * (world - 1) // world * wl.dim * wl.out_itemsize
         extra_us = max(step_us - pool_only_us, 1e-3)
-        exchange = {"method": wl.exchange_name if hasattr(wl, "exchange_name") else args.exchange,
+        exchange = {"method": args.exchange + ("+ship" if args.ship and args.exchange in ("push", "compact") else ""),
                     "wire": "f16" if wl.out_itemsize == 2 else "f32",
                     "pool_only_us": pool_only_us, "step_us": step_us,
                     "overhead_frac": (step_us - pool_only_us) / pool_only_us,
@@ -1347,6 +1348,14 @@ def main():
                     help="--workload auto: skip the secondary workloads attached to the line "
                          "(N=1: uniform-index c2 and c3; N>1: c5 and c4)")
     ap.add_argument("--no-plugin-e2e", action="store_true")
+    ap.add_argument("--lookback", default=None,
+                    help="N>1: EVERY,DEPTH of the exchange pipeline (fwd_eb_pipeline_set_lookback); "
+                         "default: the library's 6,2")
+    ap.add_argument("--ship", type=int, default=0, choices=[0, 1],
+                    help="N>1, exchanges push / compact: 1 = the pooling kernel stores its rows locally and a "
+                         "copy kernel on the side stream sends them to their owners; 0 = the pooling "
+                         "kernel stores into the peers' buffers itself (the default: shipping measured "
+                         "slower at 2 and at 8 GPUs)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "compact", "push", "stage", "a2a", "nccl"],
                     help="N>1: how pooled rows / partial bags reach their owners.  push: the pooling "
                          "kernel's own peer stores; compact (row shards only): window compaction first, "
@@ -1369,6 +1378,7 @@ def main():
                     help="untimed launches before the counted warm-up, to bring clocks up")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.lookback = tuple(int(v) for v in args.lookback.split(",")) if args.lookback else None
     C5["rows"] = args.c5_rows
     if args.exchange == "auto":
         args.exchange = "compact" if args.workload in ("rowshard", "c5") else "push"

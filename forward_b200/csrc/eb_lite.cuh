@@ -37,118 +37,112 @@ eb_pool_lite_kernel(const PoolArgs a, const PushArgs x) {
   const unsigned lane = threadIdx.x & 31u;
   const int lig = lane & (LANES - 1);
   const int gbase = lane & ~(LANES - 1);
-  const int seq0 = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> LL);
-  const int ngroups = (int)(((long long)gridDim.x * blockDim.x) >> LL);
+  const int seq = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> LL);
+  const bool live = seq < a.num_bags;
+  int bag = seq;
+  if (PUSH && live) {  // start with the next rank's bags (see eb_pool_push_kernel)
+    bag += (int)x.first_bag;
+    if (bag >= a.num_bags) bag -= (int)a.num_bags;
+  }
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int* __restrict__ indices = reinterpret_cast<const int*>(a.indices);
   const int* __restrict__ offsets = reinterpret_cast<const int*>(a.offsets);
   const int n_idx = (int)a.num_indices;
-  // a.stream_k bags per lane group, a grid's width apart.  The launchers use 1: more bags per
-  // group mean fewer groups, and the hardware's hand-out of CTAs balances ragged bags better.
-  for (int it = 0; it < a.stream_k; ++it) {
-    const int seq = seq0 + it * ngroups;
-    const bool live = seq < a.num_bags;
-    int bag = seq;
-    if (PUSH && live) {  // start with the next rank's bags (see eb_pool_push_kernel)
-      bag += (int)x.first_bag;
-      if (bag >= a.num_bags) bag -= (int)a.num_bags;
-    }
-    int start = 0, end = 0;
-    if (live) {
-      if (a.fixed_len > 0) {
-        start = bag * a.fixed_len;
-        end = start + a.fixed_len;
-      } else if (a.pairs) {
-        const int2 se = __ldg(reinterpret_cast<const int2*>(offsets) + bag);
-        start = se.x;
-        end = se.y;
-      } else {
-        start = __ldg(offsets + bag);
-        end = (a.include_last || bag + 1 < a.num_bags) ? __ldg(offsets + bag + 1) : n_idx;
-      }
-      // a malformed offsets array must not turn into a wild read
-      start = start < 0 ? 0 : start;
-      end = end > n_idx ? n_idx : end;
-      end = end < start ? start : end;
-    }
-
-    const bool chunk_ok = lig < a.nchunks;
-    const char* __restrict__ tbase = a.table + lig * (VE * (int)sizeof(TW));
-    const unsigned stride32 = (unsigned)a.row_bytes_stride;
-
-    float acc[VE];
-  #pragma unroll
-    for (int e = 0; e < VE; ++e) acc[e] = 0.0f;
-    int counted = 0;
-    bool have = false;
-
-    // one index per lane: local row (>= 0), -1 = counted but outside the window, -2 = padding / none
-    auto fetch = [&](int pos, int& row, float& w) {
-      row = -2;
-      w = 1.0f;
-      if (pos < end) {
-        const int idx = __ldg(indices + pos);
-        if (!a.pad32_on || idx != a.pad32) {
-          const unsigned r = (unsigned)idx - a.lo32;
-          row = r < a.nrows32 ? (int)r : -1;
-          if (OP == kOpWeighted) w = __ldg(a.psw + pos);
-        }
-      }
-    };
-
-    int row, nrow;
-    float w, nw;
-    fetch(start + lig, row, w);
-    for (int base = start; __any_sync(kFull, base < end); base += LANES) {
-      fetch(base + LANES + lig, nrow, nw);  // next block, early
-      if (a.mean) counted += __popc((__ballot_sync(kFull, row >= -1) >> gbase) & GMASK);
-      const int n = end - base;             // entries of this block (may exceed LANES or be <= 0)
-  #pragma unroll
-      for (int k = 0; k < LANES; k += U) {
-        if (!__any_sync(kFull, k < n)) break;
-        V val[U];
-        float wu[U];
-        unsigned ok = 0u;
-  #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int r = __shfl_sync(kFull, row, gbase + ((k + u) & (LANES - 1)));
-          if (OP == kOpWeighted) wu[u] = __shfl_sync(kFull, w, gbase + ((k + u) & (LANES - 1)));
-          const bool take = k + u < n && k + u < LANES && r >= 0;
-          ok |= (take ? 1u : 0u) << u;
-          if (take && chunk_ok) val[u] = load_chunk<V>(tbase + (unsigned long long)(unsigned)r * stride32);
-        }
-  #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (((ok >> u) & 1u) && chunk_ok) {
-            fold_chunk<OP>(acc, val[u], OP == kOpWeighted ? wu[u] : 1.0f, !have);
-            have = true;
-          }
-        }
-      }
-      row = nrow;
-      w = nw;
-    }
-
-    float v[1][VE];
-  #pragma unroll
-    for (int e = 0; e < VE; ++e) v[0][e] = acc[e];
-    if (OP == kOpMax && VE == 8) unpack_half_max(reinterpret_cast<float(&)[8]>(v[0]));
-    const bool tf16 = sizeof(TW) == 2;
-  #pragma unroll
-    for (int e = 0; e < VE; ++e) v[0][e] = finish(a, v[0][e], counted, (long long)(end - start), tf16);
-    if (PUSH) {
-      long long owner = 0;
-      if (live) owner = (long long)((unsigned)bag / (unsigned)x.bags_per_rank);
-      if (owner >= x.world) owner = x.world - 1;
-      char* base = x.peer_slots[owner] + x.col_offset * (a.out_f16 ? 2 : 4);
-      store_row<VE, 1, true>(a, base, x.row_base + (bag - owner * x.bags_per_rank), 0, v, live);
+  int start = 0, end = 0;
+  if (live) {
+    if (a.fixed_len > 0) {
+      start = bag * a.fixed_len;
+      end = start + a.fixed_len;
+    } else if (a.pairs) {
+      const int2 se = __ldg(reinterpret_cast<const int2*>(offsets) + bag);
+      start = se.x;
+      end = se.y;
     } else {
-      store_row<VE, 1, true>(a, a.out, bag, 0, v, live);
+      start = __ldg(offsets + bag);
+      end = (a.include_last || bag + 1 < a.num_bags) ? __ldg(offsets + bag + 1) : n_idx;
     }
+    // a malformed offsets array must not turn into a wild read
+    start = start < 0 ? 0 : start;
+    end = end > n_idx ? n_idx : end;
+    end = end < start ? start : end;
   }
-  if (PUSH) push_grid_done(x);
+
+  const bool chunk_ok = lig < a.nchunks;
+  const char* __restrict__ tbase = a.table + lig * (VE * (int)sizeof(TW));
+  const unsigned stride32 = (unsigned)a.row_bytes_stride;
+
+  float acc[VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) acc[e] = 0.0f;
+  int counted = 0;
+  bool have = false;
+
+  // one index per lane: local row (>= 0), -1 = counted but outside the window, -2 = padding / none
+  auto fetch = [&](int pos, int& row, float& w) {
+    row = -2;
+    w = 1.0f;
+    if (pos < end) {
+      const int idx = __ldg(indices + pos);
+      if (!a.pad32_on || idx != a.pad32) {
+        const unsigned r = (unsigned)idx - a.lo32;
+        row = r < a.nrows32 ? (int)r : -1;
+        if (OP == kOpWeighted) w = __ldg(a.psw + pos);
+      }
+    }
+  };
+
+  int row, nrow;
+  float w, nw;
+  fetch(start + lig, row, w);
+  for (int base = start; __any_sync(kFull, base < end); base += LANES) {
+    fetch(base + LANES + lig, nrow, nw);  // next block, early
+    if (a.mean) counted += __popc((__ballot_sync(kFull, row >= -1) >> gbase) & GMASK);
+    const int n = end - base;             // entries of this block (may exceed LANES or be <= 0)
+#pragma unroll
+    for (int k = 0; k < LANES; k += U) {
+      if (!__any_sync(kFull, k < n)) break;
+      V val[U];
+      float wu[U];
+      unsigned ok = 0u;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int r = __shfl_sync(kFull, row, gbase + ((k + u) & (LANES - 1)));
+        if (OP == kOpWeighted) wu[u] = __shfl_sync(kFull, w, gbase + ((k + u) & (LANES - 1)));
+        const bool take = k + u < n && k + u < LANES && r >= 0;
+        ok |= (take ? 1u : 0u) << u;
+        if (take && chunk_ok) val[u] = load_chunk<V>(tbase + (unsigned long long)(unsigned)r * stride32);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (((ok >> u) & 1u) && chunk_ok) {
+          fold_chunk<OP>(acc, val[u], OP == kOpWeighted ? wu[u] : 1.0f, !have);
+          have = true;
+        }
+      }
+    }
+    row = nrow;
+    w = nw;
+  }
+
+  float v[1][VE];
+#pragma unroll
+  for (int e = 0; e < VE; ++e) v[0][e] = acc[e];
+  if (OP == kOpMax && VE == 8) unpack_half_max(reinterpret_cast<float(&)[8]>(v[0]));
+  const bool tf16 = sizeof(TW) == 2;
+#pragma unroll
+  for (int e = 0; e < VE; ++e) v[0][e] = finish(a, v[0][e], counted, (long long)(end - start), tf16);
+  if (PUSH) {
+    long long owner = 0;
+    if (live) owner = (long long)((unsigned)bag / (unsigned)x.bags_per_rank);
+    if (owner >= x.world) owner = x.world - 1;
+    char* base = x.peer_slots[owner] + x.col_offset * (a.out_f16 ? 2 : 4);
+    store_row<VE, 1, true>(a, base, x.row_base + (bag - owner * x.bags_per_rank), 0, v, live);
+    push_grid_done(x);
+  } else {
+    store_row<VE, 1, true>(a, a.out, bag, 0, v, live);
+  }
 }
 
 }  // namespace fwd_eb

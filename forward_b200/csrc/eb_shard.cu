@@ -206,6 +206,53 @@ eb_shard_combine_kernel(const TP* slots, int world, long long slot_stride, long 
   }
 }
 
+// Ship staged rows to their owners (fwd_eb_shard_ship).  One thread moves 16 bytes at a time;
+// segment = one bag's row of one staged table.  Segments are walked bag-major with the owner
+// next, so consecutive warps talk to different peers, and every rank starts with its right-hand
+// neighbour.
+constexpr int kShipMaxTables = 32;
+struct ShipArgs {
+  const char* stage;             // this call's part: [world][per][S][seg_bytes]
+  char* peer[FWD_EB_MAX_PEERS];  // this call's part of every owner's buffer
+  long long per;                 // bags per rank
+  long long num_bags;
+  long long dst_row_stride;      // bytes between destination rows
+  long long dst_row_base;        // first destination row (row shards: rank * per)
+  int col_bytes[kShipMaxTables]; // destination column offset of staged slot j
+  int world, rank, S, seg_bytes;
+};
+
+__global__ void __launch_bounds__(256) eb_shard_ship_kernel(const ShipArgs a) {
+  const int vps = a.seg_bytes >> 4;  // 16-byte vectors per segment
+  const long long total = a.per * a.world * a.S * vps;
+  const long long step = (long long)gridDim.x * blockDim.x;
+  constexpr int UNR = 4;
+  for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < total; v0 += step * UNR) {
+    uint4 val[UNR];
+    char* dst[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long long v = v0 + u * step;
+      dst[u] = nullptr;
+      if (v < total) {
+        const long long seg = v / vps;
+        const int c = (int)(v - seg * vps);
+        const int j = (int)(seg % a.S);
+        const long long t = seg / a.S;
+        const int o = (int)((t % a.world + a.rank + 1) % a.world);
+        const long long bag = t / a.world;
+        if (o * a.per + bag < a.num_bags) {
+          val[u] = *reinterpret_cast<const uint4*>(a.stage + ((o * a.per + bag) * a.S + j) * a.seg_bytes + c * 16);
+          dst[u] = a.peer[o] + (a.dst_row_base + bag) * a.dst_row_stride + a.col_bytes[j] + c * 16;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u)
+      if (dst[u]) *reinterpret_cast<uint4*>(dst[u]) = val[u];
+  }
+}
+
 static size_t wire_bytes(int wire_dtype) {
   return wire_dtype == FWD_EB_F16 ? 2u : (wire_dtype == FWD_EB_F32_POS ? 8u : 4u);
 }
@@ -223,6 +270,15 @@ static int check_exchange(const fwd_eb_shard_exchange* x) {
   if (x->epoch == 0) return fail(FWD_EB_EINVAL, "epoch starts at 1");
   if (x->raise_from_push && !x->tickets)
     return fail(FWD_EB_EINVAL, "raise_from_push needs the ticket words");
+  if (x->stage) {
+    if (x->raise_from_push) return fail(FWD_EB_EINVAL, "staged rows are shipped: the flag follows the ship kernel");
+    if (x->layout == FWD_EB_LAYOUT_TABLE_WISE &&
+        (x->stage_tables < 1 || x->stage_tables > kShipMaxTables || x->stage_slot < 0 ||
+         x->stage_slot >= x->stage_tables))
+      return fail(FWD_EB_EINVAL, "stage_slot %d outside %d staged tables (at most %d)", x->stage_slot,
+                  x->stage_tables, kShipMaxTables);
+    if (reinterpret_cast<uintptr_t>(x->stage) & 15u) return fail(FWD_EB_EALIGN, "stage must be 16-byte aligned");
+  }
   if (!x->status) return fail(FWD_EB_EINVAL, "status word is null");
   for (int r = 0; r < x->world; ++r) {
     if (!x->peer_slots[r] || !x->peer_flags[r])
@@ -254,6 +310,15 @@ static void fill_push(const fwd_eb_shard_exchange* x, int dim, PushArgs* out) {
   } else {
     out->row_base = (long long)x->rank * x->bags_per_rank;
     out->col_offset = 0;
+  }
+  if (x->stage) {
+    // every owner's rows go to the local staging scratch, laid out [owner][bag][staged table][dim]
+    const int S = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? x->stage_tables : 1;
+    const size_t block = (size_t)x->bags_per_rank * S * dim * wire_bytes(x->wire_dtype);
+    char* base = static_cast<char*>(x->stage) + block * x->world * (x->epoch % FWD_EB_SHARD_BUFFERS);
+    for (int r = 0; r < x->world; ++r) out->peer_slots[r] = base + block * r;
+    out->row_base = 0;
+    out->col_offset = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (long long)x->stage_slot * dim : 0;
   }
   out->bags_per_rank = x->bags_per_rank;
   out->world = x->world;
@@ -344,18 +409,12 @@ template <typename TW, int LL>
 static cudaError_t launch_push_lite_ll(const PoolArgs& a, const PushArgs& x, bool weighted,
                                        cudaStream_t st) {
   constexpr int VE = 16 / (int)sizeof(TW);
-  // Bags per lane group.  A warp must wait for its peer stores before it can exit, and a second
-  // bag to walk would hide that wait; but two bags per group also halve the number of groups,
-  // and on two B200s the step got slower, not faster (32.5 against 24.5 us table-wise, 150
-  // against 133 us on config 5): one bag per group, the hardware hands out CTAs as slots free up.
-  long long per_group = 1;
-#ifdef FWD_EB_TUNE
-  if (const char* env = getenv("FWD_EB_PUSH_BAGS")) per_group = atoi(env) > 0 ? atoi(env) : per_group;
-#endif
-  PoolArgs b = a;
-  b.stream_k = (int)per_group;
-  const long long groups = (a.num_bags + per_group - 1) / per_group;
-  const long long blocks = ((groups << LL) + kCtaThreads - 1) / kCtaThreads;
+  // One bag per lane group.  (A warp must wait for its peer stores before it can exit, and a
+  // second bag to walk would hide that wait; but two bags per group also halve the number of
+  // groups, and on two B200s the step got slower, not faster: 32.5 against 24.5 us table-wise,
+  // 150 against 133 us on config 5.  The hardware's hand-out of CTAs balances ragged bags better.)
+  const PoolArgs& b = a;
+  const long long blocks = ((a.num_bags << LL) + kCtaThreads - 1) / kCtaThreads;
   if (blocks == 0) return cudaSuccess;
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   cudaLaunchConfig_t cfg = {};
@@ -418,7 +477,10 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
     if (!(q.flags & FWD_EB_FLAG_OFFSET_PAIRS) && q.strategy == FWD_EB_STRATEGY_AUTO)
       q.strategy = FWD_EB_STRATEGY_GROUP;
   }
-  q.out_stride = x->layout == FWD_EB_LAYOUT_TABLE_WISE ? (int64_t)x->num_tables * p->dim : 0;
+  q.out_stride = x->layout == FWD_EB_LAYOUT_TABLE_WISE
+                     ? (int64_t)(x->stage ? x->stage_tables : x->num_tables) * p->dim : 0;
+  if (x->stage && ((size_t)p->dim * wire_bytes(x->wire_dtype)) % 16 != 0)
+    return fail(FWD_EB_EUNSUPPORTED, "shipping needs rows that are a multiple of 16 bytes on the wire");
   PoolArgs a;
   int vec = 0, cpl = 0, tiles = 0, stream_kernel = 0;
   rc = plan_group(&q, &a, &vec, &cpl, &tiles, &stream_kernel);
@@ -443,6 +505,62 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
             : launch_push_shape<float>(a, px, vec != 0, cpl, tiles, weighted, st);
   }
   if (e != cudaSuccess) return cuda_fail(e, "push kernel launch");
+  clear_error();
+  return 0;
+}
+
+size_t fwd_eb_shard_stage_bytes(int32_t world, int64_t bags_per_rank, int32_t stage_tables, int32_t dim,
+                                int32_t wire_dtype) {
+  if (world < 1 || bags_per_rank < 1 || stage_tables < 1 || dim < 1) return 0;
+  return (size_t)FWD_EB_SHARD_BUFFERS * (size_t)world * (size_t)bags_per_rank * (size_t)stage_tables *
+         (size_t)dim * wire_bytes(wire_dtype);
+}
+
+int fwd_eb_shard_ship(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                      const int32_t* table_ids, void* stream) {
+  int rc = check_exchange(x);
+  if (rc) return rc;
+  if (!x->stage) return fail(FWD_EB_EINVAL, "nothing was staged: x->stage is null");
+  if (dim <= 0 || num_bags < 0 || num_bags > x->bags_per_rank * x->world)
+    return fail(FWD_EB_EINVAL, "bad ship arguments");
+  const bool tw = x->layout == FWD_EB_LAYOUT_TABLE_WISE;
+  if (tw && !table_ids) return fail(FWD_EB_EINVAL, "table_ids is null");
+  const size_t seg = (size_t)dim * wire_bytes(x->wire_dtype);
+  if (seg % 16 != 0 || seg > 0x7fffffffu)
+    return fail(FWD_EB_EUNSUPPORTED, "shipping needs rows that are a multiple of 16 bytes on the wire");
+  if (num_bags == 0) return 0;
+  ShipArgs a;
+  memset(&a, 0, sizeof(a));
+  a.S = tw ? x->stage_tables : 1;
+  a.seg_bytes = (int)seg;
+  a.per = x->bags_per_rank;
+  a.num_bags = num_bags;
+  a.world = x->world;
+  a.rank = x->rank;
+  const size_t block = (size_t)x->bags_per_rank * a.S * seg;
+  a.stage = static_cast<const char*>(x->stage) + block * x->world * (x->epoch % FWD_EB_SHARD_BUFFERS);
+  const size_t part = part_bytes(x, dim) * (size_t)(x->epoch % FWD_EB_SHARD_BUFFERS);
+  for (int r = 0; r < x->world; ++r) a.peer[r] = static_cast<char*>(x->peer_slots[r]) + part;
+  if (tw) {
+    a.dst_row_stride = (long long)x->num_tables * (long long)seg;
+    a.dst_row_base = 0;
+    for (int j = 0; j < a.S; ++j) {
+      if (table_ids[j] < 0 || table_ids[j] >= x->num_tables)
+        return fail(FWD_EB_EINVAL, "table_ids[%d] = %d outside %d tables", j, table_ids[j], x->num_tables);
+      a.col_bytes[j] = (int)(table_ids[j] * (long long)seg);
+    }
+  } else {
+    a.dst_row_stride = (long long)seg;
+    a.dst_row_base = (long long)x->rank * x->bags_per_rank;
+  }
+  const long long vectors = (long long)x->bags_per_rank * x->world * a.S * (long long)(seg / 16);
+  long long blocks = (vectors + 256 * 4 - 1) / (256 * 4);
+  const long long cap = sm_count() / 2 > 0 ? sm_count() / 2 : 1;   // a corner of the GPU: the pooling has the rest
+  if (blocks > cap) blocks = cap;
+  eb_shard_ship_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "ship kernel launch");
   clear_error();
   return 0;
 }
@@ -568,6 +686,8 @@ struct fwd_eb_pipeline {
   cudaEvent_t pushed[FWD_EB_SHARD_BUFFERS] = {};
   cudaEvent_t done[FWD_EB_SHARD_BUFFERS] = {};
   uint32_t epoch = 0;
+  uint32_t every = FWD_EB_PIPELINE_WAIT_EVERY;
+  uint32_t depth = FWD_EB_PIPELINE_WAIT_DEPTH;
 };
 
 // A step that fails its host-side checks before anything was launched must not leave this rank
@@ -579,19 +699,21 @@ static int pipeline_abort(fwd_eb_pipeline* pl, int rc) {
 }
 
 static int pipeline_begin(fwd_eb_pipeline* pl, fwd_eb_shard_exchange* x, cudaStream_t main) {
-  // Call numbers are 32-bit flag values and pick the buffer part modulo 3: refuse the step that
+  // Call numbers are 32-bit flag values and pick the buffer part by a modulo: refuse the step that
   // would wrap them (2^32 steps: more than a day at 25 us a step) instead of going out of phase.
   if (pl->epoch >= 0xfffffff0u)
     return fail(FWD_EB_ETOOBIG, "this pipeline has run 2^32 steps: drain it on every rank and create a new one");
   pl->epoch += 1;
   x->epoch = pl->epoch;
-  const uint32_t every = x->tickets ? FWD_EB_PIPELINE_WAIT_EVERY_TICKETS : FWD_EB_PIPELINE_WAIT_EVERY;
-  static_assert(FWD_EB_PIPELINE_WAIT_EVERY + 2 <= FWD_EB_SHARD_BUFFERS, "k + 2 parts");
-  static_assert(2 * FWD_EB_PIPELINE_WAIT_EVERY_TICKETS + 2 <= FWD_EB_SHARD_BUFFERS, "2k + 2 parts");
-  if (pl->epoch > 2 && pl->epoch % every == 0) {
-    // this rank has folded step e-2, hence seen every rank's flag e-2; see FWD_EB_SHARD_BUFFERS
-    // for why looking back this rarely is enough with eight buffer parts
-    cudaError_t e = cudaStreamWaitEvent(main, pl->done[(pl->epoch - 2) % FWD_EB_SHARD_BUFFERS], 0);
+  static_assert(FWD_EB_PIPELINE_WAIT_EVERY + FWD_EB_PIPELINE_WAIT_DEPTH <= FWD_EB_SHARD_BUFFERS, "k + d parts");
+  static_assert(2 * (FWD_EB_PIPELINE_WAIT_EVERY_TICKETS - 1) + 2 * FWD_EB_PIPELINE_WAIT_DEPTH <= FWD_EB_SHARD_BUFFERS,
+                "2(k-1) + 2d parts");
+  const uint32_t every = x->tickets ? FWD_EB_PIPELINE_WAIT_EVERY_TICKETS : pl->every;
+  const uint32_t depth = x->tickets ? FWD_EB_PIPELINE_WAIT_DEPTH : pl->depth;
+  if (pl->epoch > depth && pl->epoch % every == 0) {
+    // this rank has folded step e-d, hence seen every rank's flag e-d; see FWD_EB_SHARD_BUFFERS
+    // for why looking back this rarely is enough with the buffer parts there are
+    cudaError_t e = cudaStreamWaitEvent(main, pl->done[(pl->epoch - depth) % FWD_EB_SHARD_BUFFERS], 0);
     if (e != cudaSuccess) {
       pl->epoch -= 1;
       return cuda_fail(e, "cudaStreamWaitEvent (main)");
@@ -647,6 +769,17 @@ void fwd_eb_pipeline_destroy(fwd_eb_pipeline* pl) {
 
 void* fwd_eb_pipeline_side_stream(fwd_eb_pipeline* pl) { return pl ? pl->side : nullptr; }
 
+int fwd_eb_pipeline_set_lookback(fwd_eb_pipeline* pl, int32_t every, int32_t depth) {
+  if (!pl) return fail(FWD_EB_EINVAL, "null pipeline");
+  if (every < 1 || depth < 2 || every + depth > FWD_EB_SHARD_BUFFERS)
+    return fail(FWD_EB_EINVAL, "lookback needs every >= 1, depth >= 2 and every + depth <= %d (got %d, %d)",
+                FWD_EB_SHARD_BUFFERS, every, depth);
+  if (pl->epoch != 0) return fail(FWD_EB_EINVAL, "set the lookback before the first step");
+  pl->every = (uint32_t)every;
+  pl->depth = (uint32_t)depth;
+  return 0;
+}
+
 int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
                                   fwd_eb_shard_exchange* x, int64_t num_bags_owned,
                                   void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
@@ -655,11 +788,15 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   int rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
-  x->raise_from_push = x->tickets ? 1 : 0;
+  x->raise_from_push = (x->tickets && !x->stage) ? 1 : 0;
   rc = fwd_eb_shard_push(p, x, main);   // validates before it launches
   if (rc) return pipeline_abort(pl, rc);
   if (!x->raise_from_push) {
     rc = pipeline_handover(pl, main);
+    if (rc) return rc;
+  }
+  if (x->stage) {   // the staged rows go to their owners from the side stream
+    rc = fwd_eb_shard_ship(x, p->dim, p->num_bags, nullptr, pl->side);
     if (rc) return rc;
   }
   const int k = pl->epoch % FWD_EB_SHARD_BUFFERS;
@@ -712,11 +849,15 @@ int fwd_eb_pipeline_step_rowshard_compact(fwd_eb_pipeline* pl, const fwd_eb_para
   if (q.strategy != FWD_EB_STRATEGY_GROUP && q.strategy != FWD_EB_STRATEGY_STREAM &&
       q.strategy != FWD_EB_STRATEGY_LITE)
     q.strategy = FWD_EB_STRATEGY_AUTO;
-  x->raise_from_push = x->tickets ? 1 : 0;
+  x->raise_from_push = (x->tickets && !x->stage) ? 1 : 0;
   rc = fwd_eb_shard_push(&q, x, main);
   if (rc) return rc;   // the compaction has run: the step cannot be taken back
   if (!x->raise_from_push) {
     rc = pipeline_handover(pl, main);
+    if (rc) return rc;
+  }
+  if (x->stage) {   // the staged rows go to their owners from the side stream
+    rc = fwd_eb_shard_ship(x, p->dim, p->num_bags, nullptr, pl->side);
     if (rc) return rc;
   }
   // 3. flags, bounded wait, fold (and the mean's division) on the side stream
@@ -811,9 +952,15 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   int rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
-  const bool from_push = x->tickets != nullptr && count > 0;
+  const bool from_push = x->tickets != nullptr && count > 0 && !x->stage;
+  if (x->stage && count > kShipMaxTables)
+    return fail(FWD_EB_ETOOBIG, "shipping takes at most %d tables per rank and step (got %d)", kShipMaxTables, count);
+  int64_t batch = 0;
   for (int i = 0; i < count; ++i) {
     x->table_index = table_index[i];
+    x->stage_tables = count;
+    x->stage_slot = i;
+    if (params[i] && params[i]->num_bags > batch) batch = params[i]->num_bags;
     x->raise_from_push = (from_push && i == count - 1) ? 1 : 0;   // the step's last grid raises the flag
     rc = fwd_eb_shard_push(params[i], x, main);
     if (rc) return i == 0 ? pipeline_abort(pl, rc) : rc;   // nothing launched yet: take the number back
@@ -821,6 +968,10 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
   x->raise_from_push = from_push ? 1 : 0;
   if (!from_push) {
     rc = pipeline_handover(pl, main);
+    if (rc) return rc;
+  }
+  if (x->stage && count > 0) {   // the staged rows go to their owners from the side stream
+    rc = fwd_eb_shard_ship(x, dim, batch, table_index, pl->side);
     if (rc) return rc;
   }
   rc = fwd_eb_shard_wait(x, dim, d_result, pl->side);

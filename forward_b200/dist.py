@@ -28,7 +28,7 @@ import ctypes as C
 from . import capi
 
 MAX_PEERS = 16
-SHARD_BUFFERS = 8          # FWD_EB_SHARD_BUFFERS: parts of a receive buffer, results in rotation
+SHARD_BUFFERS = 16         # FWD_EB_SHARD_BUFFERS: parts of a receive buffer, results in rotation
 LAYOUT_ROW_SHARD, LAYOUT_TABLE_WISE = 0, 1
 SHARD_TIMEOUT = 1
 
@@ -87,6 +87,7 @@ class ShardExchange(C.Structure):
         ("status", C.c_void_p), ("max_spins", C.c_int64),
         ("layout", C.c_int32), ("num_tables", C.c_int32), ("table_index", C.c_int32),
         ("raise_from_push", C.c_int32), ("tickets", C.c_void_p),
+        ("stage", C.c_void_p), ("stage_tables", C.c_int32), ("stage_slot", C.c_int32),
     ]
 
 
@@ -102,6 +103,8 @@ SIGNATURES = {
                                                         C.POINTER(ShardExchange), C.c_int64,
                                                         C.POINTER(CompactScratch), C.POINTER(C.c_void_p),
                                                         C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]),
+    "fwd_eb_shard_stage_bytes": (C.c_size_t, [C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int32]),
+    "fwd_eb_shard_ship": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.c_int64, C.c_void_p, C.c_void_p]),
     "fwd_eb_shard_wait": (C.c_int, [C.POINTER(ShardExchange), C.c_int32, C.POINTER(C.c_void_p),
                                     C.c_void_p]),
     "fwd_eb_shard_signal": (C.c_int, [C.POINTER(ShardExchange), C.c_void_p]),
@@ -110,6 +113,7 @@ SIGNATURES = {
     "fwd_eb_pipeline_create": (C.c_int, [C.POINTER(C.c_void_p)]),
     "fwd_eb_pipeline_destroy": (None, [C.c_void_p]),
     "fwd_eb_pipeline_side_stream": (C.c_void_p, [C.c_void_p]),
+    "fwd_eb_pipeline_set_lookback": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32]),
     "fwd_eb_pipeline_step_rowshard": (C.c_int, [C.c_void_p, C.POINTER(capi.Params), C.POINTER(ShardExchange),
                                                 C.c_int64, C.POINTER(C.c_void_p), C.c_int32, C.c_void_p,
                                                 C.POINTER(C.c_int32)]),
@@ -228,7 +232,8 @@ class RowShardedBag:
 
     def __init__(self, table_local, row_lo: int, *, mode: int, max_bags: int, group=None,
                  exchange: str = "push", wire_dtype: int = capi.F32, padding_idx: int = -1,
-                 out_dtype=None, max_indices: int = 0, flag_from_pool: bool = False):
+                 out_dtype=None, max_indices: int = 0, flag_from_pool: bool = False, ship: bool = False,
+                 lookback: tuple[int, int] | None = None):
         import torch
         import torch.distributed as dist
         if mode == capi.MODE_MAX:
@@ -263,6 +268,8 @@ class RowShardedBag:
             self._out_ptrs = (C.c_void_p * SHARD_BUFFERS)(*[o.data_ptr() for o in self.outs])
             self._pl = C.c_void_p()
             capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
+            if lookback:
+                capi.check(_lib().fwd_eb_pipeline_set_lookback(self._pl, *lookback))
             self.side = torch.cuda.ExternalStream(_lib().fwd_eb_pipeline_side_stream(self._pl), device=dev)
             self._which = C.c_int32(0)
             nbytes = _lib().fwd_eb_shard_slots_bytes(self.world, self.per, self.dim, wire_dtype)
@@ -273,6 +280,15 @@ class RowShardedBag:
             self.tickets = torch.zeros(SHARD_BUFFERS, dtype=torch.int32, device=dev) if flag_from_pool else None
             self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status,
                                    tickets=self.tickets)
+            self._stage = None
+            if ship and exchange in ("push", "compact"):
+                # ship: the pooling kernel stores every partial row locally and a small copy kernel
+                # on the side stream sends them on (a pooling warp that stores to a peer has to wait
+                # for the acknowledgement before it can exit)
+                nbytes = _lib().fwd_eb_shard_stage_bytes(self.world, self.per, 1, self.dim, wire_dtype)
+                self._stage = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                self.x.stage = self._stage.data_ptr()
+                self.x.stage_tables = 1
             if exchange == "compact":
                 # scratch of the window compaction: kept indices, sub-bag bounds, and for a mean
                 # the bags' full counts (one part per step in flight: a fold reads them beside later steps)
@@ -425,7 +441,8 @@ class TableWiseBags:
 
     def __init__(self, local_tables: dict, owner: list[int], *, dim: int, max_bags: int, group=None,
                  exchange: str = "push", wire_dtype: int = capi.F32, mode: int = capi.MODE_SUM,
-                 fixed_len: int = 0, padding_idx: int = -1, flag_from_pool: bool = False):
+                 fixed_len: int = 0, padding_idx: int = -1, flag_from_pool: bool = False,
+                 ship: bool = False, lookback: tuple[int, int] | None = None):
         import torch
         import torch.distributed as dist
         self.group = group
@@ -448,6 +465,8 @@ class TableWiseBags:
         if exchange == "push":
             self._pl = C.c_void_p()
             capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
+            if lookback:
+                capi.check(_lib().fwd_eb_pipeline_set_lookback(self._pl, *lookback))
             # the flag exchange runs on the pipeline's side stream, beside the next pooling
             self.side = torch.cuda.ExternalStream(_lib().fwd_eb_pipeline_side_stream(self._pl), device=dev)
             nbytes = _lib().fwd_eb_shard_tablewise_bytes(self.per, self.num_tables, dim, wire_dtype)
@@ -457,6 +476,11 @@ class TableWiseBags:
             self.x = make_exchange(self.buffers, self.rank, self.per, wire_dtype, self.status,
                                    layout=LAYOUT_TABLE_WISE, num_tables=self.num_tables,
                                    tickets=self.tickets)
+            self._stage = None
+            if ship and self.mine:
+                nbytes = _lib().fwd_eb_shard_stage_bytes(self.world, self.per, len(self.mine), dim, wire_dtype)
+                self._stage = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+                self.x.stage = self._stage.data_ptr()
         else:
             tl = max(1, len(self.mine))
             self.send = torch.zeros((self.per * self.world, tl, dim), dtype=torch.float32, device=dev)

@@ -37,22 +37,23 @@ extern "C" {
 
 #define FWD_EB_MAX_PEERS 16
 /* Parts of a receive buffer, used in turn (call number modulo FWD_EB_SHARD_BUFFERS), and how
- * often the pipeline makes a rank look back.  Only on every k-th call does the main stream wait
- * until this rank has folded call e-2 (which implies it has seen every rank's flag e-2); the
- * calls in between are queued without a wait on another stream.  Waiting on every call cost
- * 4 us of a 29 us step on two B200s.
+ * often and how far the pipeline makes a rank look back.  Only on every k-th call does the main
+ * stream wait, and then for this rank's fold of call e-d (which implies it has seen every rank's
+ * flag e-d); the calls in between are queued without a wait on another stream.  Waiting on every
+ * call for call e-2 cost 4 us of a 29 us step on two B200s.
  *   - Flag raised by the kernel behind the pooling grid, after this rank has folded the call
  *     before (the default): seeing flag f of rank A proves A has folded f-1; a rank B writing
- *     call g has seen flags >= g-k-1, so the part it overwrites must be older than g-k-2:
- *     k + 2 parts.  k = FWD_EB_PIPELINE_WAIT_EVERY = 6.
+ *     call g has seen flags >= g-(k-1)-d, so the part it overwrites must be older than that:
+ *     k + d parts.  Default k = 6, d = 2 (fwd_eb_pipeline_set_lookback changes them).
  *   - Flag raised by the pooling grid itself (x->tickets set): a flag no longer proves a fold;
- *     seeing flag f of A only proves A had folded f-k-1, hence 2k + 2 parts.
- *     k = FWD_EB_PIPELINE_WAIT_EVERY_TICKETS = 3.
+ *     seeing flag f of A only proves A had folded f-(k-1)-d, hence 2(k-1) + 2d parts.
+ *     k = 3, d = 2.
  * The CPU model of these rules (tests/test_exchange_protocol.py) finds no overwrite of an
  * unfolded part with them and does find one with fewer parts. */
 #define FWD_EB_PIPELINE_WAIT_EVERY 6
+#define FWD_EB_PIPELINE_WAIT_DEPTH 2
 #define FWD_EB_PIPELINE_WAIT_EVERY_TICKETS 3
-#define FWD_EB_SHARD_BUFFERS 8
+#define FWD_EB_SHARD_BUFFERS 16
 #define FWD_EB_SHARD_TIMEOUT 1
 #define FWD_EB_IPC_HANDLE_BYTES 64
 
@@ -91,6 +92,16 @@ typedef struct fwd_eb_shard_exchange {
   /* this rank's own device memory: FWD_EB_SHARD_BUFFERS words, zero-initialised once; needed
    * when raise_from_push is used (NULL otherwise) */
   uint32_t* tickets;
+  /* Shipping instead of pushing.  NULL: the pooling kernel stores its rows into the peers'
+   * buffers itself.  Otherwise local scratch of fwd_eb_shard_stage_bytes() bytes: the pooling
+   * kernel writes every row into it ([parts][world][bags_per_rank][stage_tables][dim], wire
+   * type) and fwd_eb_shard_ship, a small copy kernel on the side stream, sends each owner its
+   * rows with 16-byte peer stores.  A pooling warp cannot exit before its stores have been
+   * acknowledged; with seven of eight rows going over NVLink that wait costs a quarter of the
+   * pooling step, while local stores cost nothing and the copy runs beside the next step. */
+  void* stage;
+  int32_t stage_tables;       /* TABLE_WISE: tables this rank pools in a step (1 for row shards) */
+  int32_t stage_slot;         /* TABLE_WISE: which of them this call pools, 0..stage_tables-1 */
 } fwd_eb_shard_exchange;
 
 /* Bytes of one rank's receive buffer: row-shard layout for `world` sources, or, with
@@ -99,6 +110,18 @@ size_t fwd_eb_shard_slots_bytes(int32_t world, int64_t bags_per_rank, int32_t di
                                 int32_t wire_dtype);
 size_t fwd_eb_shard_tablewise_bytes(int64_t bags_per_rank, int32_t num_tables, int32_t dim,
                                     int32_t wire_dtype);
+
+/* Bytes of the staging scratch (fwd_eb_shard_exchange.stage); stage_tables = 1 for row shards. */
+size_t fwd_eb_shard_stage_bytes(int32_t world, int64_t bags_per_rank, int32_t stage_tables,
+                                int32_t dim, int32_t wire_dtype);
+
+/* Send what this call's fwd_eb_shard_push(es) left in x->stage to the owners' buffers: one copy
+ * kernel on `stream` (which must be ordered behind the pushes), plain 16-byte stores, owners
+ * interleaved.  `num_bags` is the batch size; table_ids[j] (TABLE_WISE, stage_tables entries) is
+ * the table whose rows sit in staged slot j.  The flag is raised by the kernel that follows
+ * (fwd_eb_shard_combine / _wait).  No multicast, no library kernel on peer memory. */
+int fwd_eb_shard_ship(const fwd_eb_shard_exchange* x, int32_t dim, int64_t num_bags,
+                      const int32_t* table_ids, void* stream);
 
 /* Pool the local row window of `p` (modes SUM or MEAN, optional weights) and push
  * each bag's partial row to its owner; `p->out` is ignored.  MEAN partials are
@@ -157,6 +180,10 @@ typedef struct fwd_eb_pipeline fwd_eb_pipeline;
 int fwd_eb_pipeline_create(fwd_eb_pipeline** out);
 void fwd_eb_pipeline_destroy(fwd_eb_pipeline* pl);
 void* fwd_eb_pipeline_side_stream(fwd_eb_pipeline* pl);
+/* Look back on every `every`-th step, for the fold of step e - `depth` (see FWD_EB_SHARD_BUFFERS;
+ * every >= 1, depth >= 2, every + depth <= FWD_EB_SHARD_BUFFERS).  Every rank must use the same
+ * values; set them before the first step. */
+int fwd_eb_pipeline_set_lookback(fwd_eb_pipeline* pl, int32_t every, int32_t depth);
 
 /* Row shards: push `p` on `main_stream`, fold on the side stream into
  * d_out[epoch % FWD_EB_SHARD_BUFFERS] (caller buffers of [bags_per_rank, dim]); *which receives that

@@ -25,7 +25,7 @@ import pytest
 
 
 def simulate(world: int, parts: int, steps: int, seed: int, wait_every: int = 1,
-             flag_from_pool: bool = False):
+             flag_from_pool: bool = False, depth: int = 2):
     rng = random.Random(seed)
     pooled = [0] * world          # last P completed per rank
     folded = [0] * world          # last X completed per rank (fold done)
@@ -39,7 +39,7 @@ def simulate(world: int, parts: int, steps: int, seed: int, wait_every: int = 1,
             e = pooled[r] + 1
             # the wait for X(e-2) is issued on every `wait_every`-th call only (1 = the pipeline as
             # built); the main stream being in order, later calls inherit the last wait
-            waited_for = e - (e % wait_every) - 2
+            waited_for = e - (e % wait_every) - depth
             if e <= steps and folded[r] >= waited_for:
                 ready.append(("P", r, e))
             e = folded[r] + 1
@@ -106,6 +106,17 @@ def test_the_pipeline_as_built_wait_every_sixth_call_eight_parts(world):
         assert state == "done" and not hazards, (seed, state, hazards[:3])
     bad = sum(bool(simulate(4, parts=7, steps=60, seed=seed, wait_every=6)[1]) for seed in range(300))
     assert bad > 0          # one part fewer does let a rank overwrite an unfolded part
+
+
+@pytest.mark.parametrize("every,depth", [(8, 8), (4, 4), (12, 4), (2, 6)])
+def test_lookback_every_k_calls_for_call_e_minus_d_needs_k_plus_d_parts(every, depth):
+    """fwd_eb_pipeline_set_lookback: any (every, depth) is safe with every + depth parts."""
+    for seed in range(150):
+        state, hazards = simulate(4, parts=every + depth, steps=80, seed=seed, wait_every=every, depth=depth)
+        assert state == "done" and not hazards, (seed, state, hazards[:3])
+    bad = sum(bool(simulate(4, parts=every + depth - 1, steps=80, seed=seed, wait_every=every, depth=depth)[1])
+              for seed in range(300))
+    assert bad > 0
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])

@@ -31,15 +31,17 @@ def _worker(rank, world, port, tmp):
     local = torch.from_numpy(table[lo:lo + n]).to(dev)
     shards = [fd.shard_rows(rows, world, r) for r in range(world)]
     for exchange, wire in (("compact", capi.F32), ("compact", capi.F16), ("compact+tickets", capi.F32),
+                           ("compact+ship", capi.F32), ("compact+ship", capi.F16), ("push+ship", capi.F32),
                            ("push", capi.F32), ("push", capi.F16), ("push+tickets", capi.F16),
                            ("stage", capi.F32),
                            ("stage", capi.F16), ("a2a", capi.F32), ("nccl", capi.F32)):
         tickets = exchange.endswith("+tickets")      # the pooling grid raises the flag itself
+        ship = exchange.endswith("+ship")            # rows staged locally, sent by the copy kernel
         exchange = exchange.split("+")[0]
         for mode in (capi.MODE_SUM, capi.MODE_MEAN):
             bag = fd.RowShardedBag(local, lo, mode=mode, max_bags=nb, exchange=exchange,
                                    wire_dtype=wire, padding_idx=3, max_indices=80 * nb,
-                                   flag_from_pool=tickets)
+                                   flag_from_pool=tickets, ship=ship)
             for step in range(20 if exchange in ("compact", "push") else 3):   # beyond the eight buffer parts
                 brng = np.random.default_rng(100 + step)
                 bags = workloads.ragged_bags(rows, brng.integers(0, 80, nb), brng)
@@ -98,11 +100,11 @@ def _worker(rank, world, port, tmp):
     owner = fd.place_tables([1] * ntab, world)
     trng = np.random.default_rng(17)
     tables = [trng.standard_normal((3000 + 100 * t, dim2)).astype(np.float32) for t in range(ntab)]
-    for exchange in ("push", "push+tickets", "nccl"):
+    for exchange in ("push", "push+tickets", "push+ship", "nccl"):
         mine_t = [t for t in range(ntab) if owner[t] == rank]
         tw = fd.TableWiseBags({t: torch.from_numpy(tables[t]).to(dev) for t in mine_t}, owner,
                               dim=dim2, max_bags=nb2, exchange=exchange.split("+")[0], fixed_len=L,
-                              flag_from_pool=exchange.endswith("+tickets"))
+                              flag_from_pool=exchange.endswith("+tickets"), ship=exchange.endswith("+ship"))
         for step in range(12 if exchange != "nccl" else 2):
             irng = np.random.default_rng(200 + step)
             idx = [irng.integers(0, tables[t].shape[0], (nb2, L)).astype(np.int32) for t in range(ntab)]

@@ -170,6 +170,80 @@ def test_row_shard_compacted_push_equals_the_replicated_scan(wire, mode):
     assert all(int(k.item()) == 0 for k in keep if k.numel() == 1 and k.dtype == torch.int32)
 
 
+@pytest.mark.parametrize("wire", [capi.F32, capi.F16])
+def test_staged_rows_shipped_by_the_copy_kernel_equal_the_fused_push(wire):
+    """x->stage set: the pooling kernel writes every partial row locally and fwd_eb_shard_ship sends
+    them on.  Row shards (3 ranks, the last one owning fewer bags) and table-wise placement
+    (5 tables on 2 ranks): the owners' results are those of the fused push, bit for bit."""
+    rng = np.random.default_rng(61)
+    world, rows, dim, nb = 3, 6000, 64, 1000
+    table = rng.standard_normal((rows, dim)).astype(np.float16)
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, wire)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    shards = [fd.shard_rows(rows, world, r) for r in range(world)]
+    tabs = [_cuda(table[lo:lo + n]) for lo, n in shards]
+    stage_bytes = lib.fwd_eb_shard_stage_bytes(world, per, 1, dim, wire)
+    for epoch in (1, 2, 9):                          # 9: the part after a wrap of the eight
+        bags = workloads.ragged_bags(rows, rng.integers(0, 60, nb), rng)
+        i, o = _cuda(bags.indices), _cuda(bags.offsets)
+        for r in range(world):
+            stage = torch.zeros(stage_bytes, dtype=torch.uint8, device=DEV)
+            keep.append(stage)
+            xs[r].epoch = epoch
+            xs[r].stage = stage.data_ptr()
+            xs[r].stage_tables = 1
+            p = capi.make_params(tabs[r], i, o, out=tabs[r][:1], mode=capi.MODE_SUM, row_lo=shards[r][0])
+            capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+            capi.check(lib.fwd_eb_shard_ship(C.byref(xs[r]), dim, nb, None, stream))
+        for r in range(world):
+            capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
+        parts = np.stack([O.pool(table[lo:lo + n], bags.indices, bags.offsets, mode=O.MODE_SUM, row_lo=lo,
+                                 out_dtype=np.float32) for lo, n in shards])
+        if wire == capi.F16:
+            parts = parts.astype(np.float16)
+        expect = O.combine_partials(parts, np.float32)
+        for r in range(world):
+            lo, mine = fd.owned_bags(nb, world, r)
+            out = torch.empty((per, dim), device=DEV)
+            capi.check(lib.fwd_eb_shard_combine(C.byref(xs[r]), dim, mine, out.data_ptr(), capi.F32, stream))
+            torch.cuda.synchronize()
+            assert np.array_equal(out[:mine].cpu().numpy(), expect[lo:lo + mine])
+    # table-wise: tables 0, 2, 4 on rank 0 and 1, 3 on rank 1
+    world, ntab, L, dim, nb = 2, 5, 6, 32, 999
+    owner = [0, 1, 0, 1, 0]
+    tables = [rng.standard_normal((800 + 50 * t, dim)).astype(np.float32) for t in range(ntab)]
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep2 = _setup(world, per, dim, capi.F32, layout=fd.LAYOUT_TABLE_WISE, num_tables=ntab)
+    idx = [rng.integers(0, tables[t].shape[0], (nb, L)).astype(np.int32) for t in range(ntab)]
+    for r in range(world):
+        mine_t = [t for t in range(ntab) if owner[t] == r]
+        stage = torch.zeros(lib.fwd_eb_shard_stage_bytes(world, per, len(mine_t), dim, capi.F32),
+                            dtype=torch.uint8, device=DEV)
+        keep2.append(stage)
+        xs[r].epoch = 1
+        xs[r].stage = stage.data_ptr()
+        xs[r].stage_tables = len(mine_t)
+        for j, t in enumerate(mine_t):
+            tt, ii = _cuda(tables[t]), _cuda(idx[t])
+            keep2 += [tt, ii]
+            xs[r].table_index, xs[r].stage_slot = t, j
+            p = capi.make_params(tt, ii, None, out=tt[:1], mode=capi.MODE_SUM, fixed_len=L)
+            capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+        ids = (C.c_int32 * len(mine_t))(*mine_t)
+        capi.check(lib.fwd_eb_shard_ship(C.byref(xs[r]), dim, nb, ids, stream))
+    for r in range(world):
+        capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
+    expect = np.stack([O.pool(tables[t], idx[t], fixed_len=L) for t in range(ntab)], axis=1)
+    for r in range(world):
+        res = C.c_void_p()
+        capi.check(lib.fwd_eb_shard_wait(C.byref(xs[r]), dim, C.byref(res), stream))
+        torch.cuda.synchronize()
+        lo, mine = fd.owned_bags(nb, world, r)
+        got = torch.as_tensor(fd._DeviceView(res.value, (per, ntab, dim), "<f4"), device="cuda")
+        assert np.array_equal(got[:mine].cpu().numpy(), expect[lo:lo + mine])
+
+
 def test_row_shard_config5_geometry_small_window():
     """Config 5's numbers on a small physical window: logical rows up to 10^9 (int32 indices near
     2^30), a shard whose row_lo lies beyond 5*10^8, G = 8 windows of which this GPU holds one.
