@@ -54,6 +54,8 @@ SIGNATURES = {
     "fwd_eb_forward": (C.c_int, [C.POINTER(Params), C.c_void_p]),
     "fwd_eb_workspace_size": (C.c_size_t, [C.POINTER(Params)]),
     "fwd_eb_pick_strategy": (C.c_int, [C.POINTER(Params)]),
+    "fwd_eb_forward_static_scratch": (C.c_int, [C.POINTER(Params), C.c_void_p]),
+    "fwd_eb_static_scratch_prepare": (C.c_int, []),
     "fwd_eb_compact_window": (C.c_int, [C.POINTER(Params), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_void_p]),
     "fwd_eb_launch_count": (C.c_uint64, []),

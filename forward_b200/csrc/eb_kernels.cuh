@@ -252,6 +252,7 @@ struct Accum {
   float v[CPL][VE];
   int counted;  // non-padding indices seen (inside or outside the table window)
   bool have;    // at least one row was folded in
+  bool seeded;  // max only: the accumulators start at -inf and every row is compared strictly
 };
 
 // One lane's share of walking indices [start, end) of a bag.  All 32 lanes of
@@ -333,7 +334,8 @@ __device__ __forceinline__ void pool_range(const PoolArgs& a, long long start, l
       if (ok[u]) {
 #pragma unroll
         for (int c = 0; c < CPL; ++c) {
-          if (chunk_ok[c]) fold_chunk<OP>(s.v[c], val[u][c], OP == kOpWeighted ? w[u] : 1.0f, !s.have);
+          if (chunk_ok[c])
+            fold_chunk<OP>(s.v[c], val[u][c], OP == kOpWeighted ? w[u] : 1.0f, !s.have && !s.seeded);
         }
         s.have = true;
       }
@@ -544,6 +546,29 @@ __device__ __forceinline__ void clear(Accum<CPL, VE>& s) {
     for (int e = 0; e < VE; ++e) s.v[c][e] = 0.0f;
   s.counted = 0;
   s.have = false;
+  s.seeded = false;
+}
+
+// MAX over a slice of a bag that is not the bag's first slice: torch's sequential rule takes the
+// bag's first entry as is (a NaN there sticks) and every later entry only when strictly
+// greater (a later NaN is ignored).  A slice that took ITS first row as is would keep a NaN
+// that torch ignores, and the fold across slices would then drop the whole slice, larger values
+// included.  Such a slice therefore starts from -inf and compares every row strictly.
+// (One corner stays: a NaN that is the bag's first non-padding entry but sits in a later slice,
+// every slice before it holding padding only, is ignored where torch keeps it.)
+template <int CPL, int VE, typename TW>
+__device__ __forceinline__ void seed_max_slice(Accum<CPL, VE>& s) {
+#pragma unroll
+  for (int c = 0; c < CPL; ++c) {
+    if (sizeof(TW) == 2 && VE == 8) {  // fp16 rows: four packed pairs of -inf halves
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s.v[c][e] = __uint_as_float(0xFC00FC00u);
+    } else {
+#pragma unroll
+      for (int e = 0; e < VE; ++e) s.v[c][e] = -INFINITY;
+    }
+  }
+  s.seeded = true;
 }
 
 // ---- strategy 1: one lane group per bag -------------------------------------
@@ -707,6 +732,7 @@ eb_pool_cta_kernel(const PoolArgs a) {
 
   Accum<CPL, VE> s;
   clear(s);
+  if (OP == kOpMax && slot > 0) seed_max_slice<CPL, VE, TW>(s);
   pool_range<TW, VE, CPL, OP, U, IPL>(a, start, end, chunk0, s);
 
   float* part = smem;

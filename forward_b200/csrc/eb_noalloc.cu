@@ -71,3 +71,8 @@ extern "C" int fwd_eb_forward_static_scratch(const fwd_eb_params* p, void* strea
   q.workspace_bytes = FWD_EB_STATIC_SCRATCH_BYTES;
   return fwd_eb_forward(&q, stream);
 }
+
+extern "C" int fwd_eb_static_scratch_prepare(void) {
+  void* scratch = nullptr;
+  return scratch_address(&scratch);
+}

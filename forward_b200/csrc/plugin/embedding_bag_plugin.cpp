@@ -8,6 +8,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <map>
 
 #include "blob_io.h"
 #include "fwd_eb.h"
@@ -44,13 +45,83 @@ uint32_t PackFlags(const EmbeddingBagOptions& o) {
          (o.include_last_offset ? kIncludeLast : 0u) | (o.has_per_sample_weights ? kWeighted : 0u);
 }
 
-size_t TableBytes(int dim, int count, bool half) {
+size_t TableBytes(int dim, int64_t count, bool half) {
   return (size_t)dim * (size_t)count * (half ? 2u : 4u);
 }
 
 // Bytes of the float vector in the blob: fp16 tables ride in it padded to whole floats.
-size_t BlobFloatCount(int dim, int count, bool half) {
+size_t BlobFloatCount(int dim, int64_t count, bool half) {
   return (TableBytes(dim, count, half) + 3) / 4;
+}
+
+// Blob layout "002" (tables that stay outside the plugin).  It opens with an int that no "001"
+// blob can open with (there it is `dim`, positive):
+//   int32 -2 | char[4] "002" | int32 dim | int64 count | int64 data_offset | int32 op |
+//   uint32 flags | int64 padding_idx | uint32 key length | key bytes
+constexpr int kLayout002 = -2;
+
+// ---- registered external tables -----------------------------------------------------------
+struct ExternalTable {
+  const void* ptr;
+  int device;
+  long long rows;
+  int dim;
+  bool half;
+};
+std::mutex g_registry_lock;
+std::map<std::string, ExternalTable>& Registry() {
+  static std::map<std::string, ExternalTable> r;
+  return r;
+}
+bool FindExternal(const std::string& key, ExternalTable* out) {
+  std::lock_guard<std::mutex> hold(g_registry_lock);
+  auto it = Registry().find(key);
+  if (it == Registry().end()) return false;
+  *out = it->second;
+  return true;
+}
+
+// ---- one user of the library's built-in split scratch at a time, per GPU ---------------------
+// fwd_eb_forward_static_scratch keeps its partial sums in ONE array per GPU.  TensorRT may run
+// several execution contexts (each with its own clone of this plugin) or auxiliary streams at
+// once, so calls are chained through an event per GPU: a call waits for the previous user's
+// kernels, and leaves its own mark behind.  The lock covers wait + launch + record, so two host
+// threads cannot both wait for the same predecessor.
+std::mutex g_scratch_lock;
+cudaEvent_t g_scratch_event[64] = {};
+
+cudaEvent_t ScratchEvent(int dev) {  // call with g_scratch_lock held
+  if (dev < 0 || dev >= 64) return nullptr;
+  if (!g_scratch_event[dev] &&
+      cudaEventCreateWithFlags(&g_scratch_event[dev], cudaEventDisableTiming) != cudaSuccess) {
+    cudaGetLastError();
+    g_scratch_event[dev] = nullptr;
+  }
+  return g_scratch_event[dev];
+}
+
+int OrderedStaticScratch(fwd_eb_params* p, cudaStream_t stream) {
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  int dev = -1;
+  if (cudaStreamIsCapturing(stream, &capturing) != cudaSuccess || cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    capturing = cudaStreamCaptureStatusActive;  // cannot tell: take the path that needs no ordering
+  }
+  if (capturing == cudaStreamCaptureStatusNone) {
+    std::lock_guard<std::mutex> hold(g_scratch_lock);
+    cudaEvent_t ev = ScratchEvent(dev);
+    if (ev && cudaStreamWaitEvent(stream, ev, 0) == cudaSuccess) {
+      const int rc = fwd_eb_forward_static_scratch(p, stream);
+      cudaEventRecord(ev, stream);
+      return rc;
+    }
+    cudaGetLastError();
+  }
+  // A stream that is being captured cannot wait for work outside its graph, and the array's
+  // address must not be looked up for the first time inside a capture: one CTA per bag needs
+  // no scratch at all.
+  p->strategy = FWD_EB_STRATEGY_CTA;
+  return fwd_eb_forward(p, stream);
 }
 
 }  // namespace
@@ -86,7 +157,13 @@ EmbeddingTable::EmbeddingTable(const void* host_bytes, size_t num_bytes, bool ha
   host_.assign(p, p + num_bytes);
 }
 
+EmbeddingTable::EmbeddingTable(const void* device_table, int device, bool half, const std::string& key)
+    : half_(half), external_(true), key_(key) {
+  device_.emplace_back(device, const_cast<void*>(device_table));
+}
+
 EmbeddingTable::~EmbeddingTable() {
+  if (external_) return;  // the caller's memory
   int prev = -1;
   cudaGetDevice(&prev);
   for (auto& entry : device_) {
@@ -105,6 +182,7 @@ const void* EmbeddingTable::Device() noexcept {
   for (auto& entry : device_) {
     if (entry.first == dev) return entry.second;
   }
+  if (external_) return nullptr;  // registered for another GPU
   void* d = nullptr;
   const size_t bytes = host_.empty() ? 16 : host_.size();
   if (cudaMalloc(&d, bytes) != cudaSuccess) {
@@ -141,15 +219,74 @@ EmbeddingBagPlugin::EmbeddingBagPlugin(const void* data, int dim, int count, int
   }
 }
 
+EmbeddingBagPlugin::EmbeddingBagPlugin(const std::string& key, int dim, int64_t count, int64_t offset,
+                                       ReduceOperation op, const EmbeddingBagOptions& options)
+    : opt_(options), op_(op), dim_(dim), count_(count), data_offset_(offset) {
+  ExternalTable ext;
+  valid_ = dim > 0 && count >= 0 && FindExternal(key, &ext) && ext.dim == dim && ext.rows >= count &&
+           ext.half == opt_.half_table;
+  if (valid_) {
+    table_ = std::make_shared<EmbeddingTable>(ext.ptr, ext.device, ext.half, key);
+  } else {
+    LogError("EmbeddingBag_TRT: external weights are not registered under that name, or their "
+             "geometry (dim, rows, element type) does not match the layer");
+  }
+}
+
 EmbeddingBagPlugin::EmbeddingBagPlugin(void const* serialData, size_t serialLength) {
-  // reference order (.cpp:44-51): dim, count, data_offset, op, vector<float>
   blob::Reader in(serialData, serialLength);
+  int first = 0;
+  {
+    blob::Reader peek = in;
+    peek.value(&first);
+  }
+  if (first == kLayout002) {
+    char tag[4] = {0, 0, 0, 0};
+    int op = 0;
+    uint32_t flags = 0, keylen = 0;
+    int64_t pad = -1;
+    in.value(&first);
+    in.value(&tag);
+    in.value(&dim_);
+    in.value(&count_);
+    in.value(&data_offset_);
+    in.value(&op);
+    in.value(&flags);
+    in.value(&pad);
+    in.value(&keylen);
+    std::string key;
+    std::vector<char> raw;
+    bool ok = in.ok() && std::memcmp(tag, "002", 4) == 0 && keylen <= 4096 && keylen <= in.left();
+    if (ok) {
+      const char* base = static_cast<const char*>(serialData) + (serialLength - in.left());
+      key.assign(base, base + keylen);
+    }
+    op_ = static_cast<ReduceOperation>(op);
+    opt_.half_table = flags & kHalfTable;
+    opt_.half_output = flags & kHalfOutput;
+    opt_.include_last_offset = flags & kIncludeLast;
+    opt_.has_per_sample_weights = flags & kWeighted;
+    opt_.padding_idx = pad;
+    ExternalTable ext;
+    valid_ = ok && dim_ > 0 && count_ >= 0 && FindExternal(key, &ext) && ext.dim == dim_ &&
+             ext.rows >= count_ && ext.half == opt_.half_table;
+    if (valid_) {
+      table_ = std::make_shared<EmbeddingTable>(ext.ptr, ext.device, ext.half, key);
+    } else {
+      LogError("EmbeddingBag_TRT: \"002\" blob is damaged, or the weights it names are not registered "
+               "(fwd_eb_plugin_register_weights) with the geometry it records");
+    }
+    return;
+  }
+  // reference order (.cpp:44-51): dim, count, data_offset, op, vector<float>
   std::vector<char> payload;
-  int op = 0;
+  int op = 0, count32 = 0, offset32 = 0;
   in.value(&dim_);
-  in.value(&count_);
-  in.value(&data_offset_);
+  in.value(&count32);
+  in.value(&offset32);
   in.value(&op);
+  count_ = count32;
+  data_offset_ = offset32;
   in.counted(&payload, sizeof(float));
   op_ = static_cast<ReduceOperation>(op);
   uint32_t magic = 0, flags = 0;
@@ -249,6 +386,17 @@ void EmbeddingBagPlugin::configurePlugin(const nvinfer1::DynamicPluginTensorDesc
   if (!valid_ || d_data_) return;
   d_data_ = table_->Device();
   if (!d_data_) LogError("EmbeddingBag_TRT: could not place the table on the device");
+  // Calls with a few very long bags go through the library's built-in scratch array.  Its device
+  // address is looked up on first use, which must not happen inside a stream capture: do it
+  // here, where TensorRT is still setting up, together with the event that orders its users.
+  if (fwd_eb_static_scratch_prepare() == 0) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) == cudaSuccess) {
+      std::lock_guard<std::mutex> hold(g_scratch_lock);
+      ScratchEvent(dev);
+    }
+  }
+  cudaGetLastError();
 }
 
 size_t EmbeddingBagPlugin::getWorkspaceSize(const nvinfer1::PluginTensorDesc*, int,
@@ -316,8 +464,8 @@ int EmbeddingBagPlugin::enqueue(const nvinfer1::PluginTensorDesc* inputDesc,
   if (op_ != ReduceOperation::GATHER && fwd_eb_workspace_size(&p) > 0 &&
       fwd_eb_workspace_size(&p) <= FWD_EB_STATIC_SCRATCH_BYTES) {
     // few, very long bags: TensorRT gave no workspace (getWorkspaceSize is 0), so split through
-    // the library's built-in scratch
-    rc = fwd_eb_forward_static_scratch(&p, stream);
+    // the library's built-in scratch, one user at a time per GPU
+    rc = OrderedStaticScratch(&p, stream);
   } else {
     rc = fwd_eb_forward(&p, stream);
   }
@@ -325,6 +473,9 @@ int EmbeddingBagPlugin::enqueue(const nvinfer1::PluginTensorDesc* inputDesc,
 }
 
 size_t EmbeddingBagPlugin::getSerializationSize() const noexcept {
+  if (table_ && table_->External())
+    return sizeof(int) + 4 + sizeof(int) + 2 * sizeof(int64_t) + sizeof(int) + sizeof(uint32_t) +
+           sizeof(int64_t) + sizeof(uint32_t) + table_->Key().size();
   return 4 * sizeof(int) + sizeof(size_t) +
          BlobFloatCount(dim_, count_, opt_.half_table) * sizeof(float) + 2 * sizeof(uint32_t) +
          sizeof(int64_t);
@@ -333,9 +484,23 @@ size_t EmbeddingBagPlugin::getSerializationSize() const noexcept {
 void EmbeddingBagPlugin::serialize(void* buffer) const noexcept {
   // reference layout first (.cpp:196-202) so its reader and ours agree on the common part
   blob::Writer out(buffer);
+  if (table_ && table_->External()) {  // layout "002": the table's name instead of its bytes
+    const char tag[4] = {'0', '0', '2', 0};
+    out.value(kLayout002);
+    out.value(tag);
+    out.value(dim_);
+    out.value(count_);
+    out.value(data_offset_);
+    out.value(static_cast<int>(op_));
+    out.value(PackFlags(opt_));
+    out.value(opt_.padding_idx);
+    out.value(static_cast<uint32_t>(table_->Key().size()));
+    out.bytes(table_->Key().data(), table_->Key().size());
+    return;
+  }
   out.value(dim_);
-  out.value(count_);
-  out.value(data_offset_);
+  out.value(static_cast<int>(count_));        // an embedded table never exceeds the int the creator took
+  out.value(static_cast<int>(data_offset_));
   out.value(static_cast<int>(op_));
   const size_t floats = BlobFloatCount(dim_, count_, opt_.half_table);
   const size_t bytes = table_ ? table_->Host().size() : 0;
@@ -385,6 +550,8 @@ EmbeddingBagPluginCreator::EmbeddingBagPluginCreator() {
   mPluginAttributes.emplace_back(PluginField("include_last_offset", nullptr, PluginFieldType::kINT32, 1));
   mPluginAttributes.emplace_back(PluginField("per_sample_weights", nullptr, PluginFieldType::kINT32, 1));
   mPluginAttributes.emplace_back(PluginField("half_output", nullptr, PluginFieldType::kINT32, 1));
+  mPluginAttributes.emplace_back(PluginField("external_weights", nullptr, PluginFieldType::kCHAR, 1));
+  mPluginAttributes.emplace_back(PluginField("half_table", nullptr, PluginFieldType::kINT32, 1));
   mFC.nbFields = (int)mPluginAttributes.size();
   mFC.fields = mPluginAttributes.data();
 }
@@ -401,6 +568,8 @@ nvinfer1::IPluginV2DynamicExt* EmbeddingBagPluginCreator::createPlugin(
   const void* data = nullptr;
   bool have[5] = {false, false, false, false, false};
   EmbeddingBagOptions opt;
+  std::string external_key;
+  bool half_table_field = false;
   auto int_field = [](const nvinfer1::PluginField& f, int* out) {
     if (f.type != nvinfer1::PluginFieldType::kINT32 || !f.data) return false;
     *out = *static_cast<const int*>(f.data);
@@ -440,10 +609,25 @@ nvinfer1::IPluginV2DynamicExt* EmbeddingBagPluginCreator::createPlugin(
     } else if (!std::strcmp(f.name, "half_output")) {
       if (!int_field(f, &v)) return nullptr;
       opt.half_output = v != 0;
+    } else if (!std::strcmp(f.name, "external_weights")) {
+      // the name a device table was registered under: the plugin holds no copy of the table
+      if (f.type != nvinfer1::PluginFieldType::kCHAR || !f.data || f.length <= 0 || f.length > 4096) {
+        LogError("EmbeddingBag_TRT: field 'external_weights' must be a CHAR string");
+        return nullptr;
+      }
+      external_key.assign(static_cast<const char*>(f.data), (size_t)f.length);
+      while (!external_key.empty() && external_key.back() == '\0') external_key.pop_back();
+    } else if (!std::strcmp(f.name, "half_table")) {
+      if (!int_field(f, &v)) return nullptr;
+      half_table_field = v != 0;
     } else {
       LogError("EmbeddingBag_TRT: unknown creator field");  // the reference asserts (.cpp:286-288)
       return nullptr;
     }
+  }
+  if (!external_key.empty()) {
+    have[4] = true;  // no table bytes travel with an external table
+    opt.half_table = half_table_field;
   }
   for (bool h : have) {
     if (!h) {
@@ -462,8 +646,11 @@ nvinfer1::IPluginV2DynamicExt* EmbeddingBagPluginCreator::createPlugin(
     LogError("EmbeddingBag_TRT: per_sample_weights need op 0 (sum)");
     return nullptr;
   }
-  auto* obj = new (std::nothrow)
-      EmbeddingBagPlugin(data, dim, count, offset, static_cast<ReduceOperation>(op), opt);
+  auto* obj = external_key.empty()
+                  ? new (std::nothrow) EmbeddingBagPlugin(data, dim, count, offset,
+                                                          static_cast<ReduceOperation>(op), opt)
+                  : new (std::nothrow) EmbeddingBagPlugin(external_key, dim, count, offset,
+                                                          static_cast<ReduceOperation>(op), opt);
   if (!obj) return nullptr;
   if (!obj->Valid()) {
     obj->destroy();
@@ -488,3 +675,23 @@ nvinfer1::IPluginV2DynamicExt* EmbeddingBagPluginCreator::deserializePlugin(
 }
 
 FWD_TRT_NAMESPACE_END
+
+extern "C" int fwd_eb_plugin_register_weights(const char* key, const void* d_table, int device,
+                                              long long num_rows, int dim, int half) {
+  using namespace fwd::trt_;
+  if (!key || !*key || !d_table || device < 0 || num_rows < 0 || dim <= 0) return -1;
+  std::lock_guard<std::mutex> hold(g_registry_lock);
+  auto it = Registry().find(key);
+  if (it != Registry().end() &&
+      (it->second.rows != num_rows || it->second.dim != dim || it->second.half != (half != 0)))
+    return -2;  // the name is taken by a table of another shape
+  Registry()[key] = ExternalTable{d_table, device, num_rows, dim, half != 0};
+  return 0;
+}
+
+extern "C" int fwd_eb_plugin_unregister_weights(const char* key) {
+  using namespace fwd::trt_;
+  if (!key) return -1;
+  std::lock_guard<std::mutex> hold(g_registry_lock);
+  return Registry().erase(key) ? 0 : -1;
+}

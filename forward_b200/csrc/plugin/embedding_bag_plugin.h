@@ -10,6 +10,12 @@
 //   * fp16 tables, padding_idx, include_last_offset and per_sample_weights (a third input)
 //     are honoured; they travel as optional creator fields and as a trailer after the
 //     reference's blob layout, so a blob written by the reference still loads;
+//   * a table can stay outside the plugin: the host registers a device table under a name
+//     (fwd_eb_plugin_register_weights) and the creator field `external_weights` / blob layout
+//     "002" carry only that name plus 64-bit sizes, so a plan stays small and a table is never
+//     copied through the host (the reference embeds the table in the plan and holds it in a
+//     host vector, embedding_bag_plugin.cpp:37-51,191-202; common/fwd_weights.h:172 counts its
+//     bytes in an int);
 //   * nothing aborts: enqueue / initialize return non-zero and log through getLogger().
 #pragma once
 
@@ -55,10 +61,13 @@ void EmbeddingBag(const int* input, const int* input_2, float* output, int input
                   int block_size, const float* data, int count, int dim, int data_offset,
                   int op_type, const cudaStream_t& stream);
 
-// Host bytes of a table plus its device copies, shared by a plugin and its clones.
+// A table shared by a plugin and its clones: host bytes plus device copies made on demand, or a
+// caller-owned device table that was registered under a name (no host bytes, nothing to free).
 class EmbeddingTable {
  public:
   EmbeddingTable(const void* host_bytes, size_t num_bytes, bool half);
+  // external: `device_table` lives on GPU `device` and stays the caller's
+  EmbeddingTable(const void* device_table, int device, bool half, const std::string& key);
   ~EmbeddingTable();
   EmbeddingTable(const EmbeddingTable&) = delete;
   EmbeddingTable& operator=(const EmbeddingTable&) = delete;
@@ -68,10 +77,14 @@ class EmbeddingTable {
   const std::vector<char>& Host() const { return host_; }
   bool Half() const { return half_; }
   int Uploads() const { return uploads_; }
+  bool External() const { return external_; }
+  const std::string& Key() const { return key_; }
 
  private:
   std::vector<char> host_;
   bool half_;
+  bool external_{false};
+  std::string key_;
   std::mutex lock_;
   std::vector<std::pair<int, void*>> device_;  // (ordinal, pointer)
   int uploads_{0};
@@ -94,7 +107,10 @@ class EmbeddingBagPlugin final : public nvinfer1::IPluginV2DynamicExt {
   // extended constructor: `data` holds dim*count elements of the table's element type
   EmbeddingBagPlugin(const void* data, int dim, int count, int offset, ReduceOperation op,
                      const EmbeddingBagOptions& options);
-  // from an engine blob
+  // external table: rows [offset, offset + count) of the logical table, registered under `key`
+  EmbeddingBagPlugin(const std::string& key, int dim, int64_t count, int64_t offset, ReduceOperation op,
+                     const EmbeddingBagOptions& options);
+  // from an engine blob (layout "001" with or without trailer, or "002")
   EmbeddingBagPlugin(void const* blob, size_t blob_bytes);
   ~EmbeddingBagPlugin() noexcept override;
 
@@ -142,8 +158,8 @@ class EmbeddingBagPlugin final : public nvinfer1::IPluginV2DynamicExt {
   EmbeddingBagOptions opt_;
   ReduceOperation op_{ReduceOperation::SUM};
   int dim_{0};
-  int count_{0};
-  int data_offset_{0};
+  int64_t count_{0};        // rows held (the reference's int `count_`)
+  int64_t data_offset_{0};  // logical id of row 0 (the reference's int `data_offset_`)
   bool valid_{true};
   std::string namespace_;
 };
@@ -166,3 +182,14 @@ class EmbeddingBagPluginCreator : public nvinfer1::plugin::BaseCreator {
 };
 
 FWD_TRT_NAMESPACE_END
+
+extern "C" {
+// Tables that stay outside the plugin.  Register a device table (row-major [num_rows, dim], fp32
+// or fp16, on GPU `device`, owned by the caller, alive as long as any plugin uses it) under a
+// name before createPlugin / deserializePlugin meets that name in the `external_weights` field or
+// in a "002" blob.  0 on success; a name can be registered again with identical geometry (the
+// pointer is replaced).  Unregister when no plugin uses the name any more.
+int fwd_eb_plugin_register_weights(const char* key, const void* d_table, int device, long long num_rows,
+                                   int dim, int half);
+int fwd_eb_plugin_unregister_weights(const char* key);
+}

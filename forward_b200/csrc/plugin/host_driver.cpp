@@ -106,6 +106,28 @@ fwd_eb_host* fwd_eb_host_build(const void* table, int half_table, int count, int
                                 weights_dims);
 }
 
+// Build around a table that stays outside the plugin: `key` names a device table registered with
+// fwd_eb_plugin_register_weights.
+fwd_eb_host* fwd_eb_host_build_external(const char* key, int half_table, int count, int dim, int offset,
+                                        int op, long long padding_idx, int include_last_offset,
+                                        int half_output, int idx_rank, const int* idx_dims, int off_rank,
+                                        const int* off_dims, int weights_rank, const int* weights_dims) {
+  if (!key) return nullptr;
+  auto desc = std::make_shared<TrtEmbeddingBagDesc>();
+  desc->dim = dim;
+  desc->count = count;
+  desc->offset = offset;
+  desc->op = op;
+  desc->padding_idx = padding_idx;
+  desc->include_last_offset = include_last_offset != 0;
+  desc->has_per_sample_weights = weights_rank > 0;
+  desc->half_output = half_output != 0;
+  desc->data.SetType(half_table ? nvinfer1::DataType::kHALF : nvinfer1::DataType::kFLOAT);
+  desc->external_weights = key;
+  return fwd_eb_host_build_desc(desc.get(), idx_rank, idx_dims, off_rank, off_dims, weights_rank,
+                                weights_dims);
+}
+
 // The same from a description some parser produced (`embedding_bag_desc` is a
 // fwd::TrtEmbeddingBagDesc*; the torch parser slice enters here).
 fwd_eb_host* fwd_eb_host_build_desc(const void* embedding_bag_desc, int idx_rank, const int* idx_dims,

@@ -43,9 +43,17 @@ class TLayerCreator<TrtEmbeddingBagDesc> : public ILayerCreator {
     fields.emplace_back("count", &desc->count, nvinfer1::PluginFieldType::kINT32, 1);
     fields.emplace_back("offset", &desc->offset, nvinfer1::PluginFieldType::kINT32, 1);
     fields.emplace_back("op", &desc->op, nvinfer1::PluginFieldType::kINT32, 1);
-    fields.emplace_back("data", desc->data.Data(),
-                        half ? nvinfer1::PluginFieldType::kFLOAT16 : nvinfer1::PluginFieldType::kFLOAT32,
-                        desc->dim * desc->count);
+    const int half_table = half ? 1 : 0;
+    if (desc->external_weights.empty()) {
+      fields.emplace_back("data", desc->data.Data(),
+                          half ? nvinfer1::PluginFieldType::kFLOAT16 : nvinfer1::PluginFieldType::kFLOAT32,
+                          desc->dim * desc->count);
+    } else {
+      // the table was registered on the device under a name: only the name goes into the plugin
+      fields.emplace_back("external_weights", desc->external_weights.c_str(),
+                          nvinfer1::PluginFieldType::kCHAR, static_cast<int>(desc->external_weights.size()));
+      if (half_table) fields.emplace_back("half_table", &half_table, nvinfer1::PluginFieldType::kINT32, 1);
+    }
     if (padding >= 0) fields.emplace_back("padding_idx", &padding, nvinfer1::PluginFieldType::kINT32, 1);
     if (last) fields.emplace_back("include_last_offset", &last, nvinfer1::PluginFieldType::kINT32, 1);
     if (weighted) fields.emplace_back("per_sample_weights", &weighted, nvinfer1::PluginFieldType::kINT32, 1);

@@ -72,6 +72,9 @@ struct TrtEmbeddingBagDesc : TrtLayerDesc {
   bool include_last_offset{false};
   bool has_per_sample_weights{false};
   bool half_output{false};  // emit kHALF like torch does for fp16 tables (default kFLOAT as the reference)
+  // Non-empty: the table stays outside the plan.  It is the name a device table was registered
+  // under (fwd_eb_plugin_register_weights); `data` then carries no bytes, only its Type().
+  std::string external_weights;
 };
 
 FWD_NAMESPACE_END

@@ -206,6 +206,12 @@ size_t fwd_eb_workspace_size(const fwd_eb_params* p);
 #define FWD_EB_STATIC_SCRATCH_BYTES (8u << 20)
 int fwd_eb_forward_static_scratch(const fwd_eb_params* p, void* stream);
 
+/* Do fwd_eb_forward_static_scratch's one-time set-up for the current device now (look up and
+ * cache the array's device address), so that the first real call can come at any time — inside
+ * a stream capture, for instance.  Launches nothing and allocates nothing; 0 on success.  No
+ * counterpart in the reference. */
+int fwd_eb_static_scratch_prepare(void);
+
 /*
  * Window compaction: run the table-window / padding filter of `p` once, as a
  * streaming pass, instead of inside the pooling loop.  The reference tests every

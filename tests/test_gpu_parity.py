@@ -392,3 +392,36 @@ def test_int32_filter_edges_negative_indices_and_window_origin():
             got64 = gpu_pool(table, idx.astype(np.int64), off.astype(np.int64), mode=mode,
                              row_lo=row_lo, padding_idx=7)
             assert_close(got64, exp, np.float32, exact=True)
+
+
+@pytest.mark.parametrize("dt", ["f32", "f16"])
+def test_max_with_nan_rows_follows_torch_in_every_strategy(dt):
+    """torch's max keeps the bag's first entry as is and later entries only when strictly greater:
+    a NaN in the middle of a bag is ignored.  The CTA and split strategies cut a bag into slices;
+    a slice that starts with a NaN row must not lose the larger values behind it."""
+    rng = np.random.default_rng(71)
+    rows, dim = 500, 64
+    table = rng.standard_normal((rows, dim)).astype(NP[dt])
+    table[7] = np.nan                     # a whole NaN row
+    table[11, ::3] = np.nan               # NaN in some columns only
+    table[13] = 100.0                     # the value that must survive
+    lengths = np.array([4000, 1, 2500, 300, 0, 5000])
+    offsets = workloads.offsets_from_lengths(lengths).astype(np.int32)
+    idx = rng.integers(14, rows, int(lengths.sum())).astype(np.int32)   # no NaN rows yet
+    idx[1::5] = 7                          # NaN rows all over every bag, never at a bag's start
+    idx[3::11] = 11
+    idx[offsets[0] + 3999] = 13            # 100 at the very end of bag 0, behind many NaN rows
+    idx[offsets[2] + 1300] = 13
+    idx[offsets[:4]] = 20                  # every non-empty bag starts with an ordinary row
+    idx[offsets[5]] = 20
+    t, i, o = torch.from_numpy(table), torch.from_numpy(idx.astype(np.int64)), torch.from_numpy(offsets.astype(np.int64))
+    exp = torch.nn.functional.embedding_bag(i, t.float(), o, mode="max").numpy().astype(NP[dt])
+    assert not np.isnan(exp).any() and exp[0].max() == 100.0
+    ws = torch.empty(1 << 24, dtype=torch.uint8, device=DEV)
+    for strat in (capi.STRATEGY_GROUP, capi.STRATEGY_CTA, capi.STRATEGY_SPLIT, capi.STRATEGY_AUTO):
+        out = torch.empty((lengths.size, dim), dtype=torch.float16 if dt == "f16" else torch.float32, device=DEV)
+        p = capi.make_params(_cuda(table), _cuda(idx), _cuda(offsets), out=out, mode=capi.MODE_MAX,
+                             strategy=strat, workspace=ws)
+        capi.forward(p)
+        torch.cuda.synchronize()
+        assert np.array_equal(_bits(out.cpu().numpy()), _bits(exp)), strat

@@ -46,6 +46,12 @@ def host():
     h.fwd_eb_host_last_log.restype = C.c_char_p
     h.fwd_eb_host_creator_accepts.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     h.fwd_eb_host_creator_field_names.argtypes = [C.c_char_p, C.c_size_t]
+    h.fwd_eb_host_build_external.restype = C.c_void_p
+    h.fwd_eb_host_build_external.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                             C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                             C.c_void_p, C.c_int, C.c_void_p]
+    h.fwd_eb_plugin_register_weights.argtypes = [C.c_char_p, C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int]
+    h.fwd_eb_plugin_unregister_weights.argtypes = [C.c_char_p]
     return h
 
 
@@ -276,6 +282,102 @@ def test_long_bags_use_the_built_in_scratch_because_the_plugin_gets_no_workspace
     assert rc == 0 and np.array_equal(got, O.pool(table, idx, off, mode=O.MODE_MAX))
     assert capi.lib().fwd_eb_launch_count() - before == 2      # split pass + fold pass
     host.fwd_eb_host_free(h)
+
+
+def test_external_weights_names_must_be_registered_with_matching_geometry(host):
+    """createPlugin with `external_weights`: no table bytes travel; an unknown name, or a table
+    registered with another shape or element type, is refused with a logged reason."""
+    i, ir = _dims(10)
+    o, orank = _dims(3)
+    args = (0, 100, 8, 0, 0, -1, 0, 0, ir, i, orank, o, 0, None)
+    assert not host.fwd_eb_host_build_external(b"nobody", *args)
+    assert b"not registered" in host.fwd_eb_host_last_log()
+    fake = 0x7f0000000000      # never dereferenced on the host
+    assert host.fwd_eb_plugin_register_weights(b"t", fake, 0, 100, 8, 0) == 0
+    assert host.fwd_eb_plugin_register_weights(b"t", fake + 256, 0, 100, 8, 0) == 0    # same shape: pointer replaced
+    assert host.fwd_eb_plugin_register_weights(b"t", fake, 0, 100, 16, 0) == -2        # another shape: refused
+    h = host.fwd_eb_host_build_external(b"t", *args)
+    assert h
+    blob = blob_of(host, h)
+    assert len(blob) < 128 and struct.unpack_from("<i", blob, 0)[0] == -2 and blob[4:8] == b"002\0"
+    assert struct.unpack_from("<iqq", blob, 8) == (8, 100, 0)
+    loaded = host.fwd_eb_host_load(blob, len(blob), h)
+    assert loaded and host.fwd_eb_host_shares_table(h, loaded) == 0
+    host.fwd_eb_host_free(loaded)
+    assert not host.fwd_eb_host_build_external(b"t", 0, 101, 8, 0, 0, -1, 0, 0, ir, i, orank, o, 0, None)  # more rows than registered
+    assert not host.fwd_eb_host_build_external(b"t", 1, 100, 8, 0, 0, -1, 0, 0, ir, i, orank, o, 0, None)  # fp16 asked, fp32 registered
+    assert host.fwd_eb_plugin_unregister_weights(b"t") == 0
+    assert not host.fwd_eb_host_load(blob, len(blob), h)          # the name is gone: the blob cannot load
+    for cut in range(0, len(blob), 3):                            # truncated "002" blobs are refused, not read past
+        assert not host.fwd_eb_host_load(blob[:cut], cut, h)
+    host.fwd_eb_host_free(h)
+
+
+@pytest.mark.gpu
+def test_config3_sized_table_stays_outside_the_plan(host):
+    """A 2 GB table (config 3: 4,000,000 x 256 fp16) filled on the device, registered by name:
+    build -> serialise (a blob of some dozen bytes) -> deserialise -> enqueue, bit-equal to the
+    C-ABI result, and no copy of the table is ever made."""
+    torch = pytest.importorskip("torch")
+    from forward_b200 import workloads
+    rows, dim = 4_000_000, 256
+    table = torch.empty((rows, dim), dtype=torch.float16, device="cuda:0")
+    capi.fill_table(table, 0, seed=2, scale=0.1)
+    bags = workloads.config3_bags(seed=2)
+    idx, off = bags.indices, bags.offsets
+    assert host.fwd_eb_plugin_register_weights(b"c3", table.data_ptr(), 0, rows, dim, 1) == 0
+    i, ir = _dims(*idx.shape)
+    o, orank = _dims(*off.shape)
+    free0 = torch.cuda.mem_get_info()[0]
+    h = host.fwd_eb_host_build_external(b"c3", 1, rows, dim, 0, 2, 0, 0, 1, ir, i, orank, o, 0, None)
+    assert h, host.fwd_eb_host_last_log()
+    blob = blob_of(host, h)
+    assert len(blob) < 1024
+    loaded = host.fwd_eb_host_load(blob, len(blob), h)
+    assert loaded
+    assert free0 - torch.cuda.mem_get_info()[0] < (64 << 20)           # nothing of the table's size was allocated
+    assert host.fwd_eb_host_table_uploads(loaded) == 0
+    exp = capi.embedding_bag(table, torch.from_numpy(idx).cuda(), torch.from_numpy(off).cuda(),
+                             mode=capi.MODE_MAX, padding_idx=0)
+    for handle in (h, loaded):
+        rc, got = _run(host, handle, torch, [idx, off], (off.size, dim), torch.float16)
+        assert rc == 0 and np.array_equal(got.view(np.uint16), exp.cpu().numpy().view(np.uint16))
+    host.fwd_eb_host_free(h)
+    host.fwd_eb_host_free(loaded)
+    host.fwd_eb_plugin_unregister_weights(b"c3")
+
+
+@pytest.mark.gpu
+def test_two_contexts_on_two_streams_share_the_built_in_scratch_in_turn(host):
+    """Two execution contexts (clones) enqueue long-bag calls on different streams at once; both go
+    through the one scratch array of the GPU, which the plugin hands out one call at a time."""
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(14)
+    table = rng.standard_normal((3000, 64)).astype(np.float32)
+    table = np.round(table * 4) / 4       # sums of quarters are exact in fp32 whatever the order
+    lengths = np.array([60000, 40000, 0, 30000])
+    off = np.zeros(4, dtype=np.int32)
+    off[1:] = np.cumsum(lengths[:-1])
+    batches = [rng.integers(0, 3000, int(lengths.sum())).astype(np.int32) for _ in range(2)]
+    h = build(host, table, op=0, idx_dims=batches[0].shape, off_dims=(4,))
+    ctx = host.fwd_eb_host_clone_context(h)
+    handles = [h, ctx]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    d_idx = [torch.from_numpy(b).cuda() for b in batches]
+    d_off = torch.from_numpy(off).cuda()
+    outs = [torch.zeros((4, 64), dtype=torch.float32, device="cuda") for _ in range(2)]
+    torch.cuda.synchronize()
+    for rep in range(20):
+        for k in range(2):
+            rc = host.fwd_eb_host_run(handles[k], d_idx[k].data_ptr(), d_off.data_ptr(), None,
+                                      outs[k].data_ptr(), streams[k].cuda_stream)
+            assert rc == 0
+    torch.cuda.synchronize()
+    for k in range(2):
+        exp = O.pool(table, batches[k], off, mode=O.MODE_SUM)
+        assert np.array_equal(outs[k].cpu().numpy(), exp)
+    host.fwd_eb_host_free(h)
+    host.fwd_eb_host_free(ctx)
 
 
 def test_damaged_blobs_are_refused_or_loaded_never_crash(host):
