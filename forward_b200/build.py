@@ -138,8 +138,9 @@ def build_torch(force: bool = False, verbose: bool = False) -> str | None:
                "-I", tinc, "-I", os.path.join(tinc, "torch", "csrc", "api", "include"),
                "-I", "/usr/local/cuda/include", "-I", tdir, "-I", pdir,
                "-I", os.path.join(pdir, "trt_shim"), "-o", target] + srcs + [
-            "-L", LIBDIR, "-lfwd_eb_plugin", "-L", os.path.join(troot, "lib"), "-ltorch", "-ltorch_cpu",
-            "-lc10", "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(troot, "lib")]
+            "-L", LIBDIR, "-lfwd_eb_plugin", "-lfwd_eb", "-L", os.path.join(troot, "lib"), "-ltorch",
+            "-ltorch_cpu", "-lc10", "-L", "/usr/local/cuda/lib64", "-lcudart",
+            "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(troot, "lib")]
         _run(cmd, verbose)
     return target
 

@@ -67,6 +67,7 @@ SIGNATURES = {
                                  C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "fwd_eb_fill_table": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_int64,
                                     C.c_uint64, C.c_float, C.c_void_p]),
+    "fwd_eb_cast_i64_to_i32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "fwd_eb_combine_partials": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int64, C.c_int64,
                                           C.c_void_p, C.c_int32, C.c_void_p]),
 }

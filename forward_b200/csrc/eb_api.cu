@@ -792,6 +792,20 @@ int fwd_eb_fill_table(void* d_table, int32_t table_dtype, int64_t num_rows, int3
   return 0;
 }
 
+int fwd_eb_cast_i64_to_i32(const void* d_src, void* d_dst, int64_t count, void* stream) {
+  if (count < 0 || (count > 0 && (!d_src || !d_dst))) return fail(FWD_EB_EINVAL, "bad cast arguments");
+  if (count == 0) return 0;
+  long long blocks = (count + kCtaThreads - 1) / kCtaThreads;
+  const long long cap = (long long)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  eb_cast_i64_i32_kernel<<<(unsigned)blocks, kCtaThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const long long*>(d_src), static_cast<int*>(d_dst), count);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "cast launch");
+  return 0;
+}
+
 int fwd_eb_combine_partials(const void* d_parts, int32_t part_dtype, int32_t num_parts,
                             int64_t part_stride_elems, int64_t count, void* d_out,
                             int32_t out_dtype, void* stream) {

@@ -900,6 +900,15 @@ eb_fill_table_kernel(TW* table, long long num_rows, int dim, long long row_lo,
   }
 }
 
+static __global__ void __launch_bounds__(kCtaThreads)
+eb_cast_i64_i32_kernel(const long long* src, int* dst, long long count) {
+  for (long long i = (long long)blockIdx.x * kCtaThreads + threadIdx.x; i < count;
+       i += (long long)gridDim.x * kCtaThreads) {
+    const long long v = src[i];
+    dst[i] = (v >= -2147483647LL - 1 && v <= 2147483647LL) ? (int)v : -1;
+  }
+}
+
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kCtaThreads)
 eb_combine_partials_kernel(const TP* parts, int num_parts, long long part_stride, long long count,

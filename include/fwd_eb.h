@@ -284,6 +284,12 @@ int fwd_eb_bag_f32(const int* d_input, const int* d_offsets, float* d_output, in
 int fwd_eb_fill_table(void* d_table, int32_t table_dtype, int64_t num_rows, int32_t dim,
                       int64_t row_lo, uint64_t seed, float scale, void* stream);
 
+/* d_dst[i] = (int32) d_src[i] for `count` int64 values: the cast Forward's engine applies to
+ * int64 index tensors on their way in (TorchEngine::ParseInput,
+ * source/fwd_torch/torch_engine/torch_engine.cpp:134-149).  Values outside the int32 range map
+ * to -1, which no table window contains, instead of wrapping. */
+int fwd_eb_cast_i64_to_i32(const void* d_src, void* d_dst, int64_t count, void* stream);
+
 /* out[i] = sum over r < num_parts of parts[r][i] (fp32 or fp16 wire, fp32 math,
  * added in r order), optionally cast to `out_dtype`.  Used after a row-shard
  * exchange where each peer's partial lands in its own slot. */

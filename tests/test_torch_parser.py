@@ -186,3 +186,172 @@ def test_parsed_model_runs_through_the_plugin(tl, tmp_path, mode, half):
     assert torch.equal(out.cpu(), expect)               # bit for bit
     tl.host.fwd_eb_host_free(h)
     tl.fwd_eb_torch_free(p)
+
+
+# ---- whole graphs: several bags, concatenation, stacked offsets, int64 inputs -------------------
+
+class TensorArg(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("dtype", C.c_int), ("rank", C.c_int), ("dims", C.c_longlong * 4),
+                ("graph_input", C.c_int), ("element", C.c_int)]
+
+
+def _net_api(tl):
+    tl.fwd_eb_torch_parse_network.restype = C.c_void_p
+    tl.fwd_eb_torch_parse_network.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t]
+    tl.fwd_eb_torch_net_free.argtypes = [C.c_void_p]
+    for name in ("num_layers", "num_outputs", "num_graph_inputs"):
+        getattr(tl, "fwd_eb_torch_net_" + name).argtypes = [C.c_void_p]
+    tl.fwd_eb_torch_net_error.restype = C.c_char_p
+    tl.fwd_eb_torch_net_error.argtypes = [C.c_void_p]
+    tl.fwd_eb_torch_net_layer_info.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 3
+    tl.fwd_eb_torch_net_layer_input.argtypes = [C.c_void_p, C.c_int, C.c_int] + [C.c_void_p] * 3
+    tl.fwd_eb_torch_net_output_layers.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+    tl.fwd_eb_torch_net_run.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+    return tl
+
+
+def parse_network(tl, path):
+    _net_api(tl)
+    err = C.create_string_buffer(512)
+    n = tl.fwd_eb_torch_parse_network(path.encode(), err, 512)
+    return n, err.value.decode()
+
+
+class Tower(torch.nn.Module):
+    """DLRM's sparse side (the shape of Forward's own DLRM test, test_torch_dlrm.h:37-56): T bags,
+    offsets stacked in one [T, B] tensor, one index tensor per bag, pooled rows concatenated."""
+
+    def __init__(self, tables, dim, mode="sum"):
+        super().__init__()
+        self.bags = torch.nn.ModuleList([torch.nn.EmbeddingBag(r, dim, mode=mode) for r in tables])
+
+    def forward(self, offsets, *indices):
+        return torch.cat([bag(i, offsets[k]) for k, (bag, i) in enumerate(zip(self.bags, indices))], dim=1)
+
+
+def _tower_inputs(tables, nb, seed):
+    g = torch.Generator().manual_seed(seed)
+    lengths = [torch.randint(0, 6, (nb,), generator=g) for _ in tables]
+    offsets = torch.stack([torch.cumsum(l, 0) - l for l in lengths])
+    indices = [torch.randint(0, r, (int(l.sum()),), generator=g) for r, l in zip(tables, lengths)]
+    return offsets, indices
+
+
+@pytest.mark.parametrize("tables", [3, 26])
+def test_every_bag_of_a_graph_is_found_with_its_inputs(tl, tmp_path, tables):
+    rows = [40 + 7 * t for t in range(tables)]
+    tower = Tower(rows, 8)
+    offsets, indices = _tower_inputs(rows, 5, 0)
+    path = save_traced(tmp_path, f"tower{tables}.pth", tower, (offsets, *indices))
+    n, err = parse_network(tl, path)
+    assert n, err
+    assert tl.fwd_eb_torch_net_num_layers(n) == tables and tl.fwd_eb_torch_net_num_outputs(n) == 1
+    assert tl.fwd_eb_torch_net_num_graph_inputs(n) == tables + 1
+    order = (C.c_int * 64)()
+    assert tl.fwd_eb_torch_net_output_layers(n, 0, order, 64) == tables
+    for pos in range(tables):
+        layer = order[pos]
+        dim, count, op = C.c_int(), C.c_int(), C.c_int()
+        assert tl.fwd_eb_torch_net_layer_info(n, layer, C.byref(dim), C.byref(count), C.byref(op)) == 2
+        assert (dim.value, count.value, op.value) == (8, rows[pos], 0)       # cat order = table order
+        gi, el, fl = C.c_int(), C.c_int(), C.c_int()
+        tl.fwd_eb_torch_net_layer_input(n, layer, 0, C.byref(gi), C.byref(el), C.byref(fl))
+        assert (gi.value, el.value) == (1 + pos, -1)                          # its own index tensor
+        tl.fwd_eb_torch_net_layer_input(n, layer, 1, C.byref(gi), C.byref(el), C.byref(fl))
+        assert (gi.value, el.value, fl.value) == (0, pos, 0)                  # row `pos` of the stacked offsets
+    tl.fwd_eb_torch_net_free(n)
+
+
+def test_graphs_with_other_operators_are_refused_with_the_operator_named(tl, tmp_path):
+    class Scaled(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ee = torch.nn.EmbeddingBag(30, 4, mode="sum")
+
+        def forward(self, index, offset):
+            return torch.relu(self.ee(index, offset))
+
+    n, err = parse_network(tl, save_traced(tmp_path, "relu.pth", Scaled(), EXAMPLE))
+    assert not n and "aten::relu" in err
+
+    class Shifted(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ee = torch.nn.EmbeddingBag(30, 4, mode="sum")
+
+        def forward(self, index, offset):
+            return self.ee(index + 1, offset)
+
+    n, err = parse_network(tl, save_traced(tmp_path, "add.pth", Shifted(), EXAMPLE))
+    assert not n and "aten::add" in err
+
+    class Stacked(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = torch.nn.EmbeddingBag(30, 4, mode="sum")
+            self.b = torch.nn.EmbeddingBag(30, 4, mode="sum")
+
+        def forward(self, index, offset):
+            return torch.cat([self.a(index, offset), self.b(index, offset)], dim=0)
+
+    n, err = parse_network(tl, save_traced(tmp_path, "cat0.pth", Stacked(), EXAMPLE))
+    assert not n and "dim 1" in err
+
+
+def _run_network(tl, n, feeds, out_shape):
+    """feeds: list of (graph_input, element, CUDA tensor)."""
+    args = (TensorArg * len(feeds))()
+    for a, (gi, el, t) in zip(args, feeds):
+        a.data, a.rank, a.graph_input, a.element = t.data_ptr(), t.dim(), gi, el
+        a.dtype = {torch.int32: 0, torch.int64: 1, torch.float32: 2}[t.dtype]
+        for q, d in enumerate(t.shape):
+            a.dims[q] = d
+    out = torch.full(out_shape, float("nan"), dtype=torch.float32, device="cuda:0")
+    outs = (C.c_void_p * 1)(out.data_ptr())
+    rc = tl.fwd_eb_torch_net_run(n, args, len(feeds), outs, C.c_void_p(capi.current_stream_ptr()))
+    torch.cuda.synchronize()
+    assert rc == 0, tl.fwd_eb_torch_net_error(n)
+    return out.cpu()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tables", [3, 26])
+def test_a_tower_of_bags_runs_from_int64_inputs_and_matches_the_module(tl, tmp_path, tables):
+    """Parse -> one plugin per bag -> int64 inputs cast to int32 on the way in (as Forward's engine
+    does) -> enqueue -> concatenate; twice, the second time with fresh indices of the same sizes."""
+    rows = [300 + 11 * t for t in range(tables)]
+    tower = Tower(rows, 16).eval()
+    offsets, indices = _tower_inputs(rows, 64, 1)
+    path = save_traced(tmp_path, f"tower{tables}.pth", tower, (offsets, *indices))
+    n, err = parse_network(tl, path)
+    assert n, err
+    for rep in range(2):
+        if rep:
+            indices = [torch.randint(0, r, i.shape) for r, i in zip(rows, indices)]
+        feeds = [(0, -1, offsets.cuda())] + [(1 + k, -1, i.cuda()) for k, i in enumerate(indices)]
+        got = _run_network(tl, n, feeds, (64, 16 * tables))
+        exp = tower(offsets, *indices).detach()
+        assert torch.equal(got, exp)
+    tl.fwd_eb_torch_net_free(n)
+
+
+@pytest.mark.gpu
+def test_config1_through_parser_plugin_and_enqueue(tl, tmp_path):
+    """BASELINE config 1 (EmbeddingBag(10000, 64, mode='sum'), fp32 N(0,1) weights, 32 bags of 1..20
+    uniform indices, seed 0) through parse -> plugin -> enqueue, against torch CPU within 1e-5
+    relative (it is bit-identical: the kernel adds in bag order)."""
+    from forward_b200 import workloads
+    table, bags = workloads.config1(seed=0)
+    bag = Bag(10000, 64, "sum")
+    with torch.no_grad():
+        bag.ee.weight.copy_(torch.from_numpy(table))
+    idx = torch.from_numpy(bags.indices.astype(np.int64))
+    off = torch.from_numpy(bags.offsets.astype(np.int64))
+    path = save_traced(tmp_path, "config1.pth", bag, (idx, off))
+    n, err = parse_network(tl, path)
+    assert n, err
+    got = _run_network(tl, n, [(0, -1, idx.cuda()), (1, -1, off.cuda())], (32, 64))
+    exp = torch.nn.functional.embedding_bag(idx, torch.from_numpy(table), off, mode="sum")
+    torch.testing.assert_close(got, exp, rtol=1e-5, atol=0)
+    assert torch.equal(got, exp)
+    tl.fwd_eb_torch_net_free(n)
