@@ -96,6 +96,29 @@ def build_core(force: bool = False, verbose: bool = False) -> str:
     return target
 
 
+# Experiment builds of libfwd_eb.so (never loaded by default; FWD_EB_LIB points capi at one).
+VARIANTS = {
+    # the lean kernel with its table rows staged through shared memory: by cp.async, and by the
+    # bulk copy engine (cp.async.bulk + mbarrier); see csrc/eb_lite_staged.cuh
+    "row_staging_cp_async": ["-DFWD_EB_ROW_STAGING=1"],
+    "row_staging_bulk": ["-DFWD_EB_ROW_STAGING=2"],
+}
+
+
+def build_variant(name: str, verbose: bool = False) -> str:
+    """One nvcc call, all translation units, into build/variants/libfwd_eb_<name>.so."""
+    flags = VARIANTS[name]
+    outdir = os.path.join(ROOT, "build", "variants")
+    os.makedirs(outdir, exist_ok=True)
+    target = os.path.join(outdir, f"libfwd_eb_{name}.so")
+    srcs = [os.path.join(CSRC, f) for f in CORE_SOURCES]
+    cmd = [_nvcc()] + ARCH + NVCC_FLAGS + flags + ["-DFWD_EB_BUILD", "-I", INCLUDE, "-I", CSRC]
+    if verbose:
+        cmd += ["-Xptxas", "-v"]
+    _run(cmd + ["-o", target] + srcs, verbose)
+    return target
+
+
 def build_plugin(force: bool = False, verbose: bool = False) -> str | None:
     pdir = os.path.join(CSRC, "plugin")
     if not os.path.isdir(pdir):
@@ -177,6 +200,10 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--variant", choices=sorted(VARIANTS), help="build one experiment variant of libfwd_eb.so")
     ns = ap.parse_args()
+    if ns.variant:
+        print(build_variant(ns.variant, ns.verbose))
+        sys.exit(0)
     for path in build_all(ns.force, ns.verbose):
         print(path)

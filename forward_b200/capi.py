@@ -11,7 +11,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libfwd_eb.so")
+# FWD_EB_LIB: another build of the library (an experiment variant from forward_b200.build --variant)
+LIB_PATH = os.environ.get("FWD_EB_LIB") or os.path.join(_HERE, "lib", "libfwd_eb.so")
 
 MODE_SUM, MODE_MEAN, MODE_MAX, MODE_SQUARE_SUM, MODE_GATHER = 0, 1, 2, 3, 999
 F32, F16 = 0, 1

@@ -17,6 +17,7 @@
 #include "eb_internal.h"
 #include "eb_kernels.cuh"
 #include "eb_lite.cuh"
+#include "eb_lite_staged.cuh"
 #include "eb_stream.cuh"
 #include "fwd_eb.h"
 
@@ -410,9 +411,14 @@ static cudaError_t launch_lite_ll(const Plan& pl, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+#if defined(FWD_EB_ROW_STAGING) && FWD_EB_ROW_STAGING > 0
+  // experiment build: rows staged through shared memory (eb_lite_staged.cuh)
+  cudaError_t le = cudaLaunchKernelEx(&cfg, eb_pool_lite_staged_kernel<TW, VE, LL, OP>, a);
+#else
   PushArgs none;
   memset(&none, 0, sizeof(none));
   cudaError_t le = cudaLaunchKernelEx(&cfg, eb_pool_lite_kernel<TW, VE, LL, OP, false>, a, none);
+#endif
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return le != cudaSuccess ? le : cudaGetLastError();
 }

@@ -117,34 +117,48 @@ class TLayerDescCreator<TrtEmbeddingBagDesc> : public ILayerDescCreator {
   }
 
  private:
-  // Walks Sum -> [Square] -> Mul -> [Identity] -> GatherV2, or accepts a bare GatherV2.
+  // The three shapes a lookup takes in a frozen graph, as a table: the operator types met on the
+  // way from the pattern's top node down to its GatherV2 (optional steps in brackets), and the
+  // pooling mode each stands for.
+  //   GatherV2                                          -> GATHER (999)
+  //   Sum > Mul > [Identity] > GatherV2                 -> SUM (0)
+  //   Sum > Square > Mul > [Identity] > GatherV2        -> SQUARE_SUM (3)
+  struct Step {
+    const char* type;
+    bool optional;
+  };
+  static bool Descend(Operation at, const Step* steps, int n_steps, Operation* gather) {
+    for (int i = 0; i < n_steps; ++i) {
+      if (!at.Valid()) return false;
+      if (at.OpType() == steps[i].type) {
+        if (i + 1 == n_steps) {
+          *gather = at;
+          return true;
+        }
+        at = at.Input(0);
+      } else if (!steps[i].optional) {
+        return false;
+      }
+    }
+    return false;
+  }
   static bool Match(const Operation& op, Operation* gather, int* op_type) {
-    if (!op.Valid()) return false;
-    std::string type = op.OpType();
-    if (type == "GatherV2") {
-      *gather = op;
-      *op_type = 999;
-      return true;
+    static const Step kGather[] = {{"GatherV2", false}};
+    static const Step kSum[] = {{"Sum", false}, {"Mul", false}, {"Identity", true}, {"GatherV2", false}};
+    static const Step kSquareSum[] = {{"Sum", false}, {"Square", false}, {"Mul", false}, {"Identity", true},
+                                      {"GatherV2", false}};
+    static const struct {
+      const Step* steps;
+      int count;
+      int mode;
+    } kPatterns[] = {{kGather, 1, 999}, {kSum, 4, 0}, {kSquareSum, 5, 3}};
+    for (const auto& pattern : kPatterns) {
+      if (Descend(op, pattern.steps, pattern.count, gather)) {
+        *op_type = pattern.mode;
+        return true;
+      }
     }
-    if (type != "Sum") return false;
-    *op_type = 0;
-    Operation father = op.Input(0);
-    type = father.OpType();
-    if (type == "Square") {
-      *op_type = 3;
-      father = father.Input(0);
-      type = father.OpType();
-    }
-    if (type != "Mul") return false;
-    father = father.Input(0);
-    type = father.OpType();
-    if (type == "Identity") {
-      father = father.Input(0);
-      type = father.OpType();
-    }
-    if (type != "GatherV2") return false;
-    *gather = father;
-    return true;
+    return false;
   }
 };
 
