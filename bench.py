@@ -455,6 +455,26 @@ class GpuWorkload:
                                        row_lo=self.row_lo) for i, o in self.d_batches]
             self._params = params
 
+            if self.local_filter:
+                # one rank's share of a row-sharded table on one GPU: the two kernels a rank runs per
+                # step (window compaction, pooling of the dense sub-bags), with local stores
+                max_n = max(b.num_indices for b in self.batches)
+                kept = torch.empty(max_n, dtype=torch.int32, device=dev)
+                bounds = torch.empty((bags_n, 2), dtype=torch.int32, device=dev)
+                cp = capi.make_compacted_params(self.table, kept, bounds, out=out, mode=self.mode)
+                self._compact_keep = (kept, bounds)
+
+                def step(k, events=None):
+                    if events:
+                        events[0].record()
+                    capi.compact_window(self._params[k % self.nb], kept, bounds, stream=stream.cuda_stream)
+                    capi.forward(cp, stream.cuda_stream)
+                    if events:
+                        events[1].record()
+                    self._last = out
+                self.step = step
+                return
+
             def step(k, events=None):
                 if events:
                     events[0].record()

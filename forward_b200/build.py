@@ -102,6 +102,8 @@ VARIANTS = {
     # bulk copy engine (cp.async.bulk + mbarrier); see csrc/eb_lite_staged.cuh
     "row_staging_cp_async": ["-DFWD_EB_ROW_STAGING=1"],
     "row_staging_bulk": ["-DFWD_EB_ROW_STAGING=2"],
+    # reads tuning knobs from the environment (FWD_EB_PUSH_CTA, FWD_EB_STREAM_K, FWD_EB_IPL1)
+    "tune": ["-DFWD_EB_TUNE"],
 }
 
 

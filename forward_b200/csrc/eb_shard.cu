@@ -404,6 +404,11 @@ static cudaError_t launch_push_stream(const PoolArgs& a, const PushArgs& x, bool
   return launch_push_stream_ll<TW, 5>(a, x, weighted, st);
 }
 
+// CTA size of the lean kernel when its rows go to peers (a CTA's registers and warp slots are
+// released only when its last warp has retired, and a warp that stored to a peer retires only
+// when the store has been acknowledged).
+constexpr int kPushCtaThreads = kCtaThreads;
+
 // The lean kernel (eb_lite.cuh) with the push epilogue.
 template <typename TW, int LL>
 static cudaError_t launch_push_lite_ll(const PoolArgs& a, const PushArgs& x, bool weighted,
@@ -414,12 +419,16 @@ static cudaError_t launch_push_lite_ll(const PoolArgs& a, const PushArgs& x, boo
   // groups, and on two B200s the step got slower, not faster: 32.5 against 24.5 us table-wise,
   // 150 against 133 us on config 5.  The hardware's hand-out of CTAs balances ragged bags better.)
   const PoolArgs& b = a;
-  const long long blocks = ((a.num_bags << LL) + kCtaThreads - 1) / kCtaThreads;
+  int cta = kPushCtaThreads;
+#ifdef FWD_EB_TUNE
+  if (const char* env = getenv("FWD_EB_PUSH_CTA")) cta = atoi(env) >= 32 ? atoi(env) : cta;
+#endif
+  const long long blocks = ((a.num_bags << LL) + cta - 1) / cta;
   if (blocks == 0) return cudaSuccess;
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3((unsigned)kCtaThreads);
+  cfg.blockDim = dim3((unsigned)cta);
   cfg.stream = st;
   cudaLaunchAttribute attr[1];  // see launch_pool in eb_api.cu
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
