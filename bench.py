@@ -904,9 +904,11 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
                     "overhead_frac": (step_us - pool_only_us) / pool_only_us,
                     "nvlink_egress_bytes_per_rank": int(egress),
                     "nvlink_floor_us_at_770GBs": egress / 770e9 * 1e6,
-                    # egress over the part of a step the exchange adds, against 900 GB/s per direction
-                    "nvlink_frac": egress / (extra_us * 1e-6) / 900e9,
-                    "nvlink_frac_of_step": egress / (step_us * 1e-6) / 900e9,
+                    # this rank's egress over the whole step, against 900 GB/s per direction (the
+                    # exchange runs beside the pooling: there is no exchange-only time to divide by)
+                    "nvlink_frac": egress / (step_us * 1e-6) / 900e9,
+                    # ... and over only the time a step takes longer than the pooling alone
+                    "nvlink_frac_of_added_time": egress / (extra_us * 1e-6) / 900e9,
                     "host_us_per_step_queued": host_us}
     value = lookups / (total_ms * 1e-3)
 
