@@ -396,15 +396,25 @@ static cudaError_t launch_stream_ll(const Plan& pl, cudaStream_t st) {
   return le != cudaSuccess ? le : cudaGetLastError();
 }
 
+// CTA size of the lean kernel (the kernel reads blockDim.x).
+static int lite_cta_threads(int lanes_log2) {
+  (void)lanes_log2;
+  return kCtaThreads;
+}
+
 template <typename TW, int VE, int LL, int OP>
 static cudaError_t launch_lite_ll(const Plan& pl, cudaStream_t st) {
   const PoolArgs& a = pl.a;
-  const long long blocks = ((a.num_bags << LL) + kCtaThreads - 1) / kCtaThreads;
+  int cta = lite_cta_threads(LL);
+#ifdef FWD_EB_TUNE
+  if (const char* env = getenv("FWD_EB_LITE_CTA")) cta = atoi(env) >= 32 ? atoi(env) : cta;
+#endif
+  const long long blocks = ((a.num_bags << LL) + cta - 1) / cta;
   if (blocks == 0) return cudaSuccess;
   if (blocks > INT_MAX) return cudaErrorInvalidConfiguration;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)blocks);
-  cfg.blockDim = dim3((unsigned)kCtaThreads);
+  cfg.blockDim = dim3((unsigned)cta);
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;

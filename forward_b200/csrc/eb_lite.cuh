@@ -13,7 +13,7 @@
 //   * the padding / table-window filter is three 32-bit instructions on the loaded index;
 //     a filtered entry simply issues no row load (no compaction inside the kernel: callers
 //     with sparse windows compact first, see eb_compact.cuh);
-//   * rows are fetched in passes of up to 8 loads per lane, the row number of slot u coming
+//   * rows are fetched in passes of 6 to 8 loads per lane, the row number of slot u coming
 //     from lane u of the group by shuffle, then folded in order.
 //
 // Shapes: 16-byte vector path, one chunk per lane (rows of 128 B to 512 B), int32 indices and
@@ -25,14 +25,26 @@
 
 namespace fwd_eb {
 
-constexpr int kLitePass = 8;  // row loads in flight per lane
+#ifndef FWD_EB_LITE_PASS
+#define FWD_EB_LITE_PASS 0
+#endif
+#ifndef FWD_EB_LITE_MIN_CTAS
+#define FWD_EB_LITE_MIN_CTAS FWD_EB_MIN_CTAS
+#endif
+// Row loads in flight per lane and pass.  Measured on B200 (us per call, pass of 6 / 7 / 8): 16384
+// bags of ~40 rows of 256 B, Zipf 19.5 / 23.3 / 22.6, uniform 27.5 / 30.1 / 28.4; 8192 bags of 0..64
+// rows of 512 B 29.1 / 28.8 / 30.9 (8 spills at 64 registers, 6 does not); 131072 bags of ~6 rows of
+// 128 B 38.2 / - / 36.7 (a whole bag in one pass).
+__host__ __device__ constexpr int lite_pass(int lanes_log2) {
+  return FWD_EB_LITE_PASS > 0 ? FWD_EB_LITE_PASS : (lanes_log2 == 3 ? 8 : (lanes_log2 == 5 ? 7 : 6));
+}
 
 template <typename TW, int VE, int LL, int OP, bool PUSH>
-__global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
+__global__ void __launch_bounds__(kCtaThreads, FWD_EB_LITE_MIN_CTAS)
 eb_pool_lite_kernel(const PoolArgs a, const PushArgs x) {
   using V = typename Chunk<TW, VE>::type;
   constexpr int LANES = 1 << LL;
-  constexpr int U = kLitePass;
+  constexpr int U = lite_pass(LL);
   constexpr unsigned GMASK = LANES == 32 ? kFull : ((1u << LANES) - 1u);
   const unsigned lane = threadIdx.x & 31u;
   const int lig = lane & (LANES - 1);
