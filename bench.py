@@ -932,6 +932,10 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
                 "kernel_us_isolated_median": float(np.median(iso_us)),
                 "kernel_us_isolated_samples": int(len(iso_us)),
                 "algorithmic_bytes_per_launch": alg}
+    if workload in ("c2", "tablewise"):
+        roofline["note"] = ("Zipf indices: hot rows are served from L1 / L2 (DRAM traffic is `traffic`, a fifth of the "
+                            "algorithmic bytes), so `frac` can exceed 1; the HBM-bound figure of this kernel is "
+                            "`roofline_uniform` (same shape, uniform indices)")
     if workload == "c4":
         roofline["launches_per_step"] = wl.launches_per_step
         roofline["note"] = "kernel_us_* and the bytes cover one step = all of this rank's tables"
