@@ -2,6 +2,7 @@
 // LOG(...) and the T_CHECK family), so the creator headers compile outside Forward's tree.
 #pragma once
 
+#include <cstdlib>
 #include <iostream>
 #include <sstream>
 
@@ -21,7 +22,19 @@ struct Line {
   bool on_;
   std::ostringstream ss_;
 };
-inline bool Enabled(const char* level) { return level[0] == 'E'; }  // errors only
+// Errors always; FWD_LOG_LEVEL=WARNING or INFO (read once) lets the quieter levels through too.
+inline int Threshold() {
+  static const int t = [] {
+    const char* env = std::getenv("FWD_LOG_LEVEL");
+    if (!env) return 2;
+    return (env[0] == 'I' || env[0] == 'i') ? 0 : ((env[0] == 'W' || env[0] == 'w') ? 1 : 2);
+  }();
+  return t;
+}
+inline bool Enabled(const char* level) {
+  const int rank = level[0] == 'I' ? 0 : (level[0] == 'W' ? 1 : 2);
+  return rank >= Threshold();
+}
 }  // namespace log_detail
 }  // namespace fwd
 #define LOG(level) ::fwd::log_detail::Line(::fwd::log_detail::Enabled(#level))

@@ -371,6 +371,38 @@ def test_config4_one_table_weighted_sum():
     assert_close(got.cpu().numpy(), exp, np.float32, exact=True)
 
 
+def test_config4_all_26_tables_full_batch_every_strategy():
+    """Config 4 as stated: all 26 tables (row counts log-uniform 1e3..4e7, here capped at 2e6 rows so
+    that the tables fit next to each other; the indices keep the configuration's Zipf(1.1) law),
+    batch 65536, pooling factor 20, per-sample weights, sum — pooled into one [65536, 26, 128]
+    result as the table-wise placement lays it out, by the strategy AUTO picks and by the two other
+    lane-group kernels; a sample of bags of every table against the CPU oracle, bit for bit."""
+    rows_all = [int(min(r, 2_000_000)) for r in workloads.config4_rows()]
+    B, L, D, T = 65536, 20, 128, len(rows_all)
+    strategies = (capi.STRATEGY_AUTO, capi.STRATEGY_LITE, capi.STRATEGY_GROUP)
+    outs = [torch.full((B, T, D), float("nan"), dtype=torch.float32, device=DEV) for _ in strategies]
+    take = np.arange(0, B, 97)
+    for t, rows in enumerate(rows_all):
+        bags = workloads.config4_bags(t, rows)
+        table = torch.empty((rows, D), dtype=torch.float32, device=DEV)
+        capi.fill_table(table, 0, seed=300 + t, scale=0.1)
+        d_idx, d_w = _cuda(bags.indices), _cuda(bags.per_sample_weights)
+        for out, strat in zip(outs, strategies):
+            capi.forward(capi.make_params(table, d_idx, None, out=out[:, t, :], mode=capi.MODE_SUM, fixed_len=L,
+                                          per_sample_weights=d_w, strategy=strat))
+        torch.cuda.synchronize()
+        idx = bags.indices.reshape(B, L)[take].reshape(-1)
+        w = bags.per_sample_weights.reshape(B, L)[take].reshape(-1)
+        uniq, inv = np.unique(idx, return_inverse=True)
+        compact = O.table_rows(uniq, D, seed=300 + t, scale=0.1, dtype=np.float32)
+        exp = O.pool(compact, inv.astype(np.int32), mode=O.MODE_SUM, fixed_len=L, per_sample_weights=w)
+        got = outs[0][:, t, :].cpu().numpy()[take]
+        assert_close(got, exp, np.float32, exact=True)
+    for other in outs[1:]:
+        assert torch.equal(other.view(torch.int32), outs[0].view(torch.int32))
+    assert not torch.isnan(outs[0]).any()
+
+
 def test_int32_filter_edges_negative_indices_and_window_origin():
     """int32 indices take a 32-bit filter: negative indices, indices below the window origin and
     a negative origin (the reference's data_offset is a signed int) must behave as in the oracle."""
