@@ -298,19 +298,21 @@ static int make_plan(const fwd_eb_params* p, Plan* pl) {
   pl->strategy = pick_strategy(p);
   if (a.pairs && pl->strategy != FWD_EB_STRATEGY_STREAM && pl->strategy != FWD_EB_STRATEGY_LITE)
     pl->strategy = FWD_EB_STRATEGY_GROUP;
-  // AUTO: where a lane group per bag is the plan and the shape allows, one of the two leaner
-  // kernels runs it.  Measured on B200 (us per call, group / stream / lite): 16384 bags of ~40
-  // rows of 256 B, Zipf 23.0 / 28.0 / 22.7, uniform 29.4 / 34.4 / 28.4; 8192 bags of 0..64 rows of
-  // 512 B (max, 5 % padding) 33.8 / 32.5 / 30.9; 131072 dense bags of ~6 rows of 128 B 42.7 / 43.2 /
-  // 37.3; 65536 x 20 weighted fp32 rows of 512 B 77.9 / 63.9 / 70.0.  So: fixed-length bags stream,
-  // everything else goes lite.
+  // AUTO: where a lane group per bag is the plan and the shape allows, the lean kernel runs it.
+  // Measured on B200 (us per call, group / stream / lite): 16384 bags of ~40 rows of 256 B, Zipf
+  // 23.0 / 28.0 / 19.5, uniform 29.4 / 34.4 / 27.5; 8192 bags of 0..64 rows of 512 B (max, 5 %
+  // padding) 33.8 / 32.5 / 28.8; 131072 dense bags of ~6 rows of 128 B 42.7 / 43.2 / 32.6; fixed
+  // length, uniform indices over 4 M rows: 65536 x 20 weighted fp32 rows of 512 B 117.1 / 111.3 /
+  // 105.9; 262144 x 8 fp16 rows of 128 B 66.5 / 60.8 / 48.5; 131072 x 6 fp16 rows of 512 B 215.3 /
+  // 101.5 / 78.8; 262144 x 4 fp32 rows of 128 B 44.2 / 33.4 / 31.1.  The streaming kernel stays
+  // available by name (FWD_EB_STRATEGY_STREAM).
   // A table window that starts above row 0 says "one shard of a larger table": most indices
   // will then miss the window, and both lean kernels spend a load slot on every index, kept or
   // not, where the group kernel's survivor ring does not (142 against 80 us on a 1-in-8 window).
   // Such calls stay with the group kernel unless the indices were compacted first.
   if (p->strategy == FWD_EB_STRATEGY_AUTO && pl->strategy == FWD_EB_STRATEGY_GROUP &&
       stream_ok(p, pl) && (a.pairs || p->row_lo == 0))
-    pl->strategy = p->fixed_len > 0 ? FWD_EB_STRATEGY_STREAM : FWD_EB_STRATEGY_LITE;
+    pl->strategy = FWD_EB_STRATEGY_LITE;
   if (pl->strategy == FWD_EB_STRATEGY_LITE && !stream_ok(p, pl))
     return fail(FWD_EB_EUNSUPPORTED, "LITE needs 16-byte aligned rows of 128..512 bytes, int32 "
                 "indices and fewer than 2^31 of them");
@@ -356,7 +358,7 @@ int plan_group(const fwd_eb_params* p, PoolArgs* args, int* vec, int* cpl, int* 
   if (p->strategy == FWD_EB_STRATEGY_STREAM) want = 1;
   else if (p->strategy == FWD_EB_STRATEGY_LITE) want = 2;
   else if (p->strategy == FWD_EB_STRATEGY_AUTO && (pl.a.pairs || p->row_lo == 0))
-    want = p->fixed_len > 0 ? 1 : 2;
+    want = 2;
   *stream = 0;
   if (want && stream_ok(&q, &pl)) {
     if (want == 1) pl.a.stream_k = choose_stream_k(&q, pl.a.lanes_log2);

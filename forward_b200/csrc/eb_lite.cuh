@@ -13,7 +13,7 @@
 //   * the padding / table-window filter is three 32-bit instructions on the loaded index;
 //     a filtered entry simply issues no row load (no compaction inside the kernel: callers
 //     with sparse windows compact first, see eb_compact.cuh);
-//   * rows are fetched in passes of 6 to 8 loads per lane, the row number of slot u coming
+//   * rows are fetched in passes of 4 to 7 loads per lane, the row number of slot u coming
 //     from lane u of the group by shuffle, then folded in order.
 //
 // Shapes: 16-byte vector path, one chunk per lane (rows of 128 B to 512 B), int32 indices and
@@ -29,22 +29,34 @@ namespace fwd_eb {
 #define FWD_EB_LITE_PASS 0
 #endif
 #ifndef FWD_EB_LITE_MIN_CTAS
-#define FWD_EB_LITE_MIN_CTAS FWD_EB_MIN_CTAS
+#define FWD_EB_LITE_MIN_CTAS 0
 #endif
-// Row loads in flight per lane and pass.  Measured on B200 (us per call, pass of 6 / 7 / 8): 16384
-// bags of ~40 rows of 256 B, Zipf 19.5 / 23.3 / 22.6, uniform 27.5 / 30.1 / 28.4; 8192 bags of 0..64
-// rows of 512 B 29.1 / 28.8 / 30.9 (8 spills at 64 registers, 6 does not); 131072 bags of ~6 rows of
-// 128 B 38.2 / - / 36.7 (a whole bag in one pass).
-__host__ __device__ constexpr int lite_pass(int lanes_log2) {
-  return FWD_EB_LITE_PASS > 0 ? FWD_EB_LITE_PASS : (lanes_log2 == 3 ? 8 : (lanes_log2 == 5 ? 7 : 6));
+// Row loads in flight per lane and pass, and resident CTAs per SM (which caps the registers: 8 CTAs
+// of 128 threads = 64 registers, 10 = 48, 12 = 40).  A longer pass hides more latency per warp but
+// costs 4 registers per fp16 row slot; once the kernel spills, it loses more than the pass gains, and
+// short bags want warps in flight rather than loads per warp.  Measured on B200, us per call, as
+// pass / CTAs:
+//   fp16, 128 B rows, 131072 bags of ~6 rows     8/8 37.0   4/8 38.8   4/10 34.4   4/12 32.8   3/16 32.9
+//   fp16, 256 B rows, 16384 bags of ~40 (Zipf)    6/8 19.5   7/8 23.3   8/8 22.6   6/9 20.0   6/10 21.8   4/12 22.0
+//   fp16, 512 B rows, 8192 bags of 0..64, max     7/8 28.8   6/8 29.1   8/9 28.5   6/10 29.8   4/12 31.2
+//   fp32, 512 B rows, 65536 bags of 20, weighted  7/8 62.9   6/9 56.1   4/10 52.0   5/10 50.9   5/12 51.7   6/12 74.9
+__host__ __device__ constexpr int lite_pass(int lanes_log2, int elem_bytes) {
+  return FWD_EB_LITE_PASS > 0 ? FWD_EB_LITE_PASS
+         : elem_bytes == 4    ? 5
+                              : (lanes_log2 == 3 ? 4 : (lanes_log2 == 5 ? 7 : 6));
+}
+__host__ __device__ constexpr int lite_min_ctas(int lanes_log2, int elem_bytes) {
+  return FWD_EB_LITE_MIN_CTAS > 0 ? FWD_EB_LITE_MIN_CTAS
+         : elem_bytes == 4        ? 10
+                                  : (lanes_log2 == 3 ? 12 : FWD_EB_MIN_CTAS);
 }
 
 template <typename TW, int VE, int LL, int OP, bool PUSH>
-__global__ void __launch_bounds__(kCtaThreads, FWD_EB_LITE_MIN_CTAS)
+__global__ void __launch_bounds__(kCtaThreads, lite_min_ctas(LL, (int)sizeof(TW)))
 eb_pool_lite_kernel(const PoolArgs a, const PushArgs x) {
   using V = typename Chunk<TW, VE>::type;
   constexpr int LANES = 1 << LL;
-  constexpr int U = lite_pass(LL);
+  constexpr int U = lite_pass(LL, (int)sizeof(TW));
   constexpr unsigned GMASK = LANES == 32 ? kFull : ((1u << LANES) - 1u);
   const unsigned lane = threadIdx.x & 31u;
   const int lig = lane & (LANES - 1);

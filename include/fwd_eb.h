@@ -66,7 +66,8 @@ enum {
    * FWD_EB_EUNSUPPORTED when STREAM is asked for by name. */
   FWD_EB_STRATEGY_STREAM = 4,
   /* a lane group per bag with the least per-bag work: blocks of one index per lane, no
-   * survivor ring, passes of 6 to 8 row loads.  Same shapes as STREAM.  For short, dense bags. */
+   * survivor ring, passes of 4 to 7 row loads.  Same shapes as STREAM; what AUTO runs on them
+   * (unless the call is a row window above row 0 whose indices were not compacted). */
   FWD_EB_STRATEGY_LITE = 5
 };
 

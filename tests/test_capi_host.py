@@ -99,7 +99,7 @@ def test_strategy_choice_and_workspace():
     wide = _params(num_bags=16384, num_indices=16384 * 40, dim=1024)        # rows beyond 512 bytes
     assert lib.fwd_eb_pick_strategy(C.byref(wide)) == capi.STRATEGY_GROUP
     fixed = _params(num_bags=1000, num_indices=20000, fixed_len=20, offsets=None)
-    assert lib.fwd_eb_pick_strategy(C.byref(fixed)) == capi.STRATEGY_STREAM
+    assert lib.fwd_eb_pick_strategy(C.byref(fixed)) == capi.STRATEGY_LITE
     some_long = _params(num_bags=1000, num_indices=1000 * 500)
     assert lib.fwd_eb_pick_strategy(C.byref(some_long)) == capi.STRATEGY_CTA
     few_huge = _params(num_bags=4, num_indices=4 * 100_000)
