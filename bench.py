@@ -222,9 +222,11 @@ def describe(workload: str, world: int, args):
                     parallelism=f"rowshard{world}" if world > 1 else "single",
                     exchange=args.exchange if world > 1 else None, wire=args.wire)
     elif workload == "c4":
+        capped = f" [tables cut to {args.c4_max_rows} rows: a profiler-sized case]" \
+            if getattr(args, "c4_max_rows", 0) else ""
         base.update(workload="c4: 26 tables of 1e3..3e7 rows x 128 fp32 (42 GB), 65536 bags x 20 Zipf(1.1) "
                              "indices per table, per-sample weights, sum; tables placed whole on ranks, "
-                             f"pooled rows exchanged to [65536/{world}, 26, 128] fp32 per rank",
+                             f"pooled rows exchanged to [65536/{world}, 26, 128] fp32 per rank" + capped,
                     bags_per_step=C4["bags"], tables=C4["tables"], dim=C4["dim"],
                     parallelism=f"tablewise{world}" if world > 1 else "single",
                     exchange=args.exchange if world > 1 else None,
@@ -579,7 +581,8 @@ class C4Workload:
         self.dim, self.mode, self.pad = C4["dim"], capi.MODE_SUM, -1
         self.out_itemsize = 4
         self.L = C4["pooling"]
-        self.rows = [int(r) for r in workloads.config4_rows()]
+        cap = getattr(args, "c4_max_rows", 0) or 0
+        self.rows = [int(min(r, cap)) if cap else int(r) for r in workloads.config4_rows()]
         self.T = len(self.rows)
         n_per_table = C4["bags"] * self.L
         self.owner = fd.place_tables([r * self.dim * 4 for r in self.rows], world,
@@ -1395,6 +1398,9 @@ def main():
     ap.add_argument("--c5-window", type=int, default=1,
                     help="c5 at N=1: hold only one of this many row windows of the table and pool "
                          "that rank's partial bags (the per-rank kernel of a sharded run; no exchange)")
+    ap.add_argument("--c4-max-rows", type=int, default=0,
+                    help="c4: cut every table to this many rows (0 = the configuration's sizes; a smaller "
+                         "case for profiler captures)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-depth", type=int, default=4, help="N=1 e2e: calls in flight (1..16)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
