@@ -224,9 +224,18 @@ def describe(workload: str, world: int, args):
     elif workload == "c4":
         capped = f" [tables cut to {args.c4_max_rows} rows: a profiler-sized case]" \
             if getattr(args, "c4_max_rows", 0) else ""
+        mb = int(getattr(args, "c4_replicate_mb", 0)) if world > 1 else 0
+        if mb:
+            from forward_b200 import workloads
+            small = sum(1 for r in workloads.config4_rows() if int(r) * C4["dim"] * 4 < (mb << 20))
+            placing = (f"the {small} tables under {mb} MiB live on every rank, which pools its own bags of "
+                       f"them; the other {C4['tables'] - small} are placed whole on one rank each and their ")
+        else:
+            placing = "tables placed whole on ranks, "
         base.update(workload="c4: 26 tables of 1e3..3e7 rows x 128 fp32 (42 GB), 65536 bags x 20 Zipf(1.1) "
-                             "indices per table, per-sample weights, sum; tables placed whole on ranks, "
+                             "indices per table, per-sample weights, sum; " + placing +
                              f"pooled rows exchanged to [65536/{world}, 26, 128] fp32 per rank" + capped,
+                    replicated_below_mib=mb,
                     bags_per_step=C4["bags"], tables=C4["tables"], dim=C4["dim"],
                     parallelism=f"tablewise{world}" if world > 1 else "single",
                     exchange=args.exchange if world > 1 else None,
@@ -586,10 +595,18 @@ class C4Workload:
         self.T = len(self.rows)
         n_per_table = C4["bags"] * self.L
         self.owner = fd.place_tables([r * self.dim * 4 for r in self.rows], world,
-                                     [n_per_table] * self.T)
+                                     [n_per_table] * self.T,
+                                     replicate_below_bytes=int(getattr(args, "c4_replicate_mb", 0)) << 20)
         self.mine = [t for t in range(self.T) if self.owner[t] == rank]
+        # tables small enough to live on every rank: each rank pools its own bags of them, no exchange
+        self.replicated = [t for t in range(self.T) if self.owner[t] == fd.REPLICATED]
+        self.here = sorted(self.mine + self.replicated)
+        per = fd.bags_per_rank(C4["bags"], world)
+        self.own_lo = min(C4["bags"], rank * per)
+        self.own_n = min(C4["bags"], (rank + 1) * per) - self.own_lo
         self.tables, self.bags, self.h_in, self.d_in, self.d_idx, self.d_w = {}, {}, {}, {}, {}, {}
-        for t in self.mine:
+        self.copies = []      # (device view, pinned host view) of what a step's inputs are on this rank
+        for t in self.here:
             tab = torch.empty((self.rows[t], self.dim), dtype=torch.float32, device=dev)
             capi.fill_table(tab, 0, seed=300 + t, scale=0.1)
             self.tables[t] = tab
@@ -601,12 +618,18 @@ class C4Workload:
             self.d_in[t] = self.h_in[t].to(dev)
             self.d_idx[t] = self.d_in[t][:n_per_table]
             self.d_w[t] = self.d_in[t][n_per_table:].view(torch.float32)
+            if t in self.mine:
+                self.copies.append((self.d_in[t], self.h_in[t]))
+            else:             # a replicated table: only this rank's bags (their indices, their weights)
+                a, b = self.own_lo * self.L, (self.own_lo + self.own_n) * self.L
+                for base in (0, n_per_table):
+                    self.copies.append((self.d_in[t][base + a:base + b], self.h_in[t][base + a:base + b]))
         self.batches = [workloads.Bags(np.empty(n_per_table, dtype=np.int32), None, fixed_len=self.L)]
         self.bag = None
         self.pool_only = None
         self._last = None
         stream = torch.cuda.current_stream()
-        self.launches_per_step = len(self.mine)
+        self.launches_per_step = len(self.here)
         if world == 1:
             out = torch.empty((C4["bags"], self.T, self.dim), dtype=torch.float32, device=dev)
             params = [capi.make_params(self.tables[t], self.d_idx[t], None, out=out[:, t, :],
@@ -625,35 +648,61 @@ class C4Workload:
             return
         self.bag = fd.TableWiseBags(self.tables, self.owner, dim=self.dim, max_bags=C4["bags"],
                                     exchange=args.exchange, wire_dtype=capi.F32, mode=self.mode,
-                                    fixed_len=self.L, ship=args.ship, lookback=args.lookback)
-        prepared = self.bag.prepare({t: (self.d_idx[t], None, self.d_w[t]) for t in self.mine})
+                                    fixed_len=self.L, ship=args.ship, lookback=args.lookback,
+                                    local_streams=getattr(args, "local_streams", None))
+        prepared = self.bag.prepare({t: (self.d_idx[t], None, self.d_w[t]) for t in self.here})
 
         def step(k, events=None):
             self._last = self.bag.forward(prepared, pool_events=events)
         self.step = step
-        local = torch.empty((C4["bags"], max(1, len(self.mine)), self.dim), dtype=torch.float32,
+        local = torch.empty((C4["bags"], max(1, len(self.here)), self.dim), dtype=torch.float32,
                             device=dev)
+        a, b = self.own_lo * self.L, (self.own_lo + self.own_n) * self.L
         lp = [capi.make_params(self.tables[t], self.d_idx[t], None, out=local[:, j, :], mode=self.mode,
-                               fixed_len=self.L, per_sample_weights=self.d_w[t])
-              for j, t in enumerate(self.mine)]
+                               fixed_len=self.L, per_sample_weights=self.d_w[t]) if t in self.mine else
+              capi.make_params(self.tables[t], self.d_idx[t][a:b], None, out=local[:self.own_n, j, :],
+                               mode=self.mode, fixed_len=self.L, per_sample_weights=self.d_w[t][a:b])
+              for j, t in enumerate(self.here)]
+
+        # the same launches with local stores only, queued as the step queues them: this rank's
+        # whole tables on the current stream, the replicated ones spread over two more streams
+        n_aux = 2 if getattr(args, "local_streams", None) is None else int(args.local_streams)
+        aux = [torch.cuda.Stream() for _ in range(n_aux if len(self.replicated) > 1 else 0)]
+        fork, joins = torch.cuda.Event(), [torch.cuda.Event() for _ in aux]
+        whole = [p for p, t in zip(lp, self.here) if t in self.mine]
+        shares = [p for p, t in zip(lp, self.here) if t not in self.mine]
+        lanes = len(aux) + (1 if (not whole or not aux) else 0)
 
         def pool_only(k):
-            for p in lp:
+            if aux:
+                fork.record(stream)
+                for a_ in aux:
+                    a_.wait_event(fork)
+            for p in whole:
                 capi.forward(p, stream.cuda_stream)
+            for i, p in enumerate(shares):
+                lane = i % lanes
+                capi.forward(p, aux[lane].cuda_stream if lane < len(aux) else stream.cuda_stream)
+            for a_, j in zip(aux, joins):
+                j.record(a_)
+                stream.wait_event(j)
         self.pool_only = pool_only
 
     def result(self):
         return self._last
 
     def lookups(self, k: int) -> int:
-        return len(self.mine) * C4["bags"] * self.L
+        return (len(self.mine) * C4["bags"] + len(self.replicated) * self.own_n) * self.L
 
     def algorithmic_bytes(self, k: int) -> float:
         from forward_b200 import workloads
-        n = C4["bags"] * self.L
-        return float(len(self.mine) * workloads.algorithmic_bytes(
-            gathered_rows=n, dim=self.dim, table_itemsize=4, num_indices=n, num_offsets=0,
-            index_itemsize=4, num_bags=C4["bags"], out_itemsize=4, weighted=True))
+        total = 0.0
+        for count, bags in ((len(self.mine), C4["bags"]), (len(self.replicated), self.own_n)):
+            n = bags * self.L
+            total += count * workloads.algorithmic_bytes(
+                gathered_rows=n, dim=self.dim, table_itemsize=4, num_indices=n, num_offsets=0,
+                index_itemsize=4, num_bags=bags, out_itemsize=4, weighted=True)
+        return float(total)
 
     def egress_bytes(self) -> int:
         """Pooled bytes this rank sends to other ranks per step."""
@@ -684,7 +733,9 @@ class C4Workload:
             take = local_rows + r * per
             keep = take < C4["bags"]
             take = take[keep]
-            for t in self.mine:
+            for t in self.here:
+                if t in self.replicated and r != self.rank:
+                    continue      # a replicated table's column is checked by the rank that pooled it
                 b = self.bags[t]
                 idx = b.indices.reshape(-1, self.L)[take].reshape(-1)
                 w = b.per_sample_weights.reshape(-1, self.L)[take].reshape(-1)
@@ -738,8 +789,8 @@ class C4Workload:
                     copied[j].record(back)
         else:
             def step(k):
-                for t in self.mine:
-                    self.d_in[t].copy_(self.h_in[t], non_blocking=True)
+                for dst, src in self.copies:
+                    dst.copy_(src, non_blocking=True)
                 self.step(k)
                 self.bag.sync_result()
                 h_out[k % 2].copy_(self.result(), non_blocking=True)
@@ -759,7 +810,7 @@ class C4Workload:
             tt = torch.tensor([dt], dtype=torch.float64, device=self.dev)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             dt = float(tt.item())
-        h2d = sum(self.h_in[t].numel() * 4 for t in self.mine)
+        h2d = sum(src.numel() * 4 for _, src in self.copies)
         d2h = h_out[0].numel() * h_out[0].element_size()
         return {"value": self.T * C4["bags"] * self.L * steps / dt, "unit": "lookups/s",
                 "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
@@ -880,10 +931,13 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
         # what the host spends queueing one step (no synchronisation inside the loop): a step
         # cannot run faster than this
         barrier()
+        # few enough steps that the launch queue never fills (a full queue would make the host wait
+        # for the device and the figure would be device time)
+        reps = max(5, min(100, 300 // max(1, getattr(wl, "launches_per_step", 1) + 3)))
         t0 = time.perf_counter()
-        for k in range(100):
+        for k in range(reps):
             wl.step(k)
-        host_us = (time.perf_counter() - t0) * 1e4
+        host_us = (time.perf_counter() - t0) * 1e6 / reps
         wl.bag.sync_result()
         torch.cuda.synchronize()
     lookups = total_lookups(wl, steps, dev)
@@ -1398,6 +1452,11 @@ def main():
     ap.add_argument("--c5-window", type=int, default=1,
                     help="c5 at N=1: hold only one of this many row windows of the table and pool "
                          "that rank's partial bags (the per-rank kernel of a sharded run; no exchange)")
+    ap.add_argument("--c4-replicate-mb", type=int, default=256,
+                    help="c4 at N>1: tables smaller than this many MiB live on every rank, which pools its "
+                         "own bags of them (no exchange); 0 = every table on one rank only")
+    ap.add_argument("--local-streams", type=int, default=None, choices=[0, 1, 2],
+                    help="c4 at N>1: auxiliary streams for the replicated tables (default: the library's)")
     ap.add_argument("--c4-max-rows", type=int, default=0,
                     help="c4: cut every table to this many rows (0 = the configuration's sizes; a smaller "
                          "case for profiler captures)")

@@ -518,6 +518,27 @@ int fwd_eb_shard_push(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, vo
   return 0;
 }
 
+int fwd_eb_shard_pool_local(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream) {
+  int rc = check_exchange(x);
+  if (rc) return rc;
+  if (!p) return fail(FWD_EB_EINVAL, "params is null");
+  if (x->layout != FWD_EB_LAYOUT_TABLE_WISE)
+    return fail(FWD_EB_EINVAL, "a replicated table belongs to the table-wise layout");
+  if (p->mode == FWD_EB_MODE_GATHER) return fail(FWD_EB_EUNSUPPORTED, "GATHER has no pooled row to place");
+  if (x->wire_dtype != FWD_EB_F32 && x->wire_dtype != FWD_EB_F16)
+    return fail(FWD_EB_EINVAL, "the table-wise buffer holds fp32 or fp16 rows");
+  if (p->num_bags > x->bags_per_rank)
+    return fail(FWD_EB_EINVAL, "%lld bags, but a rank owns at most %lld", (long long)p->num_bags,
+                (long long)x->bags_per_rank);
+  fwd_eb_params q = *p;
+  const size_t part = part_bytes(x, p->dim) * (x->epoch % FWD_EB_SHARD_BUFFERS);
+  q.out = static_cast<char*>(x->peer_slots[x->rank]) + part +
+          (size_t)x->table_index * (size_t)p->dim * wire_bytes(x->wire_dtype);
+  q.out_dtype = x->wire_dtype;
+  q.out_stride = (int64_t)x->num_tables * p->dim;
+  return fwd_eb_forward(&q, stream);
+}
+
 size_t fwd_eb_shard_stage_bytes(int32_t world, int64_t bags_per_rank, int32_t stage_tables, int32_t dim,
                                 int32_t wire_dtype) {
   if (world < 1 || bags_per_rank < 1 || stage_tables < 1 || dim < 1) return 0;
@@ -697,6 +718,13 @@ struct fwd_eb_pipeline {
   uint32_t epoch = 0;
   uint32_t every = FWD_EB_PIPELINE_WAIT_EVERY;
   uint32_t depth = FWD_EB_PIPELINE_WAIT_DEPTH;
+  // Replicated tables of a hybrid table-wise step are pooled on these streams, beside the pushes
+  // on the caller's stream: the launches are independent of each other, and a rank's share of a
+  // batch is a grid of one or two waves whose ramp and tail another grid can fill.
+  cudaStream_t aux[FWD_EB_PIPELINE_LOCAL_STREAMS] = {};
+  cudaEvent_t fork = nullptr;
+  cudaEvent_t joined[FWD_EB_PIPELINE_LOCAL_STREAMS] = {};
+  int32_t local_streams = FWD_EB_PIPELINE_LOCAL_STREAMS;
 };
 
 // A step that fails its host-side checks before anything was launched must not leave this rank
@@ -756,6 +784,11 @@ int fwd_eb_pipeline_create(fwd_eb_pipeline** out) {
     e = cudaEventCreateWithFlags(&pl->pushed[k], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pl->done[k], cudaEventDisableTiming);
   }
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pl->fork, cudaEventDisableTiming);
+  for (int k = 0; k < FWD_EB_PIPELINE_LOCAL_STREAMS && e == cudaSuccess; ++k) {
+    e = cudaStreamCreateWithFlags(&pl->aux[k], cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&pl->joined[k], cudaEventDisableTiming);
+  }
   if (e != cudaSuccess) {
     int rc = cuda_fail(e, "creating the pipeline's stream and events");
     fwd_eb_pipeline_destroy(pl);
@@ -772,11 +805,27 @@ void fwd_eb_pipeline_destroy(fwd_eb_pipeline* pl) {
     if (pl->pushed[k]) cudaEventDestroy(pl->pushed[k]);
     if (pl->done[k]) cudaEventDestroy(pl->done[k]);
   }
+  for (int k = 0; k < FWD_EB_PIPELINE_LOCAL_STREAMS; ++k) {
+    if (pl->aux[k]) {
+      cudaStreamSynchronize(pl->aux[k]);
+      cudaStreamDestroy(pl->aux[k]);
+    }
+    if (pl->joined[k]) cudaEventDestroy(pl->joined[k]);
+  }
+  if (pl->fork) cudaEventDestroy(pl->fork);
   if (pl->side) cudaStreamDestroy(pl->side);
   delete pl;
 }
 
 void* fwd_eb_pipeline_side_stream(fwd_eb_pipeline* pl) { return pl ? pl->side : nullptr; }
+
+int fwd_eb_pipeline_set_local_streams(fwd_eb_pipeline* pl, int32_t streams) {
+  if (!pl) return fail(FWD_EB_EINVAL, "null pipeline");
+  if (streams < 0 || streams > FWD_EB_PIPELINE_LOCAL_STREAMS)
+    return fail(FWD_EB_EINVAL, "0..%d streams for replicated tables (got %d)", FWD_EB_PIPELINE_LOCAL_STREAMS, streams);
+  pl->local_streams = streams;
+  return 0;
+}
 
 int fwd_eb_pipeline_set_lookback(fwd_eb_pipeline* pl, int32_t every, int32_t depth) {
   if (!pl) return fail(FWD_EB_EINVAL, "null pipeline");
@@ -952,18 +1001,29 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
   return 0;
 }
 
-int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
-                                   const int32_t* table_index, int32_t count,
-                                   fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
-                                   void** d_result) {
-  if (!pl || !x || count < 0 || (count > 0 && (!params || !table_index)))
+int fwd_eb_pipeline_step_tablewise_hybrid(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
+                                          const int32_t* table_index, int32_t count,
+                                          const fwd_eb_params* const* local_params,
+                                          const int32_t* local_table_index, int32_t local_count,
+                                          fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
+                                          void** d_result) {
+  if (!pl || !x || count < 0 || (count > 0 && (!params || !table_index)) || local_count < 0 ||
+      (local_count > 0 && (!local_params || !local_table_index)))
     return fail(FWD_EB_EINVAL, "null argument");
+  if (local_count > 0 && x->tickets)
+    return fail(FWD_EB_EUNSUPPORTED, "replicated tables need the flag raised behind the step's last "
+                "kernel (x->tickets must be null)");
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   int rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
   const bool from_push = x->tickets != nullptr && count > 0 && !x->stage;
   if (x->stage && count > kShipMaxTables)
     return fail(FWD_EB_ETOOBIG, "shipping takes at most %d tables per rank and step (got %d)", kShipMaxTables, count);
+  if (local_count > 1 && pl->local_streams > 0) {
+    cudaError_t e = cudaEventRecord(pl->fork, main);
+    for (int k = 0; k < pl->local_streams && e == cudaSuccess; ++k) e = cudaStreamWaitEvent(pl->aux[k], pl->fork, 0);
+    if (e != cudaSuccess) return pipeline_abort(pl, cuda_fail(e, "forking the streams of the replicated tables"));
+  }
   int64_t batch = 0;
   for (int i = 0; i < count; ++i) {
     x->table_index = table_index[i];
@@ -975,6 +1035,23 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
     if (rc) return i == 0 ? pipeline_abort(pl, rc) : rc;   // nothing launched yet: take the number back
   }
   x->raise_from_push = from_push ? 1 : 0;
+  // Replicated tables: independent launches with local stores, spread over the auxiliary streams
+  // (which start where the caller's stream stood before this step's pushes and are joined before
+  // the hand-over), so that they run beside the pushes and beside each other.  A rank without
+  // pushes of its own takes a share on the caller's stream too.
+  const int aux = local_count > 1 ? pl->local_streams : 0;
+  const int lanes = aux + ((count == 0 || aux == 0) ? 1 : 0);
+  for (int i = 0; i < local_count; ++i) {
+    const int lane = i % lanes;
+    x->table_index = local_table_index[i];
+    rc = fwd_eb_shard_pool_local(local_params[i], x, lane < aux ? pl->aux[lane] : main);
+    if (rc) return (count == 0 && i == 0) ? pipeline_abort(pl, rc) : rc;   // nothing launched yet
+  }
+  for (int k = 0; k < aux; ++k) {
+    cudaError_t e = cudaEventRecord(pl->joined[k], pl->aux[k]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(main, pl->joined[k], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "joining the streams of the replicated tables");
+  }
   if (!from_push) {
     rc = pipeline_handover(pl, main);
     if (rc) return rc;
@@ -988,6 +1065,14 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
   cudaError_t e = cudaEventRecord(pl->done[pl->epoch % FWD_EB_SHARD_BUFFERS], pl->side);
   if (e != cudaSuccess) return cuda_fail(e, "cudaEventRecord (side)");
   return 0;
+}
+
+int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
+                                   const int32_t* table_index, int32_t count,
+                                   fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
+                                   void** d_result) {
+  return fwd_eb_pipeline_step_tablewise_hybrid(pl, params, table_index, count, nullptr, nullptr, 0, x, dim,
+                                               main_stream, d_result);
 }
 
 int fwd_eb_pipeline_sync_result(fwd_eb_pipeline* pl, void* stream) {

@@ -52,16 +52,30 @@ def owned_bags(num_bags: int, world: int, rank: int) -> tuple[int, int]:
     return lo, min(per, num_bags - lo)
 
 
-def place_tables(table_bytes: list[int], world: int, lookups: list[int] | None = None) -> list[int]:
+REPLICATED = -1   # owner value of a table that every rank holds
+
+
+def place_tables(table_bytes: list[int], world: int, lookups: list[int] | None = None,
+                 replicate_below_bytes: int = 0) -> list[int]:
     """Owner rank of every table.  Greedy longest-processing-time on the per-call cost (lookups per
     table; equal when None) with ties broken towards the rank holding fewer bytes, so both time
-    and capacity stay balanced.  Deterministic."""
+    and capacity stay balanced.  Deterministic.
+
+    Tables smaller than `replicate_below_bytes` get REPLICATED instead of an owner: every rank
+    holds them and pools its own bags only, so they cost no exchange and spread evenly whatever
+    the table count (a few hundred MB per table is nothing next to 180 GB of HBM)."""
     n = len(table_bytes)
     cost = list(lookups) if lookups is not None else [1] * n
-    order = sorted(range(n), key=lambda t: (-cost[t], -table_bytes[t], t))
+    owner = [0] * n
+    placed = []
+    for t in range(n):
+        if world > 1 and table_bytes[t] < replicate_below_bytes:
+            owner[t] = REPLICATED
+        else:
+            placed.append(t)
+    order = sorted(placed, key=lambda t: (-cost[t], -table_bytes[t], t))
     load = [0] * world
     held = [0] * world
-    owner = [0] * n
     for t in order:
         r = min(range(world), key=lambda k: (load[k], held[k], k))
         owner[t] = r
@@ -125,6 +139,14 @@ SIGNATURES = {
                                                  C.POINTER(C.c_int32), C.c_int32,
                                                  C.POINTER(ShardExchange), C.c_int32, C.c_void_p,
                                                  C.POINTER(C.c_void_p)]),
+    "fwd_eb_pipeline_step_tablewise_hybrid": (C.c_int, [C.c_void_p, C.POINTER(C.POINTER(capi.Params)),
+                                                        C.POINTER(C.c_int32), C.c_int32,
+                                                        C.POINTER(C.POINTER(capi.Params)),
+                                                        C.POINTER(C.c_int32), C.c_int32,
+                                                        C.POINTER(ShardExchange), C.c_int32, C.c_void_p,
+                                                        C.POINTER(C.c_void_p)]),
+    "fwd_eb_pipeline_set_local_streams": (C.c_int, [C.c_void_p, C.c_int32]),
+    "fwd_eb_shard_pool_local": (C.c_int, [C.POINTER(capi.Params), C.POINTER(ShardExchange), C.c_void_p]),
     "fwd_eb_pipeline_sync_result": (C.c_int, [C.c_void_p, C.c_void_p]),
     "fwd_eb_pipeline_drain": (C.c_int, [C.c_void_p]),
     "fwd_eb_ipc_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
@@ -433,7 +455,9 @@ class _DeviceView:
 
 
 class TableWiseBags:
-    """Many tables, each held whole by one rank; pooled outputs land as [bags_owned, T, dim].
+    """Many tables, each held whole by one rank (owner[t] = that rank) or by every rank (owner[t] =
+    REPLICATED: no exchange, each rank pools the bags it owns); pooled outputs land as
+    [bags_owned, T, dim].
 
     exchange="push": each pooling kernel writes its table's column block of every owner's result
     buffer over NVLink (no staging copy, no separate all-to-all kernel).  exchange="nccl": pooled
@@ -442,7 +466,8 @@ class TableWiseBags:
     def __init__(self, local_tables: dict, owner: list[int], *, dim: int, max_bags: int, group=None,
                  exchange: str = "push", wire_dtype: int = capi.F32, mode: int = capi.MODE_SUM,
                  fixed_len: int = 0, padding_idx: int = -1, flag_from_pool: bool = False,
-                 ship: bool = False, lookback: tuple[int, int] | None = None):
+                 ship: bool = False, lookback: tuple[int, int] | None = None,
+                 local_streams: int | None = None):
         import torch
         import torch.distributed as dist
         self.group = group
@@ -451,8 +476,11 @@ class TableWiseBags:
         self.owner = list(owner)
         self.num_tables = len(owner)
         self.mine = [t for t, r in enumerate(owner) if r == self.rank]
-        if sorted(local_tables) != self.mine:
-            raise ValueError("local_tables must hold exactly the tables this rank owns")
+        self.replicated = [t for t, r in enumerate(owner) if r == REPLICATED]
+        if sorted(local_tables) != sorted(self.mine + self.replicated):
+            raise ValueError("local_tables must hold exactly the tables this rank owns and the replicated ones")
+        if self.replicated and flag_from_pool:
+            raise ValueError("replicated tables need the flag raised behind the step's last kernel")
         self.tables = local_tables
         self.dim, self.mode, self.fixed_len, self.padding_idx = dim, mode, fixed_len, padding_idx
         self.per = bags_per_rank(max_bags, self.world)
@@ -467,6 +495,8 @@ class TableWiseBags:
             capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
             if lookback:
                 capi.check(_lib().fwd_eb_pipeline_set_lookback(self._pl, *lookback))
+            if local_streams is not None:
+                capi.check(_lib().fwd_eb_pipeline_set_local_streams(self._pl, local_streams))
             # the flag exchange runs on the pipeline's side stream, beside the next pooling
             self.side = torch.cuda.ExternalStream(_lib().fwd_eb_pipeline_side_stream(self._pl), device=dev)
             nbytes = _lib().fwd_eb_shard_tablewise_bytes(self.per, self.num_tables, dim, wire_dtype)
@@ -484,16 +514,41 @@ class TableWiseBags:
         else:
             tl = max(1, len(self.mine))
             self.send = torch.zeros((self.per * self.world, tl, dim), dtype=torch.float32, device=dev)
-            self.recv = torch.empty((self.per * self.num_tables, dim), dtype=torch.float32, device=dev)
+            placed = sum(1 for r in owner if r != REPLICATED)
+            self.recv = torch.empty((self.per * placed, dim), dtype=torch.float32, device=dev)
             self.result = torch.empty((self.per, self.num_tables, dim), dtype=torch.float32, device=dev)
+            self._max_bags = max_bags
             counts = [sum(1 for r in owner if r == src) for src in range(self.world)]
             self.in_splits = [self.per * len(self.mine)] * self.world
             self.out_splits = [self.per * c for c in counts]
             self.by_src = [[t for t, r in enumerate(owner) if r == src] for src in range(self.world)]
 
+    def _own_bags(self, idx, off, w):
+        """The part of a whole-batch input that describes the bags this rank owns: (indices,
+        offsets, weights, include_last_offset), or None when it owns none of them."""
+        lo = self.rank * self.per
+        if self.fixed_len > 0:
+            L = self.fixed_len
+            nb = idx.numel() // L
+            hi = min(nb, lo + self.per)
+            if hi <= lo:
+                return None
+            flat = idx.reshape(-1)
+            return flat[lo * L:hi * L], None, (w.reshape(-1)[lo * L:hi * L] if w is not None else None), False
+        nb = off.numel()
+        hi = min(nb, lo + self.per)
+        if hi <= lo:
+            return None
+        # offsets stay absolute: the indices (and weights) are passed whole; a next bag's start, where
+        # there is one, closes this rank's last bag
+        if hi < nb:
+            return idx, off[lo:hi + 1], w, True
+        return idx, off[lo:hi], w, False
+
     def prepare(self, inputs: dict):
         """Argument blocks for forward() on these tensors, built once for inputs that are reused
-        (the tensors must stay alive and in place)."""
+        (the tensors must stay alive and in place).  inputs[t] describes the WHOLE batch, for the
+        replicated tables too."""
         blocks = []
         for k, t in enumerate(self.mine):
             idx, off, w = inputs[t]
@@ -505,7 +560,22 @@ class TableWiseBags:
         n = len(blocks)
         ptrs = (C.POINTER(capi.Params) * max(n, 1))(*[C.pointer(p) for _, p in blocks])
         tabs = (C.c_int32 * max(n, 1))(*[t for t, _ in blocks])
-        return [blocks, ptrs, tabs, n]
+        local, keep = [], []
+        for t in self.replicated:
+            own = self._own_bags(*inputs[t])
+            if own is None:
+                continue
+            idx, off, w, incl = own
+            keep.append(own)
+            nb = idx.numel() // self.fixed_len if self.fixed_len > 0 else off.numel() - (1 if incl else 0)
+            out = self.tables[t][:1] if self.exchange == "push" else self.result[:nb, t, :]
+            local.append((t, capi.make_params(self.tables[t], idx, off, out=out, mode=self.mode,
+                                              fixed_len=self.fixed_len, per_sample_weights=w,
+                                              padding_idx=self.padding_idx, include_last_offset=incl)))
+        m = len(local)
+        lptrs = (C.POINTER(capi.Params) * max(m, 1))(*[C.pointer(p) for _, p in local])
+        ltabs = (C.c_int32 * max(m, 1))(*[t for t, _ in local])
+        return [blocks, ptrs, tabs, n, local, lptrs, ltabs, m, keep]
 
     def forward(self, inputs, pool_events=None):
         """inputs[t] = (indices, offsets_or_None, weights_or_None) for every table this rank owns,
@@ -515,14 +585,15 @@ class TableWiseBags:
         import torch
         import torch.distributed as dist
         prepared = inputs if isinstance(inputs, list) else self.prepare(inputs)
-        blocks, ptrs, tabs, n = prepared
+        blocks, ptrs, tabs, n, local, lptrs, ltabs, m, _ = prepared
         stream = capi.current_stream_ptr()
         if self.exchange == "push":
             if pool_events:
                 pool_events[0].record()
             res = C.c_void_p()
-            capi.check(_lib().fwd_eb_pipeline_step_tablewise(self._pl, ptrs, tabs, n, C.byref(self.x),
-                                                             self.dim, C.c_void_p(stream), C.byref(res)))
+            capi.check(_lib().fwd_eb_pipeline_step_tablewise_hybrid(
+                self._pl, ptrs, tabs, n, lptrs, ltabs, m, C.byref(self.x), self.dim, C.c_void_p(stream),
+                C.byref(res)))
             if pool_events:
                 pool_events[1].record()   # after the push launches (the flag exchange is on the side stream)
             self.ready = True
@@ -536,7 +607,7 @@ class TableWiseBags:
         tl = len(self.mine)
         if pool_events:
             pool_events[0].record()
-        for t, p in blocks:
+        for t, p in blocks + local:
             capi.forward(p, stream)
         if pool_events:
             pool_events[1].record()

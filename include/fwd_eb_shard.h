@@ -54,6 +54,7 @@ extern "C" {
 #define FWD_EB_PIPELINE_WAIT_DEPTH 2
 #define FWD_EB_PIPELINE_WAIT_EVERY_TICKETS 3
 #define FWD_EB_SHARD_BUFFERS 16
+#define FWD_EB_PIPELINE_LOCAL_STREAMS 2   /* auxiliary streams for a hybrid step's replicated tables */
 #define FWD_EB_SHARD_TIMEOUT 1
 #define FWD_EB_IPC_HANDLE_BYTES 64
 
@@ -236,6 +237,26 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
                                    const int32_t* table_index, int32_t count,
                                    fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
                                    void** d_result);
+
+/* Table-wise with replicated tables.  A table small enough to live on every rank needs no
+ * exchange: each rank pools only the bags it owns and stores the rows into its own buffer.
+ * fwd_eb_shard_pool_local does that for one table: `p` describes this rank's bags only (bag 0 of
+ * `p` is the first bag this rank owns, num_bags <= bags_per_rank), the rows land in column block
+ * x->table_index of this rank's buffer part of call x->epoch, written by the single-GPU kernels
+ * with local stores; `p->out` is ignored.  The hybrid step queues the pushes of the `count`
+ * tables this rank holds alone, then the `local_count` replicated tables, then the flag exchange
+ * as fwd_eb_pipeline_step_tablewise does.  Needs x->tickets == NULL when local_count > 0. */
+int fwd_eb_shard_pool_local(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream);
+/* The hybrid step pools the replicated tables on up to FWD_EB_PIPELINE_LOCAL_STREAMS streams of
+ * the pipeline's own, forked from `main_stream` before the step's pushes and joined before the
+ * flag exchange; 0 queues them on `main_stream` behind the pushes instead. */
+int fwd_eb_pipeline_set_local_streams(fwd_eb_pipeline* pl, int32_t streams);
+int fwd_eb_pipeline_step_tablewise_hybrid(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
+                                          const int32_t* table_index, int32_t count,
+                                          const fwd_eb_params* const* local_params,
+                                          const int32_t* local_table_index, int32_t local_count,
+                                          fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
+                                          void** d_result);
 
 /* Make `stream` wait for the last step's result. */
 int fwd_eb_pipeline_sync_result(fwd_eb_pipeline* pl, void* stream);

@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from forward_b200 import dist as fd
+from forward_b200 import workloads
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -67,6 +68,43 @@ def _worker(rank, world, port, method, tmp):
     mine = fd2.exchange_partials(torch.from_numpy(partial), world, per, method=method, fold=fold)
     np.save(os.path.join(tmp, f"{method}_{rank}.npy"), mine.numpy())
     dist.destroy_process_group()
+
+
+def test_small_tables_are_replicated_and_the_rest_placed_evenly():
+    rows = workloads.config4_rows()
+    nbytes = [int(r) * 128 * 4 for r in rows]
+    owner = fd.place_tables(nbytes, 8, replicate_below_bytes=256 << 20)
+    rep = [t for t, r in enumerate(owner) if r == fd.REPLICATED]
+    assert len(rep) == 18 and all(nbytes[t] < (256 << 20) for t in rep)
+    placed = [r for r in owner if r != fd.REPLICATED]
+    assert sorted(placed) == list(range(8))                  # the eight large tables: one per rank
+    assert sum(nbytes[t] for t in rep) < 1.2e9               # 1.15 GB on every rank
+    assert fd.REPLICATED not in fd.place_tables(nbytes, 1, replicate_below_bytes=256 << 20)   # one rank: nothing to replicate
+
+
+def test_a_rank_s_own_bags_of_a_replicated_table():
+    """TableWiseBags._own_bags: the slice of a whole-batch input that a rank pools itself."""
+    import types
+
+    import torch
+    own = fd.TableWiseBags._own_bags
+    idx = torch.arange(40, dtype=torch.int32)
+    w = torch.arange(40, dtype=torch.float32)
+    # fixed length 4, 10 bags on 3 ranks (4 + 4 + 2)
+    for rank, (lo, n) in enumerate([(0, 4), (4, 4), (8, 2)]):
+        me = types.SimpleNamespace(rank=rank, per=4, fixed_len=4)
+        i, o, ww, incl = own(me, idx.view(10, 4), None, w)
+        assert o is None and not incl
+        assert i.tolist() == list(range(lo * 4, (lo + n) * 4)) and ww.tolist() == i.float().tolist()
+    assert own(types.SimpleNamespace(rank=3, per=4, fixed_len=4), idx.view(10, 4), None, w) is None
+    # ragged: offsets stay absolute, the next rank's first start closes the last bag
+    off = torch.tensor([0, 3, 3, 10, 12, 20, 31, 31, 35, 36], dtype=torch.int32)
+    me = types.SimpleNamespace(rank=1, per=4, fixed_len=0)
+    i, o, ww, incl = own(me, idx, off, None)
+    assert i is idx and ww is None and incl and o.tolist() == [12, 20, 31, 31, 35]
+    me = types.SimpleNamespace(rank=2, per=4, fixed_len=0)
+    i, o, ww, incl = own(me, idx, off, None)
+    assert not incl and o.tolist() == [35, 36]               # the batch's last bags end at num_indices
 
 
 @pytest.mark.parametrize("method", ["a2a", "nccl"])

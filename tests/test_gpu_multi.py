@@ -122,6 +122,48 @@ def _worker(rank, world, port, tmp):
                 failures.append(f"tablewise {exchange} step{step}")
         dist.barrier()
         tw.close()
+    # table-wise with replicated tables: the two large tables live on one rank each, the three
+    # small ones on every rank (pooled there for the rank's own bags); fixed-length weighted bags
+    # and ragged bags, 1022 bags (the last rank owns fewer)
+    sizes = [600, 9000, 500, 12000, 700]
+    nb3 = 1022
+    owner = fd.place_tables([n * dim2 * 4 for n in sizes], world, replicate_below_bytes=1000 * dim2 * 4)
+    tables = [trng.standard_normal((n, dim2)).astype(np.float32) for n in sizes]
+    here = [t for t in range(ntab) if owner[t] in (rank, fd.REPLICATED)]
+    d_tables = {t: torch.from_numpy(tables[t]).to(dev) for t in here}
+    per = fd.bags_per_rank(nb3, world)
+    blo, mine_b = fd.owned_bags(nb3, world, rank)
+    for exchange in ("push", "nccl"):
+        for fixed in (L, 0):
+            tw = fd.TableWiseBags(d_tables, owner, dim=dim2, max_bags=nb3, exchange=exchange, fixed_len=fixed,
+                                  mode=capi.MODE_SUM if fixed else capi.MODE_MEAN)
+            for step in range(20 if exchange == "push" else 2):
+                irng = np.random.default_rng(300 + step)
+                if fixed:
+                    idx = [irng.integers(0, sizes[t], (nb3, L)).astype(np.int32) for t in range(ntab)]
+                    w = [irng.random(nb3 * L).astype(np.float32) for _ in range(ntab)]
+                    inputs = {t: (torch.from_numpy(idx[t]).to(dev), None, torch.from_numpy(w[t]).to(dev))
+                              for t in here}
+                else:
+                    bgs = [workloads.ragged_bags(sizes[t], irng.integers(0, 20, nb3), irng) for t in range(ntab)]
+                    inputs = {t: (torch.from_numpy(bgs[t].indices).to(dev), torch.from_numpy(bgs[t].offsets).to(dev),
+                                  None) for t in here}
+                res = tw.forward(inputs)
+                if step % 5 != 4 and exchange == "push":
+                    continue
+                tw.sync_result()
+                torch.cuda.synchronize()
+                if fixed:
+                    expect = np.stack([O.pool(tables[t], idx[t], fixed_len=L, per_sample_weights=w[t])
+                                       for t in range(ntab)], axis=1)
+                else:
+                    expect = np.stack([O.pool(tables[t], bgs[t].indices, bgs[t].offsets, mode=O.MODE_MEAN)
+                                       for t in range(ntab)], axis=1)
+                if not np.array_equal(res.cpu().numpy()[:mine_b], expect[blo:blo + mine_b]) or \
+                        tw.check_status() != 0:
+                    failures.append(f"tablewise replicated {exchange} fixed{fixed} step{step}")
+            dist.barrier()
+            tw.close()
     with open(os.path.join(tmp, f"rank{rank}.txt"), "w") as f:
         f.write("\n".join(failures))
     dist.destroy_process_group()

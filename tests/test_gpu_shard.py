@@ -391,6 +391,60 @@ def test_table_wise_push_lands_in_result_layout():
     assert all(int(k.item()) == 0 for k in keep)
 
 
+@pytest.mark.parametrize("wire", [capi.F32, capi.F16])
+def test_table_wise_with_replicated_tables_pooled_by_each_rank_for_its_own_bags(wire):
+    """Three ranks, five tables: the two large ones live on one rank each and are pushed, the
+    three small ones are held by every rank, which pools only the bags it owns straight into its
+    own buffer (fwd_eb_shard_pool_local).  Ragged bags, mean, 100 bags on 3 ranks (the last rank
+    owns fewer); every rank's [per, T, dim] equals the single-GPU result."""
+    rng = np.random.default_rng(19)
+    world, ntab, dim, nb = 3, 5, 64, 100
+    sizes = [300, 4000, 200, 5000, 250]
+    owner = fd.place_tables([n * dim * 2 for n in sizes], world, replicate_below_bytes=1000 * dim * 2)
+    assert [o == fd.REPLICATED for o in owner] == [True, False, True, False, True]
+    per = fd.bags_per_rank(nb, world)
+    lib, bufs, xs, keep = _setup(world, per, dim, wire, layout=fd.LAYOUT_TABLE_WISE, num_tables=ntab)
+    stream = C.c_void_p(capi.current_stream_ptr())
+    tables = [rng.standard_normal((n, dim)).astype(np.float16) for n in sizes]
+    bags = [workloads.ragged_bags(n, rng.integers(0, 30, nb), rng) for n in sizes]
+    d_tab = [_cuda(t) for t in tables]
+    d_idx = [_cuda(b.indices) for b in bags]
+    d_off = [_cuda(b.offsets) for b in bags]
+    for r in range(world):
+        xs[r].epoch = 2
+        for t in range(ntab):
+            xs[r].table_index = t
+            if owner[t] == r:
+                p = capi.make_params(d_tab[t], d_idx[t], d_off[t], out=d_tab[t][:1], mode=capi.MODE_MEAN)
+                capi.check(lib.fwd_eb_shard_push(C.byref(p), C.byref(xs[r]), stream))
+            elif owner[t] == fd.REPLICATED:
+                lo, hi = r * per, min(nb, (r + 1) * per)
+                last = hi == nb
+                off = d_off[t][lo:hi] if last else d_off[t][lo:hi + 1]
+                p = capi.make_params(d_tab[t], d_idx[t], off, out=d_tab[t][:1], mode=capi.MODE_MEAN,
+                                     include_last_offset=not last)
+                assert p.num_bags == hi - lo
+                capi.check(lib.fwd_eb_shard_pool_local(C.byref(p), C.byref(xs[r]), stream))
+    for r in range(world):
+        capi.check(lib.fwd_eb_shard_signal(C.byref(xs[r]), stream))
+    odt = np.float16 if wire == capi.F16 else np.float32
+    expect = np.stack([O.pool(tables[t], bags[t].indices, bags[t].offsets, mode=O.MODE_MEAN, out_dtype=odt)
+                       for t in range(ntab)], axis=1)
+    for r in range(world):
+        res = C.c_void_p()
+        capi.check(lib.fwd_eb_shard_wait(C.byref(xs[r]), dim, C.byref(res), stream))
+        torch.cuda.synchronize()
+        got = torch.as_tensor(fd._DeviceView(res.value, (per, ntab, dim), "<f2" if wire == capi.F16 else "<f4"),
+                              device="cuda").cpu().numpy()
+        mine = min(nb, (r + 1) * per) - r * per
+        assert np.array_equal(got[:mine].view(np.uint16 if wire == capi.F16 else np.uint32),
+                              expect[r * per:r * per + mine].view(np.uint16 if wire == capi.F16 else np.uint32))
+    assert all(int(k.item()) == 0 for k in keep)
+    # a batch larger than a rank's share is refused
+    p = capi.make_params(d_tab[0], d_idx[0], d_off[0], out=d_tab[0][:1], mode=capi.MODE_MEAN)
+    assert lib.fwd_eb_shard_pool_local(C.byref(p), C.byref(xs[0]), stream) == capi.EINVAL
+
+
 def test_wait_gives_up_and_reports_instead_of_hanging():
     """Nothing raises rank 1's flag: the bounded wait runs out after a few thousand polls, sets
     the status word and leaves the output alone; the context stays usable."""
