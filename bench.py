@@ -636,11 +636,17 @@ class C4Workload:
                                        mode=self.mode, fixed_len=self.L,
                                        per_sample_weights=self.d_w[t]) for t in self.mine]
 
+            packed = capi.pack_params(params)
+            one_stream = getattr(args, "local_streams", None) == 0
+
             def step(k, events=None):
                 if events:
                     events[0].record()
-                for p in params:
-                    capi.forward(p, stream.cuda_stream)
+                if one_stream:
+                    for p in params:
+                        capi.forward(p, stream.cuda_stream)
+                else:       # the 26 tables are independent: spread over the library's streams
+                    capi.forward_many(packed, stream.cuda_stream)
                 if events:
                     events[1].record()
                 self._last = out
@@ -1456,7 +1462,8 @@ def main():
                     help="c4 at N>1: tables smaller than this many MiB live on every rank, which pools its "
                          "own bags of them (no exchange); 0 = every table on one rank only")
     ap.add_argument("--local-streams", type=int, default=None, choices=[0, 1, 2],
-                    help="c4 at N>1: auxiliary streams for the replicated tables (default: the library's)")
+                    help="c4: auxiliary streams for independent tables (N=1: 0 = one stream, else "
+                         "fwd_eb_forward_many; N>1: streams for the replicated tables; default: the library's)")
     ap.add_argument("--c4-max-rows", type=int, default=0,
                     help="c4: cut every table to this many rows (0 = the configuration's sizes; a smaller "
                          "case for profiler captures)")

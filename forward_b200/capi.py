@@ -53,6 +53,7 @@ SIGNATURES = {
     "fwd_eb_params_size": (C.c_size_t, []),
     "fwd_eb_last_error_string": (C.c_char_p, []),
     "fwd_eb_forward": (C.c_int, [C.POINTER(Params), C.c_void_p]),
+    "fwd_eb_forward_many": (C.c_int, [C.POINTER(C.POINTER(Params)), C.c_int32, C.c_void_p]),
     "fwd_eb_workspace_size": (C.c_size_t, [C.POINTER(Params)]),
     "fwd_eb_pick_strategy": (C.c_int, [C.POINTER(Params)]),
     "fwd_eb_forward_static_scratch": (C.c_int, [C.POINTER(Params), C.c_void_p]),
@@ -179,6 +180,20 @@ def make_params(table, indices, offsets=None, *, out, mode=MODE_SUM, fixed_len=0
 def forward(params: Params, stream: int | None = None) -> None:
     check(lib().fwd_eb_forward(C.byref(params), C.c_void_p(stream if stream is not None
                                                            else current_stream_ptr())))
+
+
+def pack_params(params_list):
+    """A C array of pointers to the given Params, for forward_many (keep the list alive)."""
+    n = len(params_list)
+    return (C.POINTER(Params) * max(n, 1))(*[C.pointer(p) for p in params_list]), n
+
+
+def forward_many(packed, stream: int | None = None) -> None:
+    """Independent calls (one per table of a model) spread over the caller's stream and the
+    library's auxiliary streams; `packed` = pack_params([...])."""
+    ptrs, n = packed
+    check(lib().fwd_eb_forward_many(ptrs, n, C.c_void_p(stream if stream is not None
+                                                        else current_stream_ptr())))
 
 
 def embedding_bag(table, indices, offsets=None, *, mode=MODE_SUM, fixed_len=0,

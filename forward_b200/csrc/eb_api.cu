@@ -12,6 +12,7 @@
 #include <cstring>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "eb_compact.cuh"
 #include "eb_internal.h"
@@ -664,6 +665,68 @@ int fwd_eb_forward(const fwd_eb_params* p, void* stream) {
   if (e != cudaSuccess) return cuda_fail(e, "kernel launch");
   g_err[0] = '\0';
   return 0;
+}
+
+// Auxiliary streams of fwd_eb_forward_many, per GPU, created on first use and kept.
+namespace {
+struct ManyStreams {
+  bool ready = false;
+  cudaStream_t aux[FWD_EB_MANY_STREAMS] = {};
+  cudaEvent_t fork = nullptr;
+  cudaEvent_t joined[FWD_EB_MANY_STREAMS] = {};
+};
+constexpr int kManyDevices = 64;
+std::mutex g_many_lock;
+ManyStreams g_many[kManyDevices];
+}  // namespace
+
+int fwd_eb_forward_many(const fwd_eb_params* const* params, int32_t count, void* stream) {
+  if (count < 0 || (count > 0 && !params)) return fail(FWD_EB_EINVAL, "bad argument list");
+  for (int i = 0; i < count; ++i) {   // everything is checked before anything is launched
+    if (!params[i]) return fail(FWD_EB_EINVAL, "params[%d] is null", i);
+    Plan pl;
+    int rc = make_plan(params[i], &pl);
+    if (rc) return rc;
+  }
+  if (count <= 1) return count == 1 ? fwd_eb_forward(params[0], stream) : 0;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  if (dev < 0 || dev >= kManyDevices) {   // no slot for this ordinal: one after the other
+    for (int i = 0; i < count; ++i) {
+      int rc = fwd_eb_forward(params[i], stream);
+      if (rc) return rc;
+    }
+    return 0;
+  }
+  std::lock_guard<std::mutex> hold(g_many_lock);
+  ManyStreams& m = g_many[dev];
+  if (!m.ready) {
+    e = cudaEventCreateWithFlags(&m.fork, cudaEventDisableTiming);
+    for (int k = 0; k < FWD_EB_MANY_STREAMS && e == cudaSuccess; ++k) {
+      e = cudaStreamCreateWithFlags(&m.aux[k], cudaStreamNonBlocking);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m.joined[k], cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "creating the auxiliary streams");
+    m.ready = true;
+  }
+  cudaStream_t main = static_cast<cudaStream_t>(stream);
+  const int aux = count - 1 < FWD_EB_MANY_STREAMS ? count - 1 : FWD_EB_MANY_STREAMS;
+  e = cudaEventRecord(m.fork, main);
+  for (int k = 0; k < aux && e == cudaSuccess; ++k) e = cudaStreamWaitEvent(m.aux[k], m.fork, 0);
+  if (e != cudaSuccess) return cuda_fail(e, "forking the auxiliary streams");
+  int rc = 0;
+  for (int i = 0; i < count && rc == 0; ++i) {
+    const int lane = i % (aux + 1);
+    rc = fwd_eb_forward(params[i], lane == 0 ? stream : static_cast<void*>(m.aux[lane - 1]));
+  }
+  // joined even after a failed launch: `stream` must stay ordered behind what did start
+  for (int k = 0; k < aux; ++k) {
+    e = cudaEventRecord(m.joined[k], m.aux[k]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(main, m.joined[k], 0);
+    if (e != cudaSuccess && rc == 0) rc = cuda_fail(e, "joining the auxiliary streams");
+  }
+  return rc;
 }
 
 int fwd_eb_compact_window(const fwd_eb_params* p, int32_t* d_kept, float* d_kept_weights,

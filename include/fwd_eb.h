@@ -166,6 +166,18 @@ const char* fwd_eb_last_error_string(void);
  * (embedding_bag_plugin.cpp:146-189) plus the launchers it calls. */
 int fwd_eb_forward(const fwd_eb_params* p, void* stream);
 
+/* Several independent calls at once (the tables of one model; the reference enqueues one
+ * plugin per table, one after the other, embedding_bag_plugin.cpp:146-189).  The result is that of
+ * fwd_eb_forward on each in turn on `stream`; the launches are spread over `stream` and
+ * FWD_EB_MANY_STREAMS auxiliary streams the library keeps per GPU (created on first use), forked
+ * from `stream` and joined back into it, because a table's grid is often only a wave or two and
+ * its ramp and tail are time another table's grid can use (26 tables of 65536 x 20 lookups:
+ * 1204 us one after the other).  The calls must be independent: no call's output may be another
+ * call's input or output.  Every call is validated before the first launch; calls of different
+ * host threads on one GPU are serialised on the host. */
+#define FWD_EB_MANY_STREAMS 2
+int fwd_eb_forward_many(const fwd_eb_params* const* params, int32_t count, void* stream);
+
 /* Scratch bytes fwd_eb_forward needs for `p` (0 unless the SPLIT strategy is
  * requested or AUTO would choose it when scratch is offered).  The reference
  * plugin reports 0 (embedding_bag_plugin.cpp:129-133). */

@@ -403,6 +403,50 @@ def test_config4_all_26_tables_full_batch_every_strategy():
     assert not torch.isnan(outs[0]).any()
 
 
+def test_forward_many_equals_one_call_after_the_other():
+    """Seven independent tables of different shapes and modes through fwd_eb_forward_many (the
+    caller's stream + the library's auxiliary streams), twice in a row into the same outputs, then
+    a dependent kernel on the caller's stream: same bits as fwd_eb_forward on each, and the
+    consumer sees finished results (the auxiliary streams are joined)."""
+    rng = np.random.default_rng(31)
+    shapes = [(3000, 64, torch.float16, capi.MODE_SUM), (500, 128, torch.float32, capi.MODE_MEAN),
+              (70000, 256, torch.float16, capi.MODE_MAX), (1200, 32, torch.float32, capi.MODE_SUM),
+              (9000, 128, torch.float16, capi.MODE_MEAN), (100, 64, torch.float32, capi.MODE_MAX),
+              (40000, 96, torch.float16, capi.MODE_SUM)]
+    keep, ps, outs, singles = [], [], [], []
+    for k, (rows, dim, dt, mode) in enumerate(shapes):
+        table = torch.from_numpy(rng.standard_normal((rows, dim)).astype(np.float32)).to(DEV).to(dt)
+        bags = workloads.ragged_bags(rows, rng.integers(0, 50, 3000 + 500 * k), rng)
+        i, o = _cuda(bags.indices), _cuda(bags.offsets)
+        out = torch.full((bags.num_bags, dim), float("nan"), dtype=dt, device=DEV)
+        ref = torch.empty_like(out)
+        keep += [table, i, o]
+        ps.append(capi.make_params(table, i, o, out=out, mode=mode))
+        capi.forward(capi.make_params(table, i, o, out=ref, mode=mode))
+        outs.append(out)
+        singles.append(ref)
+    packed = capi.pack_params(ps)
+    capi.forward_many(packed)
+    capi.forward_many(packed)
+    total = sum(o.float().nan_to_num().sum() for o in outs)      # the caller's stream reads every output
+    torch.cuda.synchronize()
+    for out, ref in zip(outs, singles):
+        assert torch.equal(out.view(torch.int16 if out.dtype == torch.float16 else torch.int32),
+                           ref.view(torch.int16 if ref.dtype == torch.float16 else torch.int32))
+    assert torch.isfinite(total)
+    # an invalid call anywhere in the list: nothing is launched, the others' outputs stay as they were
+    for o in outs:
+        o.fill_(7.0)
+    bad = capi.make_params(keep[0], keep[1], keep[2], out=outs[0], mode=capi.MODE_SUM)
+    bad.dim = -5
+    with pytest.raises(capi.FwdEbError):
+        capi.forward_many(capi.pack_params(ps[1:] + [bad]))
+    torch.cuda.synchronize()
+    assert all(bool((o == 7.0).all()) for o in outs)
+    capi.forward_many(capi.pack_params([]))
+    capi.forward_many(capi.pack_params(ps[:1]))
+
+
 def test_int32_filter_edges_negative_indices_and_window_origin():
     """int32 indices take a 32-bit filter: negative indices, indices below the window origin and
     a negative origin (the reference's data_offset is a signed int) must behave as in the oracle."""
