@@ -670,25 +670,28 @@ class C4Workload:
                                mode=self.mode, fixed_len=self.L, per_sample_weights=self.d_w[t][a:b])
               for j, t in enumerate(self.here)]
 
-        # the same launches with local stores only, queued as the step queues them: this rank's
-        # whole tables on the current stream, the replicated ones spread over two more streams
+        # the same launches with local stores only, queued as the step queues them: round robin over
+        # the current stream and two more
         n_aux = 2 if getattr(args, "local_streams", None) is None else int(args.local_streams)
-        aux = [torch.cuda.Stream() for _ in range(n_aux if len(self.replicated) > 1 else 0)]
+        order = [p for p, t in zip(lp, self.here) if t in self.mine] + \
+                [p for p, t in zip(lp, self.here) if t not in self.mine]
+        n_mine, shares = len(self.mine), len(self.replicated) > 0
+        aux = [torch.cuda.Stream() for _ in range(min(n_aux, max(0, len(order) - 1)))]
         fork, joins = torch.cuda.Event(), [torch.cuda.Event() for _ in aux]
-        whole = [p for p, t in zip(lp, self.here) if t in self.mine]
-        shares = [p for p, t in zip(lp, self.here) if t not in self.mine]
-        lanes = len(aux) + (1 if (not whole or not aux) else 0)
 
         def pool_only(k):
             if aux:
                 fork.record(stream)
                 for a_ in aux:
                     a_.wait_event(fork)
-            for p in whole:
-                capi.forward(p, stream.cuda_stream)
-            for i, p in enumerate(shares):
-                lane = i % lanes
-                capi.forward(p, aux[lane].cuda_stream if lane < len(aux) else stream.cuda_stream)
+            for i, p in enumerate(order):
+                if i < n_mine and shares:        # whole tables together, the shares beside them
+                    lane = 0
+                elif shares and n_mine:
+                    lane = 1 + (i - n_mine) % len(aux) if aux else 0
+                else:
+                    lane = i % (len(aux) + 1)
+                capi.forward(p, stream.cuda_stream if lane == 0 else aux[lane - 1].cuda_stream)
             for a_, j in zip(aux, joins):
                 j.record(a_)
                 stream.wait_event(j)

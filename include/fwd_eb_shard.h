@@ -247,9 +247,11 @@ int fwd_eb_pipeline_step_tablewise(fwd_eb_pipeline* pl, const fwd_eb_params* con
  * tables this rank holds alone, then the `local_count` replicated tables, then the flag exchange
  * as fwd_eb_pipeline_step_tablewise does.  Needs x->tickets == NULL when local_count > 0. */
 int fwd_eb_shard_pool_local(const fwd_eb_params* p, const fwd_eb_shard_exchange* x, void* stream);
-/* The hybrid step pools the replicated tables on up to FWD_EB_PIPELINE_LOCAL_STREAMS streams of
- * the pipeline's own, forked from `main_stream` before the step's pushes and joined before the
- * flag exchange; 0 queues them on `main_stream` behind the pushes instead. */
+/* A table-wise step's launches (one per table, pushes and replicated tables alike) are
+ * independent, so the step spreads them over `main_stream` and up to
+ * FWD_EB_PIPELINE_LOCAL_STREAMS streams of the pipeline's own, forked from `main_stream` and
+ * joined before the flag exchange; 0 queues everything on `main_stream`.  (With x->tickets the
+ * pushes stay on `main_stream`: the last push grid raises the flag.) */
 int fwd_eb_pipeline_set_local_streams(fwd_eb_pipeline* pl, int32_t streams);
 int fwd_eb_pipeline_step_tablewise_hybrid(fwd_eb_pipeline* pl, const fwd_eb_params* const* params,
                                           const int32_t* table_index, int32_t count,
