@@ -193,6 +193,10 @@ def describe(workload: str, world: int, args):
     base = {"l2_policy": "no flush: table (shard) larger than the 126 MB L2 and rotating index "
                          "batches; skewed laws keep their hot rows cached, which is a property "
                          "of the workload"}
+    if world == 1 and workload != "c4" and int(getattr(args, "streams", 1) or 1) > 1:
+        base["streams"] = (f"consecutive steps (independent batches) rotate over {int(args.streams)} CUDA streams, "
+                           "each with its own output buffer; the timed region forks them behind its start "
+                           "event and joins them before its end event")
     if workload == "c2":
         base.update(workload="c2: EmbeddingBag mean, table 1000000x128 fp16, 16384 bags/step, lengths "
                              "Poisson(40) clipped [1,200], Zipf(1.05) indices",
@@ -461,38 +465,51 @@ class GpuWorkload:
         stream = torch.cuda.current_stream()
         bags_n = self.batches[0].num_bags
         if self.world == 1:
-            out = torch.empty((bags_n, self.dim), dtype=torch.float16, device=dev)
-            params = [capi.make_params(self.table, i, o, out=out, mode=self.mode, padding_idx=self.pad,
-                                       row_lo=self.row_lo) for i, o in self.d_batches]
-            self._params = params
+            # Consecutive steps are independent batches: they rotate over `lanes` streams (lane 0 is
+            # the current stream), each lane with its own output and scratch, so that one step's grid
+            # runs beside the tail of the step before (a grid of this size is under two waves, and on
+            # one stream the next grid starts only when the last CTA of this one has finished).
+            lanes = max(1, int(getattr(args, "streams", 1) or 1))
+            self.lane_streams = [stream] + [torch.cuda.Stream() for _ in range(lanes - 1)]
+            self._fork = torch.cuda.Event()
+            self._joins = [torch.cuda.Event() for _ in range(lanes - 1)]
+            outs = [torch.empty((bags_n, self.dim), dtype=torch.float16, device=dev) for _ in range(lanes)]
+            self._outs = outs
+            self._params = [[capi.make_params(self.table, i, o, out=out, mode=self.mode, padding_idx=self.pad,
+                                              row_lo=self.row_lo) for i, o in self.d_batches] for out in outs]
 
             if self.local_filter:
                 # one rank's share of a row-sharded table on one GPU: the two kernels a rank runs per
                 # step (window compaction, pooling of the dense sub-bags), with local stores
                 max_n = max(b.num_indices for b in self.batches)
-                kept = torch.empty(max_n, dtype=torch.int32, device=dev)
-                bounds = torch.empty((bags_n, 2), dtype=torch.int32, device=dev)
-                cp = capi.make_compacted_params(self.table, kept, bounds, out=out, mode=self.mode)
-                self._compact_keep = (kept, bounds)
+                scratch = [(torch.empty(max_n, dtype=torch.int32, device=dev),
+                            torch.empty((bags_n, 2), dtype=torch.int32, device=dev)) for _ in range(lanes)]
+                cps = [capi.make_compacted_params(self.table, kept, bounds, out=out, mode=self.mode)
+                       for (kept, bounds), out in zip(scratch, outs)]
+                self._compact_keep = scratch
 
-                def step(k, events=None):
+                def step(k, events=None, lane=None):
+                    lane = 0 if events else (k % lanes if lane is None else lane)
+                    st = self.lane_streams[lane]
+                    kept, bounds = scratch[lane]
                     if events:
                         events[0].record()
-                    capi.compact_window(self._params[k % self.nb], kept, bounds, stream=stream.cuda_stream)
-                    capi.forward(cp, stream.cuda_stream)
+                    capi.compact_window(self._params[lane][k % self.nb], kept, bounds, stream=st.cuda_stream)
+                    capi.forward(cps[lane], st.cuda_stream)
                     if events:
                         events[1].record()
-                    self._last = out
+                    self._last = outs[lane]
                 self.step = step
                 return
 
-            def step(k, events=None):
+            def step(k, events=None, lane=None):
+                lane = 0 if events else (k % lanes if lane is None else lane)
                 if events:
                     events[0].record()
-                capi.forward(self._params[k % self.nb], stream.cuda_stream)
+                capi.forward(self._params[lane][k % self.nb], self.lane_streams[lane].cuda_stream)
                 if events:
                     events[1].record()
-                self._last = out
+                self._last = outs[lane]
             self.step = step
             return
         if self.workload == "tablewise":
@@ -542,6 +559,22 @@ class GpuWorkload:
         else:
             self.pool_only = lambda k: capi.forward(lp[k % self.nb], stream.cuda_stream)
 
+    def fork(self):
+        """The other lanes start where the current stream stands (call after the region's start event)."""
+        lanes = getattr(self, "lane_streams", None)
+        if lanes and len(lanes) > 1:
+            self._fork.record(lanes[0])
+            for st in lanes[1:]:
+                st.wait_event(self._fork)
+
+    def join(self):
+        """The current stream waits for every lane (call before the region's end event)."""
+        lanes = getattr(self, "lane_streams", None)
+        if lanes and len(lanes) > 1:
+            for st, ev in zip(lanes[1:], self._joins):
+                ev.record(st)
+                lanes[0].wait_event(ev)
+
     def set_device_batches(self, d_batches):
         """Point the step at other device copies of the same batches (the e2e loop's)."""
         self.d_batches = d_batches
@@ -551,11 +584,9 @@ class GpuWorkload:
             else:
                 self._prepared = [self.bag.prepare(i, o) for i, o in d_batches]
         if self.world == 1:
-            out = self._last if self._last is not None else self.torch.empty(
-                (self.batches[0].num_bags, self.dim), dtype=self.torch.float16, device=self.dev)
-            self._params = [self.capi.make_params(self.table, i, o, out=out, mode=self.mode,
-                                                  padding_idx=self.pad, row_lo=self.row_lo)
-                            for i, o in d_batches]
+            self._params = [[self.capi.make_params(self.table, i, o, out=out, mode=self.mode,
+                                                   padding_idx=self.pad, row_lo=self.row_lo)
+                             for i, o in d_batches] for out in self._outs]
 
     def result(self):
         return self._last
@@ -852,13 +883,18 @@ def timed_regions(wl, steps: int, regions: int, barrier, multi: bool):
     end = [torch.cuda.Event(enable_timing=True) for _ in range(regions)]
     step = wl.step
     sync_result = wl.bag.sync_result if multi else None
+    fork, join = getattr(wl, "fork", None), getattr(wl, "join", None)
     for r in range(regions):
         barrier()
         begin[r].record()
+        if fork:
+            fork()           # N = 1: the other lanes' streams start behind the start event
         for k in range(steps):
             step(k)
         if sync_result:
             sync_result()    # the last step's fold / flag wait (side stream) is inside the region
+        if join:
+            join()           # ... and the end event waits for every lane
         end[r].record()
     barrier()
     return np.array([begin[r].elapsed_time(end[r]) for r in range(regions)])
@@ -989,6 +1025,20 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
         alg = float(np.mean([wl.algorithmic_bytes(k) for k in range(steps)]))
         launch_ms = total_ms / steps
         timed_by = "events around the median timed region / steps"
+    one_stream_us = None
+    n_lanes = len(getattr(wl, "lane_streams", [])) if not multi else 0
+    if n_lanes > 1:
+        # the same steps back to back on ONE stream, for comparison (no overlap of consecutive grids)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        ev0.record()
+        for k in range(steps):
+            wl.step(k, lane=0)
+        ev1.record()
+        torch.cuda.synchronize()
+        one_stream_us = ev0.elapsed_time(ev1) * 1e3 / steps
+        timed_by += (f"; consecutive steps rotate over {n_lanes} streams, so this is the time per launch with "
+                     "neighbouring grids overlapping (`kernel_us_one_stream`: the same steps on one stream)")
     achieved = alg / (launch_ms * 1e-3) / 1e9
     traffic, traffic_src = ncu_traffic(workload)
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -998,6 +1048,14 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
                 "kernel_us_isolated_median": float(np.median(iso_us)),
                 "kernel_us_isolated_samples": int(len(iso_us)),
                 "algorithmic_bytes_per_launch": alg}
+    if traffic:
+        # DRAM bytes per launch (ncu) over the same duration: what the memory system moved, beside
+        # the algorithmic figure that counts every repeated row again
+        roofline["dram_achieved"] = traffic / (launch_ms * 1e-3) / 1e9
+        roofline["dram_frac"] = roofline["dram_achieved"] / peak
+    if one_stream_us is not None:
+        roofline["kernel_us_one_stream"] = one_stream_us
+        roofline["streams"] = n_lanes
     if workload in ("c2", "tablewise"):
         roofline["note"] = ("Zipf indices: hot rows are served from L1 / L2 (DRAM traffic is `traffic`, a fifth of the "
                             "algorithmic bytes), so `frac` can exceed 1; the HBM-bound figure of this kernel is "
@@ -1038,6 +1096,9 @@ def extra_object(m: dict) -> dict:
          "roofline": {k: m["roofline"][k] for k in ("achieved", "peak", "frac", "frac_of_8000", "traffic",
                                                      "kernel_us_mean", "algorithmic_bytes_per_launch",
                                                      "peak_kind")}}
+    for k in ("kernel_us_one_stream", "streams", "dram_achieved", "dram_frac"):
+        if k in m["roofline"]:
+            o["roofline"][k] = m["roofline"][k]
     if m["exchange"]:
         x = m["exchange"]
         o.update(step_us=x["step_us"], pool_only_us=x["pool_only_us"], overhead_frac=x["overhead_frac"],
@@ -1433,6 +1494,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto",
                     choices=["auto", "c2", "c2u", "tablewise", "rowshard", "c5", "c3", "c4"])
+    ap.add_argument("--streams", type=int, default=2,
+                    help="N=1: consecutive steps (independent batches) rotate over this many streams, each "
+                         "with its own output buffer; 1 = every step on one stream")
     ap.add_argument("--regions", type=int, default=REGIONS,
                     help="timed regions of --steps steps each (barrier before each); `value` is the "
                          "median region")
