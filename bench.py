@@ -193,6 +193,9 @@ def describe(workload: str, world: int, args):
     base = {"l2_policy": "no flush: table (shard) larger than the 126 MB L2 and rotating index "
                          "batches; skewed laws keep their hot rows cached, which is a property "
                          "of the workload"}
+    if world > 1 and workload != "c4" and int(getattr(args, "streams", 1) or 1) > 1:
+        base["streams"] = ("consecutive steps (independent batches) alternate over 2 CUDA streams per rank; flags, "
+                           "waits and folds stay in step order on the pipeline's side stream")
     if world == 1 and workload != "c4" and int(getattr(args, "streams", 1) or 1) > 1:
         base["streams"] = (f"consecutive steps (independent batches) rotate over {int(args.streams)} CUDA streams, "
                            "each with its own output buffer; the timed region forks them behind its start "
@@ -417,6 +420,7 @@ class GpuWorkload:
         self.capi, self.fd, self.torch = capi, fd, torch
         self.bag = None
         self.pool_only = None
+        self.resident = True      # the timed steps read device-resident batches; the e2e loop clears this
         self.out_itemsize = 2
         self.row_lo = 0
         local_filter = None
@@ -515,49 +519,74 @@ class GpuWorkload:
         if self.workload == "tablewise":
             self.bag = fd.TableWiseBags({self.rank: self.table}, list(range(self.world)), dim=self.dim,
                                         max_bags=bags_n, exchange=args.exchange, wire_dtype=capi.F16,
-                                        mode=self.mode, ship=args.ship, lookback=args.lookback)
+                                        mode=self.mode, ship=args.ship, lookback=args.lookback,
+                                        lanes=min(2, max(1, int(args.streams))))
             self.out_itemsize = 2 if args.exchange == "push" else 4
 
             self._prepared = [self.bag.prepare({self.rank: (i, o, None)}) for i, o in self.d_batches]
 
             def step(k, events=None):
-                self._last = self.bag.forward(self._prepared[k % self.nb], pool_events=events)
+                self._last = self.bag.forward(self._prepared[k % self.nb], pool_events=events,
+                                               inputs_ready=self.resident)
         else:
             wire = capi.F16 if args.wire == "f16" else capi.F32
             max_n = max(b.num_indices for b in self.batches)
             self.bag = fd.RowShardedBag(self.table, self.row_lo, mode=self.mode, max_bags=bags_n,
                                         exchange=args.exchange, wire_dtype=wire, max_indices=max_n,
-                                        ship=args.ship, lookback=args.lookback)
+                                        ship=args.ship, lookback=args.lookback,
+                                        lanes=min(2, max(1, int(args.streams))) if args.exchange in
+                                        ("push", "stage", "compact") else 1)
             self.out_itemsize = 2 if (args.exchange in ("push", "stage", "compact") and args.wire == "f16") else 4
 
             self._prepared = [self.bag.prepare(i, o) for i, o in self.d_batches]
 
             def step(k, events=None):
-                self._last = self.bag.forward(self._prepared[k % self.nb], pool_events=events)
+                self._last = self.bag.forward(self._prepared[k % self.nb], pool_events=events,
+                                               inputs_ready=self.resident)
         self.step = step
-        # the same pooling without any exchange, for the overhead figure
+        # the same pooling without any exchange, for the overhead figure — queued as the steps are:
+        # alternating over as many streams, each with its own output and scratch
+        lanes = min(2, max(1, int(args.streams))) if (self.workload == "tablewise" or args.exchange in
+                                                      ("push", "stage", "compact")) else 1
+        self._po_streams = [stream] + [torch.cuda.Stream() for _ in range(lanes - 1)]
+        self._po_fork = torch.cuda.Event()
+        self._po_joins = [torch.cuda.Event() for _ in range(lanes - 1)]
         local_dtype = torch.float16 if self.workload == "tablewise" else torch.float32
-        local_out = torch.empty((bags_n, self.dim), dtype=local_dtype, device=dev)
-
-        lp = [capi.make_params(self.table, i, o, out=local_out, mode=self.mode, padding_idx=self.pad,
-                               row_lo=self.row_lo) for i, o in self.d_batches]
+        local_outs = [torch.empty((bags_n, self.dim), dtype=local_dtype, device=dev) for _ in range(lanes)]
+        lps = [[capi.make_params(self.table, i, o, out=lo, mode=self.mode, padding_idx=self.pad,
+                                 row_lo=self.row_lo) for i, o in self.d_batches] for lo in local_outs]
         if self.workload != "tablewise" and args.exchange == "compact":
             # the same two kernels as the step (window compaction, pooling of the dense sub-bags)
             # with local stores and no flags or fold
             max_n = max(b.num_indices for b in self.batches)
-            kept = torch.empty(max_n, dtype=torch.int32, device=dev)
-            bounds = torch.empty((bags_n, 2), dtype=torch.int32, device=dev)
             wire_dt = torch.float16 if args.wire == "f16" else torch.float32
-            local_w = torch.empty((bags_n, self.dim), dtype=wire_dt, device=dev)
-            cp = capi.make_compacted_params(self.table, kept, bounds, out=local_w, mode=capi.MODE_SUM)
-            self._po_keep = (kept, bounds, local_w)
+            scratch = [(torch.empty(max_n, dtype=torch.int32, device=dev),
+                        torch.empty((bags_n, 2), dtype=torch.int32, device=dev),
+                        torch.empty((bags_n, self.dim), dtype=wire_dt, device=dev)) for _ in range(lanes)]
+            cps = [capi.make_compacted_params(self.table, kept, bounds, out=lw, mode=capi.MODE_SUM)
+                   for kept, bounds, lw in scratch]
+            self._po_keep = scratch
 
             def pool_only(k):
-                capi.compact_window(lp[k % self.nb], kept, bounds, stream=stream.cuda_stream)
-                capi.forward(cp, stream.cuda_stream)
+                lane = k % lanes
+                st = self._po_streams[lane].cuda_stream
+                capi.compact_window(lps[lane][k % self.nb], scratch[lane][0], scratch[lane][1], stream=st)
+                capi.forward(cps[lane], st)
             self.pool_only = pool_only
         else:
-            self.pool_only = lambda k: capi.forward(lp[k % self.nb], stream.cuda_stream)
+            self.pool_only = lambda k: capi.forward(lps[k % lanes][k % self.nb],
+                                                    self._po_streams[k % lanes].cuda_stream)
+
+    def pool_fork(self):
+        if len(self._po_streams) > 1:
+            self._po_fork.record(self._po_streams[0])
+            for st in self._po_streams[1:]:
+                st.wait_event(self._po_fork)
+
+    def pool_join(self):
+        for st, ev in zip(self._po_streams[1:], self._po_joins):
+            ev.record(st)
+            self._po_streams[0].wait_event(ev)
 
     def fork(self):
         """The other lanes start where the current stream stands (call after the region's start event)."""
@@ -953,12 +982,20 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
     if wl.pool_only:
         barrier()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if hasattr(wl, "pool_fork"):
+            wl.pool_fork()
         for k in range(20):
             wl.pool_only(k)
+        if hasattr(wl, "pool_join"):
+            wl.pool_join()
         n_po = max(20, min(steps, 200))
         a.record()
+        if hasattr(wl, "pool_fork"):
+            wl.pool_fork()
         for k in range(n_po):
             wl.pool_only(k)
+        if hasattr(wl, "pool_join"):
+            wl.pool_join()
         b.record()
         torch.cuda.synchronize()
         pool_only_us = a.elapsed_time(b) * 1e3 / n_po
@@ -1454,6 +1491,7 @@ def run_e2e_multi(args, wl, rank, world, dev):
     h_out = [torch.empty(shape, dtype=dtype).pin_memory() for _ in range(wl.nb)]
     saved = wl.d_batches
     wl.set_device_batches(list(zip(d_idx, d_off)))
+    wl.resident = False      # every step's inputs now arrive by a copy on the current stream
 
     def step(k):
         j = k % wl.nb

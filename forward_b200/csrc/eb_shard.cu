@@ -725,6 +725,15 @@ struct fwd_eb_pipeline {
   cudaEvent_t fork = nullptr;
   cudaEvent_t joined[FWD_EB_PIPELINE_LOCAL_STREAMS] = {};
   int32_t local_streams = FWD_EB_PIPELINE_LOCAL_STREAMS;
+  // Steps may be issued on more than one caller stream (consecutive steps are independent
+  // batches, and on two alternating streams one step's grid runs beside the tail of the step
+  // before).  The look-back is a property of the stream a step is issued on: for each stream
+  // seen, the newest fold it has been made to wait for.
+  struct Seen {
+    cudaStream_t stream;
+    uint32_t waited;
+    bool used;
+  } seen[FWD_EB_PIPELINE_MAIN_STREAMS] = {};
 };
 
 // A step that fails its host-side checks before anything was launched must not leave this rank
@@ -747,14 +756,30 @@ static int pipeline_begin(fwd_eb_pipeline* pl, fwd_eb_shard_exchange* x, cudaStr
                 "2(k-1) + 2d parts");
   const uint32_t every = x->tickets ? FWD_EB_PIPELINE_WAIT_EVERY_TICKETS : pl->every;
   const uint32_t depth = x->tickets ? FWD_EB_PIPELINE_WAIT_DEPTH : pl->depth;
-  if (pl->epoch > depth && pl->epoch % every == 0) {
-    // this rank has folded step e-d, hence seen every rank's flag e-d; see FWD_EB_SHARD_BUFFERS
-    // for why looking back this rarely is enough with the buffer parts there are
+  // Step e may start only behind this rank's fold of some step >= e - (every - 1) - depth (see
+  // FWD_EB_SHARD_BUFFERS for why that is enough with the buffer parts there are).  On one stream
+  // that is a wait on every `every`-th step, inherited by the steps queued behind it; a stream
+  // that was not seen before, or when the table of streams is full, waits now.
+  fwd_eb_pipeline::Seen* slot = nullptr;
+  for (auto& sn : pl->seen)
+    if (sn.used && sn.stream == main) slot = &sn;
+  if (!slot) {
+    for (auto& sn : pl->seen)
+      if (!sn.used && !slot) slot = &sn;
+    if (slot) {
+      slot->used = true;
+      slot->stream = main;
+      slot->waited = 0;
+    }
+  }
+  const uint32_t waited = slot ? slot->waited : 0;
+  if (pl->epoch > depth && (uint64_t)waited + (every - 1) + depth < pl->epoch) {
     cudaError_t e = cudaStreamWaitEvent(main, pl->done[(pl->epoch - depth) % FWD_EB_SHARD_BUFFERS], 0);
     if (e != cudaSuccess) {
       pl->epoch -= 1;
       return cuda_fail(e, "cudaStreamWaitEvent (main)");
     }
+    if (slot) slot->waited = pl->epoch - depth;
   }
   return 0;
 }

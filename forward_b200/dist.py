@@ -247,6 +247,34 @@ def make_exchange(buffers: PeerBuffers, rank: int, per_rank_bags: int, wire_dtyp
     return x
 
 
+class _StepLanes:
+    """Consecutive steps are independent batches.  Queued on one stream, a step's pooling grid starts
+    only when the last CTA (and the last peer store) of the step before has finished; on two
+    alternating streams it runs beside that tail.  Each step's stream is first put behind the
+    caller's current stream (whatever produced the inputs), then the step is queued on it; the
+    pipeline keeps flags, waits and folds in call order on its own side stream."""
+
+    def __init__(self, lanes: int, dev):
+        import torch
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(lanes)] if lanes > 1 else []
+        self.events = [torch.cuda.Event() for _ in self.streams]
+        self.calls = 0
+
+    def next(self, inputs_ready: bool = False):
+        """(lane number, stream) of the next step; the current stream itself with one lane.
+        `inputs_ready`: the caller vouches that nothing queued on the current stream produces this
+        step's inputs (device-resident batches), which saves the event that orders the lane behind it."""
+        import torch
+        if not self.streams:
+            return 0, torch.cuda.current_stream()
+        lane = self.calls % len(self.streams)
+        self.calls += 1
+        if not inputs_ready:
+            self.events[lane].record(torch.cuda.current_stream())
+            self.streams[lane].wait_event(self.events[lane])
+        return lane, self.streams[lane]
+
+
 # ---- row-sharded table -------------------------------------------------------------------------------
 
 class RowShardedBag:
@@ -255,7 +283,7 @@ class RowShardedBag:
     def __init__(self, table_local, row_lo: int, *, mode: int, max_bags: int, group=None,
                  exchange: str = "push", wire_dtype: int = capi.F32, padding_idx: int = -1,
                  out_dtype=None, max_indices: int = 0, flag_from_pool: bool = False, ship: bool = False,
-                 lookback: tuple[int, int] | None = None):
+                 lookback: tuple[int, int] | None = None, lanes: int = 1):
         import torch
         import torch.distributed as dist
         if mode == capi.MODE_MAX:
@@ -281,6 +309,11 @@ class RowShardedBag:
         self.side = None
         self.ready = None
         self.piped = exchange in ("push", "stage", "compact")
+        if lanes < 1 or lanes > 2:
+            raise ValueError("1 or 2 lanes")
+        # steps alternate over `lanes` private streams (see _StepLanes); the plain NCCL exchanges stay
+        # on the caller's stream
+        self._lanes = _StepLanes(lanes if self.piped else 1, dev)
         if exchange == "compact" and max_indices <= 0:
             raise ValueError("exchange='compact' needs max_indices (its scratch is sized up front)")
         if self.piped:
@@ -290,6 +323,10 @@ class RowShardedBag:
             self._out_ptrs = (C.c_void_p * SHARD_BUFFERS)(*[o.data_ptr() for o in self.outs])
             self._pl = C.c_void_p()
             capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
+            if lanes > 1 and not lookback:
+                # with two steps in flight a look-back of two calls is a stall on every wait: measured on
+                # two B200s, table-wise step 22.2 us with (6, 2), 19.7 with (8, 8), 20.3 with (12, 4)
+                lookback = (8, 8)
             if lookback:
                 capi.check(_lib().fwd_eb_pipeline_set_lookback(self._pl, *lookback))
             self.side = torch.cuda.ExternalStream(_lib().fwd_eb_pipeline_side_stream(self._pl), device=dev)
@@ -315,11 +352,12 @@ class RowShardedBag:
                 # scratch of the window compaction: kept indices, sub-bag bounds, and for a mean
                 # the bags' full counts (one part per step in flight: a fold reads them beside later steps)
                 nb_all = self.per * self.world
-                self._kept = torch.empty(max_indices, dtype=torch.int32, device=dev)
-                self._bounds = torch.empty((nb_all, 2), dtype=torch.int32, device=dev)
+                # kept indices and bounds are read by the step's own pooling only: one set per lane
+                self._kept = [torch.empty(max_indices, dtype=torch.int32, device=dev) for _ in range(lanes)]
+                self._bounds = [torch.empty((nb_all, 2), dtype=torch.int32, device=dev) for _ in range(lanes)]
                 self._counts = torch.zeros((SHARD_BUFFERS, nb_all), dtype=torch.int32, device=dev)
-                self._scratch = CompactScratch(self._kept.data_ptr(), None, self._bounds.data_ptr(),
-                                               self._counts.data_ptr())
+                self._scratch = [CompactScratch(k.data_ptr(), None, b.data_ptr(), self._counts.data_ptr())
+                                 for k, b in zip(self._kept, self._bounds)]
                 self.max_indices = max_indices
             if exchange == "stage":
                 # "stage": the plain pooling kernel writes all partial bags here and the copy
@@ -356,21 +394,21 @@ class RowShardedBag:
         out = self.out if self.piped else self.partial
         return (self.params(indices, offsets, out), mine, num_bags)
 
-    def forward(self, indices, offsets=None, pool_events=None):
+    def forward(self, indices, offsets=None, pool_events=None, inputs_ready: bool = False):
         """Returns this rank's [bags_owned, dim] slice of the pooled output (a buffer reused
         SHARD_BUFFERS calls later).  `indices` may be a prepare()d argument block.  `pool_events` = (start, end)
-        CUDA events recorded around the pooling launch."""
+        CUDA events recorded around the pooling launch.  `inputs_ready`: see _StepLanes.next."""
         import torch
         import torch.distributed as dist
         p, mine, num_bags = indices if isinstance(indices, tuple) else self.prepare(indices, offsets)
-        main = torch.cuda.current_stream()
+        lane, main = self._lanes.next(inputs_ready)
         stream = main.cuda_stream
         if self.piped:
             if pool_events:
-                pool_events[0].record()
+                pool_events[0].record(main)
             if self.exchange == "compact":
                 capi.check(_lib().fwd_eb_pipeline_step_rowshard_compact(
-                    self._pl, C.byref(p), C.byref(self.x), mine, C.byref(self._scratch), self._out_ptrs,
+                    self._pl, C.byref(p), C.byref(self.x), mine, C.byref(self._scratch[lane]), self._out_ptrs,
                     capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))
             elif self.exchange == "stage":
                 capi.check(_lib().fwd_eb_pipeline_step_rowshard_staged(
@@ -381,7 +419,7 @@ class RowShardedBag:
                     self._pl, C.byref(p), C.byref(self.x), mine, self._out_ptrs,
                     capi._torch_dtype_code(self.out), C.c_void_p(stream), C.byref(self._which)))
             if pool_events:
-                pool_events[1].record()   # after the push launch (the fold went to the side stream)
+                pool_events[1].record(main)   # after the push launch (the fold went to the side stream)
             self.ready = True
             return self.outs[self._which.value][:mine]
         if num_bags < self.per * self.world:
@@ -467,7 +505,7 @@ class TableWiseBags:
                  exchange: str = "push", wire_dtype: int = capi.F32, mode: int = capi.MODE_SUM,
                  fixed_len: int = 0, padding_idx: int = -1, flag_from_pool: bool = False,
                  ship: bool = False, lookback: tuple[int, int] | None = None,
-                 local_streams: int | None = None):
+                 local_streams: int | None = None, lanes: int = 1):
         import torch
         import torch.distributed as dist
         self.group = group
@@ -487,12 +525,19 @@ class TableWiseBags:
         self.exchange = exchange
         self.wire_dtype = wire_dtype
         dev = torch.device("cuda", torch.cuda.current_device())
+        if lanes < 1 or lanes > 2:
+            raise ValueError("1 or 2 lanes")
+        self._lanes = _StepLanes(lanes if exchange == "push" else 1, dev)   # see _StepLanes
         self.side = None
         self.ready = None
         self._views = {}
         if exchange == "push":
             self._pl = C.c_void_p()
             capi.check(_lib().fwd_eb_pipeline_create(C.byref(self._pl)))
+            if lanes > 1 and not lookback:
+                # with two steps in flight a look-back of two calls is a stall on every wait: measured on
+                # two B200s, table-wise step 22.2 us with (6, 2), 19.7 with (8, 8), 20.3 with (12, 4)
+                lookback = (8, 8)
             if lookback:
                 capi.check(_lib().fwd_eb_pipeline_set_lookback(self._pl, *lookback))
             if local_streams is not None:
@@ -577,7 +622,7 @@ class TableWiseBags:
         ltabs = (C.c_int32 * max(m, 1))(*[t for t, _ in local])
         return [blocks, ptrs, tabs, n, local, lptrs, ltabs, m, keep]
 
-    def forward(self, inputs, pool_events=None):
+    def forward(self, inputs, pool_events=None, inputs_ready: bool = False):
         """inputs[t] = (indices, offsets_or_None, weights_or_None) for every table this rank owns,
         or a prepare()d list.  Returns [per, T, dim] (rows past the bags this rank owns are
         unspecified).  `pool_events` = (start, end) CUDA events recorded around the pooling
@@ -586,16 +631,17 @@ class TableWiseBags:
         import torch.distributed as dist
         prepared = inputs if isinstance(inputs, list) else self.prepare(inputs)
         blocks, ptrs, tabs, n, local, lptrs, ltabs, m, _ = prepared
-        stream = capi.current_stream_ptr()
+        _, main = self._lanes.next(inputs_ready)
+        stream = main.cuda_stream
         if self.exchange == "push":
             if pool_events:
-                pool_events[0].record()
+                pool_events[0].record(main)
             res = C.c_void_p()
             capi.check(_lib().fwd_eb_pipeline_step_tablewise_hybrid(
                 self._pl, ptrs, tabs, n, lptrs, ltabs, m, C.byref(self.x), self.dim, C.c_void_p(stream),
                 C.byref(res)))
             if pool_events:
-                pool_events[1].record()   # after the push launches (the flag exchange is on the side stream)
+                pool_events[1].record(main)   # after the push launches (the flag exchange is on the side stream)
             self.ready = True
             view = self._views.get(res.value)
             if view is None:

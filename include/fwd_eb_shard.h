@@ -48,12 +48,19 @@ extern "C" {
  *   - Flag raised by the pooling grid itself (x->tickets set): a flag no longer proves a fold;
  *     seeing flag f of A only proves A had folded f-(k-1)-d, hence 2(k-1) + 2d parts.
  *     k = 3, d = 2.
+ * The caller may issue consecutive steps on different streams (independent batches: one step's
+ * grid then runs beside the tail of the step before).  The look-back is kept per caller stream
+ * (up to FWD_EB_PIPELINE_MAIN_STREAMS of them; a stream beyond that waits on every call): a
+ * step waits, on its own stream, unless that stream is already behind this rank's fold of some
+ * call >= e-(k-1)-d, which is all the argument above uses.  Flags, waits and folds stay in call
+ * order on the pipeline's side stream whatever stream a step came in on.
  * The CPU model of these rules (tests/test_exchange_protocol.py) finds no overwrite of an
  * unfolded part with them and does find one with fewer parts. */
 #define FWD_EB_PIPELINE_WAIT_EVERY 6
 #define FWD_EB_PIPELINE_WAIT_DEPTH 2
 #define FWD_EB_PIPELINE_WAIT_EVERY_TICKETS 3
 #define FWD_EB_SHARD_BUFFERS 16
+#define FWD_EB_PIPELINE_MAIN_STREAMS 4    /* distinct caller streams a pipeline keeps look-back state for */
 #define FWD_EB_PIPELINE_LOCAL_STREAMS 2   /* auxiliary streams for a hybrid step's replicated tables */
 #define FWD_EB_SHARD_TIMEOUT 1
 #define FWD_EB_IPC_HANDLE_BYTES 64

@@ -137,3 +137,67 @@ def test_flag_from_the_pooling_grid_needs_more_parts_than_flag_after_the_fold(wa
         assert state == "done"
         hazardous += bool(hazards)
     assert hazardous > 0
+
+
+def simulate_lanes(world: int, parts: int, steps: int, seed: int, every: int, depth: int, lanes: int):
+    """The same model with a rank's steps issued on `lanes` alternating caller streams (step e on
+    stream e % lanes; a stream runs its steps in order, different streams run freely) and the
+    look-back kept per stream as pipeline_begin keeps it: a step waits for this rank's fold of
+    e - depth unless its stream is already behind a fold >= e - (every - 1) - depth."""
+    rng = random.Random(seed)
+    # the host decides the waits in issue order (the same on every rank)
+    waited = [0] * lanes
+    wait_for = [0] * (steps + 1)
+    for e in range(1, steps + 1):
+        lane = e % lanes
+        if e > depth and waited[lane] + (every - 1) + depth < e:
+            wait_for[e] = e - depth
+            waited[lane] = e - depth
+    done_p = [set() for _ in range(world)]
+    lane_next = [[next((e for e in range(1, steps + 1) if e % lanes == lane), None) for lane in range(lanes)]
+                 for _ in range(world)]
+    folded = [0] * world
+    flags = [[0] * world for _ in range(world)]
+    holds = [[[0] * world for _ in range(parts)] for _ in range(world)]
+    hazards = []
+    while min(folded) < steps:
+        ready = []
+        for r in range(world):
+            for lane in range(lanes):
+                e = lane_next[r][lane]
+                if e is not None and e <= steps and folded[r] >= wait_for[e]:
+                    ready.append(("P", r, e, lane))
+            e = folded[r] + 1
+            if e <= steps and e in done_p[r]:
+                ready.append(("X", r, e, 0))
+        if not ready:
+            return "deadlock", hazards
+        kind, r, e, lane = rng.choice(ready)
+        if kind == "P":
+            for owner in range(world):
+                slot = holds[owner][e % parts]
+                if slot[r] != 0 and folded[owner] < slot[r]:
+                    hazards.append((r, owner, e, slot[r], folded[owner]))
+                slot[r] = e
+            done_p[r].add(e)
+            nxt = e + lanes
+            lane_next[r][lane] = nxt if nxt <= steps else None
+        else:
+            for owner in range(world):
+                flags[owner][r] = max(flags[owner][r], e)
+            if all(f >= e for f in flags[r]):
+                if any(holds[r][e % parts][src] != e for src in range(world)):
+                    hazards.append(("stale", r, e, list(holds[r][e % parts])))
+                folded[r] = e
+    return "done", hazards
+
+
+@pytest.mark.parametrize("lanes", [1, 2, 3])
+@pytest.mark.parametrize("every,depth", [(6, 2), (8, 8), (1, 2), (4, 4)])
+def test_steps_on_alternating_caller_streams_keep_the_k_plus_d_parts_rule(lanes, every, depth):
+    for seed in range(60):
+        state, hazards = simulate_lanes(4, every + depth, 60, seed, every, depth, lanes)
+        assert state == "done" and not hazards, (seed, state, hazards[:3])
+    if lanes == 1:          # on one stream the rule is tight: one part fewer is one too few
+        bad = sum(bool(simulate_lanes(4, every + depth - 1, 60, seed, every, depth, lanes)[1]) for seed in range(200))
+        assert bad > 0

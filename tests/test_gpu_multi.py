@@ -30,19 +30,22 @@ def _worker(rank, world, port, tmp):
     lo, n = fd.shard_rows(rows, world, rank)
     local = torch.from_numpy(table[lo:lo + n]).to(dev)
     shards = [fd.shard_rows(rows, world, r) for r in range(world)]
-    for exchange, wire in (("compact", capi.F32), ("compact", capi.F16), ("compact+tickets", capi.F32),
+    for exchange, wire in (("compact", capi.F32), ("compact", capi.F16), ("compact+lanes", capi.F32),
+                           ("compact+lanes", capi.F16), ("push+lanes", capi.F32), ("stage+lanes", capi.F16),
+                           ("compact+tickets", capi.F32),
                            ("compact+ship", capi.F32), ("compact+ship", capi.F16), ("push+ship", capi.F32),
                            ("push", capi.F32), ("push", capi.F16), ("push+tickets", capi.F16),
                            ("stage", capi.F32),
                            ("stage", capi.F16), ("a2a", capi.F32), ("nccl", capi.F32)):
         tickets = exchange.endswith("+tickets")      # the pooling grid raises the flag itself
         ship = exchange.endswith("+ship")            # rows staged locally, sent by the copy kernel
+        lanes = 2 if exchange.endswith("+lanes") else 1   # consecutive steps on two alternating streams
         exchange = exchange.split("+")[0]
         for mode in (capi.MODE_SUM, capi.MODE_MEAN):
             bag = fd.RowShardedBag(local, lo, mode=mode, max_bags=nb, exchange=exchange,
                                    wire_dtype=wire, padding_idx=3, max_indices=80 * nb,
-                                   flag_from_pool=tickets, ship=ship)
-            for step in range(20 if exchange in ("compact", "push") else 3):   # beyond the eight buffer parts
+                                   flag_from_pool=tickets, ship=ship, lanes=lanes)
+            for step in range(20 if (exchange in ("compact", "push") or lanes > 1) else 3):   # beyond the buffer parts
                 brng = np.random.default_rng(100 + step)
                 bags = workloads.ragged_bags(rows, brng.integers(0, 80, nb), brng)
                 bags.indices[::11] = 3
@@ -100,18 +103,21 @@ def _worker(rank, world, port, tmp):
     owner = fd.place_tables([1] * ntab, world)
     trng = np.random.default_rng(17)
     tables = [trng.standard_normal((3000 + 100 * t, dim2)).astype(np.float32) for t in range(ntab)]
-    for exchange in ("push", "push+tickets", "push+ship", "nccl"):
+    for exchange in ("push", "push+lanes", "push+tickets", "push+ship", "nccl"):
         mine_t = [t for t in range(ntab) if owner[t] == rank]
         tw = fd.TableWiseBags({t: torch.from_numpy(tables[t]).to(dev) for t in mine_t}, owner,
                               dim=dim2, max_bags=nb2, exchange=exchange.split("+")[0], fixed_len=L,
-                              flag_from_pool=exchange.endswith("+tickets"), ship=exchange.endswith("+ship"))
-        for step in range(12 if exchange != "nccl" else 2):
+                              flag_from_pool=exchange.endswith("+tickets"), ship=exchange.endswith("+ship"),
+                              lanes=2 if exchange.endswith("+lanes") else 1)
+        for step in range(20 if exchange != "nccl" else 2):
             irng = np.random.default_rng(200 + step)
             idx = [irng.integers(0, tables[t].shape[0], (nb2, L)).astype(np.int32) for t in range(ntab)]
             w = [irng.random(nb2 * L).astype(np.float32) for _ in range(ntab)]
             inputs = {t: (torch.from_numpy(idx[t]).to(dev), None, torch.from_numpy(w[t]).to(dev))
                       for t in mine_t}
             res = tw.forward(inputs)
+            if step % 3 != 2 and exchange != "nccl":
+                continue          # steps queued back to back (on alternating streams with lanes), then one is checked
             tw.sync_result()
             torch.cuda.synchronize()
             expect = np.stack([O.pool(tables[t], idx[t], fixed_len=L, per_sample_weights=w[t])
@@ -133,11 +139,12 @@ def _worker(rank, world, port, tmp):
     d_tables = {t: torch.from_numpy(tables[t]).to(dev) for t in here}
     per = fd.bags_per_rank(nb3, world)
     blo, mine_b = fd.owned_bags(nb3, world, rank)
-    for exchange in ("push", "nccl"):
+    for exchange in ("push", "push+lanes", "nccl"):
         for fixed in (L, 0):
-            tw = fd.TableWiseBags(d_tables, owner, dim=dim2, max_bags=nb3, exchange=exchange, fixed_len=fixed,
-                                  mode=capi.MODE_SUM if fixed else capi.MODE_MEAN)
-            for step in range(20 if exchange == "push" else 2):
+            tw = fd.TableWiseBags(d_tables, owner, dim=dim2, max_bags=nb3, exchange=exchange.split("+")[0],
+                                  fixed_len=fixed, mode=capi.MODE_SUM if fixed else capi.MODE_MEAN,
+                                  lanes=2 if exchange.endswith("+lanes") else 1)
+            for step in range(20 if exchange != "nccl" else 2):
                 irng = np.random.default_rng(300 + step)
                 if fixed:
                     idx = [irng.integers(0, sizes[t], (nb3, L)).astype(np.int32) for t in range(ntab)]
@@ -149,7 +156,7 @@ def _worker(rank, world, port, tmp):
                     inputs = {t: (torch.from_numpy(bgs[t].indices).to(dev), torch.from_numpy(bgs[t].offsets).to(dev),
                                   None) for t in here}
                 res = tw.forward(inputs)
-                if step % 5 != 4 and exchange == "push":
+                if step % 5 != 4 and exchange != "nccl":
                     continue
                 tw.sync_result()
                 torch.cuda.synchronize()
