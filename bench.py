@@ -913,9 +913,12 @@ def timed_regions(wl, steps: int, regions: int, barrier, multi: bool):
     step = wl.step
     sync_result = wl.bag.sync_result if multi else None
     fork, join = getattr(wl, "fork", None), getattr(wl, "join", None)
+    order = wl.bag.order_behind_current if multi else None
     for r in range(regions):
         barrier()
         begin[r].record()
+        if order:
+            order()          # N > 1: the step streams start behind the start event
         if fork:
             fork()           # N = 1: the other lanes' streams start behind the start event
         for k in range(steps):

@@ -260,6 +260,15 @@ class _StepLanes:
         self.events = [torch.cuda.Event() for _ in self.streams]
         self.calls = 0
 
+    def fork(self):
+        """Put every lane behind the current stream's position once (then steps may be issued with
+        inputs_ready=True until the current stream produces something they need again)."""
+        import torch
+        cur = torch.cuda.current_stream()
+        for ev, st in zip(self.events, self.streams):
+            ev.record(cur)
+            st.wait_event(ev)
+
     def next(self, inputs_ready: bool = False):
         """(lane number, stream) of the next step; the current stream itself with one lane.
         `inputs_ready`: the caller vouches that nothing queued on the current stream produces this
@@ -437,6 +446,11 @@ class RowShardedBag:
         if self.out32 is not self.out:
             self.out.copy_(self.out32)
         return self.out[:mine]
+
+    def order_behind_current(self):
+        """Steps issued from now on start behind whatever is queued on the current stream (see
+        _StepLanes.fork); forward(..., inputs_ready=True) relies on it."""
+        self._lanes.fork()
 
     def sync_result(self):
         """Make the current stream wait until the result of the last forward() is complete.
@@ -671,6 +685,11 @@ class TableWiseBags:
             self.result[:, ts, :] = block
             pos += self.per * len(ts)
         return self.result
+
+    def order_behind_current(self):
+        """Steps issued from now on start behind whatever is queued on the current stream (see
+        _StepLanes.fork); forward(..., inputs_ready=True) relies on it."""
+        self._lanes.fork()
 
     def sync_result(self):
         """Make the current stream wait until the result of the last forward() is complete (the
