@@ -53,7 +53,9 @@ extern "C" {
  * (up to FWD_EB_PIPELINE_MAIN_STREAMS of them; a stream beyond that waits on every call): a
  * step waits, on its own stream, unless that stream is already behind this rank's fold of some
  * call >= e-(k-1)-d, which is all the argument above uses.  Flags, waits and folds stay in call
- * order on the pipeline's side stream whatever stream a step came in on.
+ * order on the pipeline's side stream whatever stream a step came in on.  A pipeline is driven
+ * by one host thread, and a caller stream it has seen must stay alive (its handle must not be
+ * reused for another stream) while the pipeline is in use.
  * The CPU model of these rules (tests/test_exchange_protocol.py) finds no overwrite of an
  * unfolded part with them and does find one with fewer parts. */
 #define FWD_EB_PIPELINE_WAIT_EVERY 6
