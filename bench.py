@@ -942,6 +942,7 @@ def isolated_launch_us(wl, samples: int = 40):
           for _ in range(samples)]
     for k in range(samples):
         wl.step(k, events=ev[k])
+        ev[k][1].synchronize()     # one step at a time: with steps alternating over streams two would overlap
     if wl.bag is not None:
         wl.bag.sync_result()
     torch.cuda.synchronize()
