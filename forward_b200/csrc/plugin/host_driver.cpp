@@ -31,6 +31,14 @@ struct fwd_eb_host {
   std::string layer_name;
   std::vector<char> blob;
   bool configured{false};
+  // every way out of build / load / clone, the failing ones included, releases the engine's
+  // plugin the way TensorRT does: terminate, then destroy
+  ~fwd_eb_host() {
+    if (engine_plugin) {
+      engine_plugin->terminate();
+      engine_plugin->destroy();
+    }
+  }
 };
 
 namespace {
@@ -71,14 +79,7 @@ void FillDescs(fwd_eb_host* h, mini_trt::Layer* layer) {
 
 extern "C" {
 
-void fwd_eb_host_free(fwd_eb_host* h) {
-  if (!h) return;
-  if (h->engine_plugin) {
-    h->engine_plugin->terminate();
-    h->engine_plugin->destroy();
-  }
-  delete h;
-}
+void fwd_eb_host_free(fwd_eb_host* h) { delete h; }
 
 fwd_eb_host* fwd_eb_host_build_desc(const void* embedding_bag_desc, int idx_rank, const int* idx_dims,
                                     int off_rank, const int* off_dims, int weights_rank,
