@@ -645,6 +645,7 @@ size_t fwd_eb_workspace_size(const fwd_eb_params* p) {
 }
 
 int fwd_eb_forward(const fwd_eb_params* p, void* stream) {
+  NvtxRange range("fwd_eb_forward");
   Plan pl;
   int rc = make_plan(p, &pl);
   if (rc) return rc;
@@ -681,6 +682,7 @@ ManyStreams g_many[kManyDevices];
 }  // namespace
 
 int fwd_eb_forward_many(const fwd_eb_params* const* params, int32_t count, void* stream) {
+  NvtxRange range("fwd_eb_forward_many");
   if (count < 0 || (count > 0 && !params)) return fail(FWD_EB_EINVAL, "bad argument list");
   for (int i = 0; i < count; ++i) {   // everything is checked before anything is launched
     if (!params[i]) return fail(FWD_EB_EINVAL, "params[%d] is null", i);
@@ -731,6 +733,7 @@ int fwd_eb_forward_many(const fwd_eb_params* const* params, int32_t count, void*
 
 int fwd_eb_compact_window(const fwd_eb_params* p, int32_t* d_kept, float* d_kept_weights,
                           int32_t* d_bounds, int32_t* d_counts, void* stream) {
+  NvtxRange range("fwd_eb_compact_window");
   if (!p) return fail(FWD_EB_EINVAL, "params is null");
   if (p->num_rows < 0 || p->num_indices < 0 || p->num_bags < 0) return fail(FWD_EB_EINVAL, "negative size");
   if (p->num_rows > INT_MAX)

@@ -867,6 +867,7 @@ int fwd_eb_pipeline_step_rowshard(fwd_eb_pipeline* pl, const fwd_eb_params* p,
                                   fwd_eb_shard_exchange* x, int64_t num_bags_owned,
                                   void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
                                   void* main_stream, int32_t* which) {
+  NvtxRange range("fwd_eb_pipeline_step_rowshard");
   if (!pl || !p || !x || !d_out) return fail(FWD_EB_EINVAL, "null argument");
   cudaStream_t main = static_cast<cudaStream_t>(main_stream);
   int rc = pipeline_begin(pl, x, main);
@@ -896,6 +897,7 @@ int fwd_eb_pipeline_step_rowshard_compact(fwd_eb_pipeline* pl, const fwd_eb_para
                                           const fwd_eb_compact_scratch* scratch,
                                           void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
                                           void* main_stream, int32_t* which) {
+  NvtxRange range("fwd_eb_pipeline_step_rowshard_compact");
   if (!pl || !p || !x || !d_out || !scratch) return fail(FWD_EB_EINVAL, "null argument");
   if (x->layout != FWD_EB_LAYOUT_ROW_SHARD)
     return fail(FWD_EB_EINVAL, "window compaction is for the row-shard layout");
@@ -983,6 +985,7 @@ int fwd_eb_pipeline_step_rowshard_staged(fwd_eb_pipeline* pl, const fwd_eb_param
                                          void* const d_stage[FWD_EB_SHARD_BUFFERS],
                                          void* const d_out[FWD_EB_SHARD_BUFFERS], int32_t out_dtype,
                                          void* main_stream, int32_t* which) {
+  NvtxRange range("fwd_eb_pipeline_step_rowshard_staged");
   if (!pl || !p || !x || !d_out || !d_stage) return fail(FWD_EB_EINVAL, "null argument");
   int rc = 0;
   if (x->layout != FWD_EB_LAYOUT_ROW_SHARD)
@@ -1032,6 +1035,7 @@ int fwd_eb_pipeline_step_tablewise_hybrid(fwd_eb_pipeline* pl, const fwd_eb_para
                                           const int32_t* local_table_index, int32_t local_count,
                                           fwd_eb_shard_exchange* x, int32_t dim, void* main_stream,
                                           void** d_result) {
+  NvtxRange range("fwd_eb_pipeline_step_tablewise_hybrid");
   if (!pl || !x || count < 0 || (count > 0 && (!params || !table_index)) || local_count < 0 ||
       (local_count > 0 && (!local_params || !local_table_index)))
     return fail(FWD_EB_EINVAL, "null argument");
