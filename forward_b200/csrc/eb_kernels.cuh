@@ -616,7 +616,7 @@ eb_pool_group_kernel(const PoolArgs a) {
 constexpr int kNoPos = 0x7fffffff;
 
 template <typename TW, int VE>
-__global__ void __launch_bounds__(kCtaThreads)
+__global__ void __launch_bounds__(kCtaThreads, FWD_EB_MIN_CTAS)
 eb_pool_maxpos_kernel(const PoolArgs a) {
   using V = typename Chunk<TW, VE>::type;
   const int lanes_log2 = a.lanes_log2;
