@@ -1046,8 +1046,9 @@ int fwd_eb_pipeline_step_tablewise_hybrid(fwd_eb_pipeline* pl, const fwd_eb_para
   int rc = pipeline_begin(pl, x, main);
   if (rc) return rc;
   const bool from_push = x->tickets != nullptr && count > 0 && !x->stage;
-  if (x->stage && count > kShipMaxTables)
-    return fail(FWD_EB_ETOOBIG, "shipping takes at most %d tables per rank and step (got %d)", kShipMaxTables, count);
+  if (x->stage && count > kShipMaxTables)   // nothing launched yet: take the call number back
+    return pipeline_abort(pl, fail(FWD_EB_ETOOBIG, "shipping takes at most %d tables per rank and step (got %d)",
+                                   kShipMaxTables, count));
   // The step's launches are independent of each other (one table each): they are spread over
   // the caller's stream and the auxiliary streams, which start where the caller's stream stands
   // now and are joined before the hand-over, so that a grid of one or two waves runs beside
