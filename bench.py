@@ -1101,6 +1101,10 @@ def measure(workload: str, args, world: int, rank: int, dev, sampler=None, *, st
         roofline["note"] = ("Zipf indices: hot rows are served from L1 / L2 (DRAM traffic is `traffic`, a fifth of the "
                             "algorithmic bytes), so `frac` can exceed 1; the HBM-bound figure of this kernel is "
                             "`roofline_uniform` (same shape, uniform indices)")
+    if workload == "c2u":
+        roofline["note"] = ("uniform indices over a 256 MB table: the 126 MB L2 still serves about a fifth of the row "
+                            "reads (`traffic` against `algorithmic_bytes_per_launch`), so `frac`, which counts every "
+                            "repeated row, can exceed 1; `dram_frac` is what DRAM moved over the same time")
     if workload == "c4":
         roofline["launches_per_step"] = wl.launches_per_step
         roofline["note"] = "kernel_us_* and the bytes cover one step = all of this rank's tables"
@@ -1137,7 +1141,7 @@ def extra_object(m: dict) -> dict:
          "roofline": {k: m["roofline"][k] for k in ("achieved", "peak", "frac", "frac_of_8000", "traffic",
                                                      "kernel_us_mean", "algorithmic_bytes_per_launch",
                                                      "peak_kind")}}
-    for k in ("kernel_us_one_stream", "streams", "dram_achieved", "dram_frac"):
+    for k in ("kernel_us_one_stream", "streams", "dram_achieved", "dram_frac", "note"):
         if k in m["roofline"]:
             o["roofline"][k] = m["roofline"][k]
     if m["exchange"]:
