@@ -1529,7 +1529,9 @@ def run_e2e_multi(args, wl, rank, world, dev):
     d2h = int(np.prod(shape)) * h_out[0].element_size()
     return {"value": lookups / dt, "unit": "lookups/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h, "ms_per_step": dt / args.steps * 1e3,
-            "note": "bytes are per rank", "api": "forward_b200.dist forward()"}
+            "note": "bytes are per rank; at N > 1 this leg is bound by the host (N processes share its memory "
+                    "bandwidth and cores for the pinned copies), not by the GPUs or NVLink",
+            "api": "forward_b200.dist forward()"}
 
 
 def main():
