@@ -168,3 +168,40 @@ def test_sharded_bag_refuses_combinations_it_cannot_honour(tmp_path):
         assert len(lines) == 4 and "accepted" not in lines
         assert "exchange='stage'" in lines[0] and "exchange='stage'" in lines[1]
         assert "belongs to max" in lines[2] and "sum, mean and max" in lines[3]
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("num_bags", [1022, 1024, 5, 1])
+def test_own_bags_of_all_ranks_cover_a_batch_exactly_once(world, num_bags):
+    """Replicated tables: the ranks' own-bag slices, fixed-length and ragged, put together give the
+    whole batch, each bag once and with its own indices."""
+    import types
+
+    import torch
+    own = fd.TableWiseBags._own_bags
+    per = fd.bags_per_rank(num_bags, world)
+    L = 3
+    idx = torch.arange(num_bags * L, dtype=torch.int32)
+    seen = []
+    for rank in range(world):
+        got = own(types.SimpleNamespace(rank=rank, per=per, fixed_len=L), idx.view(num_bags, L), None, None)
+        if got is not None:
+            seen += got[0].tolist()
+    assert seen == idx.tolist()
+    rng = np.random.default_rng(num_bags * 10 + world)
+    lengths = rng.integers(0, 5, num_bags)
+    off = torch.from_numpy(np.concatenate([[0], np.cumsum(lengths)[:-1]]).astype(np.int32))
+    total = int(lengths.sum())
+    ridx = torch.arange(total, dtype=torch.int32)
+    bags = []
+    for rank in range(world):
+        got = own(types.SimpleNamespace(rank=rank, per=per, fixed_len=0), ridx, off, None)
+        if got is None:
+            continue
+        i, o, _, incl = got
+        starts = o.tolist()
+        n = len(starts) - (1 if incl else 0)
+        ends = starts[1:] + ([] if incl else [total])
+        bags += [(starts[b], ends[b]) for b in range(n)]
+    expect = list(zip(off.tolist(), off.tolist()[1:] + [total]))
+    assert bags == expect
