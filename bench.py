@@ -2,8 +2,9 @@
 """Throughput of the EmbeddingBag gather-and-pool path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload auto|c2|tablewise|rowshard|c5|c3|c4] [--exchange push|stage|a2a|nccl]
-                    [--wire f32|f16]
+                    [--workload auto|c2|c2u|tablewise|rowshard|c5|c3|c4]
+                    [--exchange auto|compact|push|stage|a2a|nccl] [--wire f32|f16] [--streams 1|2]
+                    [--regions R] [--lookback EVERY,DEPTH] [--c4-replicate-mb M] [--local-streams 0|1|2]
 
 One "step" is one pooled call over one synthetic batch.  Rank 0 prints ONE JSON line.
 
@@ -22,14 +23,19 @@ Workloads (all synthetic: shapes and distributions only, rotating index batches 
   c3         N = 1.  Table 4,000,000 x 256 fp16, 8192 bags of 0..64 uniform indices, 5 % of the
              indices are padding_idx 0, max pooling.
   c4         N >= 1.  26 tables of 1e3..3e7 rows x 128 fp32 (42 GB in all), 65536 bags of exactly
-             20 Zipf(1.1) indices per table with per-sample weights, sum.  Tables are placed
-             whole on ranks (greedy by lookups, then bytes); every rank pools the whole batch
-             for its tables and the pooled rows go to [65536/N, 26, 128] fp32 on the rank owning
-             the bag.  Strong scaling; N = 1 holds all 26 tables.
+             20 Zipf(1.1) indices per table with per-sample weights, sum.  Tables under
+             --c4-replicate-mb MiB (default 256: 18 of the 26) live on every rank, which pools
+             its own bags of them; the others are placed whole on one rank each (greedy by
+             lookups, then bytes), pooled there for the whole batch, and their rows go to
+             [65536/N, 26, 128] fp32 on the rank owning the bag.  Strong scaling; N = 1 holds
+             all 26 tables and pools them with fwd_eb_forward_many.
   auto       c2 at N = 1, tablewise at N > 1.
 
 `value` times K steps on data resident in HBM (CUDA events, barrier + synchronize on both sides,
-max over ranks); `roofline` is the pooling kernel's algorithmic bytes over its mean event time;
+max over ranks; the median of --regions such regions).  Steps are independent batches and, with
+--streams 2 (the default), alternate over two CUDA streams per GPU, each with its own output and
+scratch, so that one step's grid runs beside the tail of the step before; --streams 1 queues every
+step on one stream (`roofline.kernel_us_one_stream` carries that figure in the default line too); `roofline` is the pooling kernel's algorithmic bytes over its mean event time;
 `e2e` repeats the steps with inputs copied from pinned host memory and results copied back every
 step; `cpu_baseline` / `--impl reference` time torch CPU EmbeddingBag (the ground truth of the
 reference's own unit test and the CPU baseline the metric names) on the same workload.
